@@ -1,0 +1,608 @@
+// Host runtime and C ABI (include/gtm_b200.h) of the B200-native Graph Tsetlin Machine engine.
+#include "../../include/gtm_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "gtm_host.cuh"
+#include "gtm_kernels.cuh"
+#include "gtm_stream.cuh"
+
+using namespace gtm;
+
+// ---------------------------------------------------------------------------------------------- handles
+struct gtm_model {
+    gtm_config cfg;
+    DevModel dm;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    bool has_state = false;
+    u32 *recorded = nullptr;
+    // learning-kernel buffers
+    int fit_grid = 0, fit_block = 512;
+    int *partial = nullptr, *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
+    unsigned *barrier = nullptr;
+    // node-stream scoring: derived include lists (rebuilt when the automata changed)
+    StreamModel sm;
+    bool lists_dirty = true;
+};
+
+struct gtm_dataset {
+    gtm_model *model;
+    DevGraphs dg;
+    int64_t n_graphs, total_nodes, total_edges;
+    int max_nodes, NC;
+    std::vector<void *> owned;
+    // learning scratch (every layer kept) and its message ping-pong
+    EvalScratch fit_sc;
+    u32 *P_pair[2] = {nullptr, nullptr};
+    // scoring scratch of the general path: one slice per CTA
+    EvalScratch score_sc;
+    size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
+    int score_grid = 0;
+    int *Y = nullptr;
+    size_t Y_capacity = 0;
+    // node-stream scoring
+    StreamData sd;
+};
+
+static int bind(gtm_model *m)
+{
+    if (!m) return fail(GTM_ERR_ARG, "null model handle");
+    GTM_CU(cudaSetDevice(m->cfg.device));
+    return GTM_OK;
+}
+
+static int words_for(int bits) { return (bits - 1) / 32 + 1; }
+static u32 tail_mask(int bits) { return (bits % 32) ? ~(0xffffffffu << (bits % 32)) : 0xffffffffu; }
+static int layer_words(const gtm_model *m, int layer) { return layer == 0 ? m->dm.L0 : m->dm.M; }
+
+// --------------------------------------------------------------------------------------------- library
+extern "C" const char *gtm_version(void) { return "gtm_b200 0.1 (sm_100a)"; }
+extern "C" const char *gtm_last_error(void) { return gtm_error_text().c_str(); }
+
+extern "C" int gtm_device_count(int *count_out)
+{
+    if (!count_out) return fail(GTM_ERR_ARG, "count_out is null");
+    GTM_CU(cudaGetDeviceCount(count_out));
+    return GTM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- model
+extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
+{
+    if (!cfg || !out) return fail(GTM_ERR_ARG, "null argument");
+    *out = nullptr;
+    if (cfg->number_of_clauses < 1 || cfg->number_of_outputs < 1 || cfg->number_of_literals < 1)
+        return fail(GTM_ERR_ARG, "clauses, outputs and literals must be positive");
+    if (cfg->number_of_state_bits < 1 || cfg->number_of_state_bits > GTM_MAX_STATE_BITS)
+        return fail(GTM_ERR_ARG, "number_of_state_bits must be in 1..%d", GTM_MAX_STATE_BITS);
+    if (cfg->depth < 1 || cfg->depth > GTM_MAX_DEPTH) return fail(GTM_ERR_ARG, "depth must be in 1..%d", GTM_MAX_DEPTH);
+    if (cfg->T < 1) return fail(GTM_ERR_ARG, "T must be positive");
+    if (cfg->depth > 1 && (cfg->message_size < 1 || cfg->message_bits < 1))
+        return fail(GTM_ERR_ARG, "message_size and message_bits must be positive when depth > 1");
+    for (int d = 0; d < cfg->depth; ++d)
+        if (!(cfg->s[d] > 0.0f)) return fail(GTM_ERR_ARG, "s[%d] must be positive", d);
+    int ndev = 0;
+    GTM_CU(cudaGetDeviceCount(&ndev));
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(GTM_ERR_ARG, "device %d out of range (%d visible)", cfg->device, ndev);
+    GTM_CU(cudaSetDevice(cfg->device));
+
+    gtm_model *m = new (std::nothrow) gtm_model();
+    if (!m) return fail(GTM_ERR_OOM, "host allocation failed");
+    m->cfg = *cfg;
+    DevModel &d = m->dm;
+    memset(&d, 0, sizeof d);
+    d.C = cfg->number_of_clauses; d.K = cfg->number_of_outputs; d.literals = cfg->number_of_literals;
+    d.SB = cfg->number_of_state_bits; d.boost = cfg->boost_true_positive_feedback; d.T = cfg->T;
+    d.max_included = cfg->max_included_literals; d.MS = std::max(1, cfg->message_size);
+    d.MB = std::max(1, cfg->message_bits); d.D = cfg->depth;
+    d.L0 = words_for(d.literals); d.M = words_for(2 * d.MS); d.MW = words_for(d.MS);
+    d.lit_mask = tail_mask(d.literals); d.msg_mask = tail_mask(2 * d.MS);
+    for (int i = 0; i < kMaxDepth; ++i) d.s[i] = cfg->s[i];
+    d.q_keep = 1.0 * cfg->q / (double)std::max(1, d.K - 1);
+    d.seed_lo = (u32)cfg->seed; d.seed_hi = (u32)(cfg->seed >> 32);
+
+    cudaDeviceProp prop;
+    GTM_CU(cudaGetDeviceProperties(&prop, cfg->device));
+    m->sm_count = prop.multiProcessorCount;
+
+    int st = GTM_OK;
+    for (int l = 0; l < d.D && st == GTM_OK; ++l) st = dev_alloc(&d.ta[l], (size_t)d.C * d.SB * (l == 0 ? d.L0 : d.M));
+    u32 *hv = nullptr;
+    if (st == GTM_OK) st = dev_alloc(&d.weights, (size_t)d.K * d.C);
+    if (st == GTM_OK) st = dev_alloc(&hv, (size_t)d.C * d.MB);
+    if (st == GTM_OK) st = dev_alloc(&d.draw_pos, (size_t)d.C);
+    if (st == GTM_OK) st = dev_alloc(&m->clause_node, (size_t)d.C);
+    if (st == GTM_OK) st = dev_alloc(&m->update, (size_t)d.K * d.C);
+    if (st == GTM_OK) st = dev_alloc(&m->class_sum_tap, (size_t)d.K);
+    if (st == GTM_OK) st = dev_alloc(&m->barrier, 1);
+    if (st == GTM_OK) st = dev_alloc(&m->error, 1);
+    if (st != GTM_OK) { gtm_destroy(m); return st; }
+    d.hv = hv;
+    cudaMemset(hv, 0, (size_t)d.C * d.MB * sizeof(u32));
+    cudaMemset(d.draw_pos, 0, (size_t)d.C * sizeof(u64));
+    cudaMemset(d.weights, 0, (size_t)d.K * d.C * sizeof(int));
+
+    // learning grid: all CTAs must be co-resident (cooperative launch); no more warps than clauses
+    int per_sm = 0;
+    size_t smem = 2 * (size_t)d.K * sizeof(int);
+    cudaError_t e = d.SB <= 8
+        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<8>, m->fit_block, smem)
+        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<32>, m->fit_block, smem);
+    if (e != cudaSuccess || per_sm < 1) { gtm_destroy(m); return fail(GTM_ERR_CUDA, "learning kernel does not fit on this device: %s", cudaGetErrorString(e)); }
+    const int warps_per_cta = m->fit_block / 32;
+    m->fit_grid = std::max(1, std::min(m->sm_count * std::min(per_sm, 2), (d.C + warps_per_cta - 1) / warps_per_cta));
+    st = dev_alloc(&m->partial, 2 * (size_t)m->fit_grid * d.K);
+    if (st == GTM_OK) st = stream_model_create(&m->sm, d);
+    if (st != GTM_OK) { gtm_destroy(m); return fail(st, "device allocation failed"); }
+    *out = m;
+    return GTM_OK;
+}
+
+extern "C" int gtm_destroy(gtm_model *m)
+{
+    if (!m) return GTM_OK;
+    cudaSetDevice(m->cfg.device);
+    for (int l = 0; l < kMaxDepth; ++l) cudaFree(m->dm.ta[l]);
+    cudaFree(m->dm.weights); cudaFree((void *)m->dm.hv); cudaFree(m->dm.draw_pos); cudaFree(m->recorded);
+    cudaFree(m->partial); cudaFree(m->error); cudaFree(m->clause_node); cudaFree(m->update);
+    cudaFree(m->class_sum_tap); cudaFree(m->barrier);
+    stream_model_destroy(&m->sm);
+    delete m;
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_stream(gtm_model *m, void *stream)
+{
+    GTM_TRY(bind(m));
+    m->stream = (cudaStream_t)stream;
+    return GTM_OK;
+}
+
+extern "C" int gtm_init_state(gtm_model *m, int reset_message_layers)
+{
+    GTM_TRY(bind(m));
+    const DevModel &d = m->dm;
+    init_weights_kernel<<<(d.C + 255) / 256, 256, 0, m->stream>>>(d);
+    for (int l = 0; l < d.D; ++l) {
+        if (l > 0 && !reset_message_layers) break;
+        const size_t total = (size_t)d.C * d.SB * layer_words(m, l);
+        init_planes_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(d.ta[l], d.C, d.SB, layer_words(m, l));
+    }
+    GTM_CU(cudaGetLastError());
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    m->has_state = true;
+    m->lists_dirty = true;
+    return GTM_OK;
+}
+
+static int check_layer(gtm_model *m, int layer)
+{
+    if (layer < 0 || layer >= m->dm.D) return fail(GTM_ERR_ARG, "layer %d out of range (depth %d)", layer, m->dm.D);
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_ta_state(gtm_model *m, int layer, const uint32_t *ta)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_layer(m, layer));
+    if (!ta) return fail(GTM_ERR_ARG, "ta_state is null");
+    const DevModel &d = m->dm;
+    const int W = layer_words(m, layer);
+    const size_t total = (size_t)d.C * d.SB * W;
+    u32 *tmp;
+    GTM_TRY(dev_alloc(&tmp, total));
+    cudaError_t e = cudaMemcpyAsync(tmp, ta, total * sizeof(u32), cudaMemcpyHostToDevice, m->stream);
+    if (e == cudaSuccess) {
+        planes_from_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(tmp, d.ta[layer], d.C, d.SB, W);
+        e = cudaStreamSynchronize(m->stream);
+    }
+    cudaFree(tmp);
+    GTM_CU(e);
+    m->has_state = true;
+    m->lists_dirty = true;
+    return GTM_OK;
+}
+
+extern "C" int gtm_get_ta_state(gtm_model *m, int layer, uint32_t *out)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_layer(m, layer));
+    if (!out) return fail(GTM_ERR_ARG, "ta_state_out is null");
+    const DevModel &d = m->dm;
+    const int W = layer_words(m, layer);
+    const size_t total = (size_t)d.C * d.SB * W;
+    u32 *tmp;
+    GTM_TRY(dev_alloc(&tmp, total));
+    planes_to_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(d.ta[layer], tmp, d.C, d.SB, W);
+    cudaError_t e = cudaMemcpyAsync(out, tmp, total * sizeof(u32), cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    cudaFree(tmp);
+    GTM_CU(e);
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_weights(gtm_model *m, const int32_t *w)
+{
+    GTM_TRY(bind(m));
+    if (!w) return fail(GTM_ERR_ARG, "clause_weights is null");
+    GTM_CU(cudaMemcpyAsync(m->dm.weights, w, (size_t)m->dm.K * m->dm.C * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    m->lists_dirty = true;
+    return GTM_OK;
+}
+
+extern "C" int gtm_get_weights(gtm_model *m, int32_t *w)
+{
+    GTM_TRY(bind(m));
+    if (!w) return fail(GTM_ERR_ARG, "clause_weights_out is null");
+    GTM_CU(cudaMemcpyAsync(w, m->dm.weights, (size_t)m->dm.K * m->dm.C * sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_hypervectors(gtm_model *m, const uint32_t *hv)
+{
+    GTM_TRY(bind(m));
+    if (!hv) return fail(GTM_ERR_ARG, "hypervectors is null");
+    GTM_CU(cudaMemcpyAsync((void *)m->dm.hv, hv, (size_t)m->dm.C * m->dm.MB * sizeof(u32), cudaMemcpyHostToDevice, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    m->lists_dirty = true;
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_draw_positions(gtm_model *m, const uint64_t *pos)
+{
+    GTM_TRY(bind(m));
+    if (!pos) return fail(GTM_ERR_ARG, "positions is null");
+    GTM_CU(cudaMemcpyAsync(m->dm.draw_pos, pos, (size_t)m->dm.C * sizeof(u64), cudaMemcpyHostToDevice, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    return GTM_OK;
+}
+
+extern "C" int gtm_get_draw_positions(gtm_model *m, uint64_t *pos)
+{
+    GTM_TRY(bind(m));
+    if (!pos) return fail(GTM_ERR_ARG, "positions_out is null");
+    GTM_CU(cudaMemcpyAsync(pos, m->dm.draw_pos, (size_t)m->dm.C * sizeof(u64), cudaMemcpyDeviceToHost, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    return GTM_OK;
+}
+
+extern "C" int gtm_set_recorded_draws(gtm_model *m, const uint32_t *draws, uint64_t per_clause)
+{
+    GTM_TRY(bind(m));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    cudaFree(m->recorded);
+    m->recorded = nullptr; m->dm.recorded = nullptr; m->dm.recorded_len = 0;
+    if (!draws) return GTM_OK;
+    if (per_clause == 0) return fail(GTM_ERR_ARG, "draws_per_clause must be positive");
+    const size_t total = (size_t)m->dm.C * per_clause;
+    GTM_TRY(dev_alloc(&m->recorded, total));
+    GTM_CU(cudaMemcpy(m->recorded, draws, total * sizeof(u32), cudaMemcpyHostToDevice));
+    m->dm.recorded = m->recorded;
+    m->dm.recorded_len = per_clause;
+    return GTM_OK;
+}
+
+// --------------------------------------------------------------------------------------------- datasets
+template <class T>
+static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s)
+{
+    T *p;
+    GTM_TRY(dev_alloc(&p, count));
+    ds->owned.push_back(p);
+    if (count && host) GTM_CU(cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, s));
+    *dev = p;
+    return GTM_OK;
+}
+
+template <class T>
+static int scratch(gtm_dataset *ds, T **dev, size_t count)
+{
+    GTM_TRY(dev_alloc(dev, count));
+    ds->owned.push_back(*dev);
+    return GTM_OK;
+}
+
+static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds)
+{
+    const DevModel &d = m->dm;
+    cudaStream_t s = m->stream;
+    GTM_TRY(upload(ds, &ds->dg.X, v->X, (size_t)v->total_nodes * d.L0, s));
+    GTM_TRY(upload(ds, &ds->dg.node_type, v->node_type, (size_t)v->total_nodes, s));
+    GTM_TRY(upload(ds, &ds->dg.degree, v->number_of_graph_node_edges, (size_t)v->total_nodes, s));
+    GTM_TRY(upload(ds, &ds->dg.edge_index, v->edge_index, (size_t)v->total_nodes, s));
+    GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s));
+    GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s));
+    GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s));
+    ds->dg.n_types = 1;
+
+    // learning scratch
+    const size_t p_words = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW;
+    ds->fit_sc.NC = ds->NC; ds->fit_sc.cno_slots = d.D; ds->fit_sc.max_nodes = ds->max_nodes;
+    GTM_TRY(scratch(ds, &ds->fit_sc.cno, (size_t)d.D * d.C * ds->NC));
+    GTM_TRY(scratch(ds, &ds->fit_sc.n_inc, (size_t)d.C));
+    GTM_TRY(scratch(ds, &ds->P_pair[0], p_words));
+    GTM_TRY(scratch(ds, &ds->P_pair[1], p_words));
+    ds->fit_sc.P = ds->P_pair[0];
+
+    // general scoring scratch: one slice per resident CTA
+    int per_sm = 0;
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_graphs_kernel, 256, (size_t)d.K * sizeof(int)));
+    ds->score_grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)m->sm_count * std::max(1, per_sm), v->number_of_graphs));
+    ds->cno_stride = (size_t)2 * d.C * ds->NC;
+    ds->P_stride = p_words;
+    ds->ninc_stride = (size_t)d.C;
+    ds->score_sc.NC = ds->NC; ds->score_sc.cno_slots = 2; ds->score_sc.max_nodes = ds->max_nodes;
+    GTM_TRY(scratch(ds, &ds->score_sc.cno, ds->cno_stride * ds->score_grid));
+    GTM_TRY(scratch(ds, &ds->score_sc.P, ds->P_stride * ds->score_grid));
+    GTM_TRY(scratch(ds, &ds->score_sc.n_inc, ds->ninc_stride * ds->score_grid));
+
+    GTM_TRY(stream_data_create(&ds->sd, m->sm, d, ds->dg, v, m->sm_count, s));
+    GTM_CU(cudaStreamSynchronize(s));
+    return GTM_OK;
+}
+
+extern "C" int gtm_dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **out)
+{
+    GTM_TRY(bind(m));
+    if (!v || !out) return fail(GTM_ERR_ARG, "null argument");
+    *out = nullptr;
+    if (v->number_of_graphs < 1 || v->total_nodes < 1) return fail(GTM_ERR_ARG, "empty graph set");
+    if (!v->X || !v->node_type || !v->number_of_graph_node_edges || !v->edge_index || !v->node_index || !v->number_of_graph_nodes)
+        return fail(GTM_ERR_ARG, "graph arrays must not be null");
+    if (v->total_edges > 0 && !v->edge) return fail(GTM_ERR_ARG, "edge array is null but total_edges > 0");
+    if (v->max_number_of_graph_nodes < 1) return fail(GTM_ERR_ARG, "max_number_of_graph_nodes must be positive");
+    if (v->total_nodes >= (int64_t)1 << 31 || v->total_edges >= (int64_t)1 << 31)
+        return fail(GTM_ERR_ARG, "graph sets beyond 2^31 nodes or edges are not supported");
+    gtm_dataset *ds = new (std::nothrow) gtm_dataset();
+    if (!ds) return fail(GTM_ERR_OOM, "host allocation failed");
+    ds->model = m;
+    ds->n_graphs = v->number_of_graphs; ds->total_nodes = v->total_nodes; ds->total_edges = v->total_edges;
+    ds->max_nodes = v->max_number_of_graph_nodes;
+    ds->NC = words_for(ds->max_nodes);
+    memset(&ds->sd, 0, sizeof ds->sd);
+    int st = dataset_build(m, v, ds);
+    if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
+    *out = ds;
+    return GTM_OK;
+}
+
+extern "C" int gtm_dataset_destroy(gtm_dataset *ds)
+{
+    if (!ds) return GTM_OK;
+    cudaSetDevice(ds->model->cfg.device);
+    cudaStreamSynchronize(ds->model->stream);
+    for (void *p : ds->owned) cudaFree(p);
+    cudaFree(ds->Y);
+    stream_data_destroy(&ds->sd);
+    delete ds;
+    return GTM_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- scoring
+static int check_range(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count)
+{
+    if (!ds || ds->model != m) return fail(GTM_ERR_ARG, "dataset does not belong to this model");
+    if (!m->has_state) return fail(GTM_ERR_STATE, "model has no state: call gtm_init_state or gtm_set_ta_state first");
+    if (n_types < 1) return fail(GTM_ERR_ARG, "number_of_node_types must be positive");
+    if (first < 0 || count < 0 || first + count > ds->n_graphs)
+        return fail(GTM_ERR_ARG, "graph range [%lld, %lld) outside the set of %lld graphs", (long long)first,
+                    (long long)(first + count), (long long)ds->n_graphs);
+    return GTM_OK;
+}
+
+static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
+                                int *sums_dev, int *clause_out_dev)
+{
+    DevGraphs g = ds->dg;
+    g.n_types = n_types;
+    ScoreArgs a;
+    a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = clause_out_dev;
+    a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
+    const int grid = (int)std::min<int64_t>(ds->score_grid, count);
+    score_graphs_kernel<<<grid, 256, (size_t)m->dm.K * sizeof(int), m->stream>>>(m->dm, g, ds->score_sc, a);
+    GTM_CU(cudaGetLastError());
+    return GTM_OK;
+}
+
+static int refresh_lists(gtm_model *m)
+{
+    if (!m->lists_dirty) return GTM_OK;
+    GTM_TRY(stream_model_refresh(&m->sm, m->dm, m->stream));
+    m->lists_dirty = false;
+    return GTM_OK;
+}
+
+extern "C" int gtm_score_device(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
+                                int32_t *sums_dev)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_range(m, ds, n_types, first, count));
+    if (count == 0) return GTM_OK;
+    if (!sums_dev) return fail(GTM_ERR_ARG, "class_sums_device is null");
+    if (stream_supported(ds->sd)) {
+        GTM_TRY(refresh_lists(m));
+        return stream_score(m->sm, ds->sd, m->dm, ds->dg, n_types, first, count, sums_dev, m->stream);
+    }
+    return launch_score_general(m, ds, n_types, first, count, sums_dev, nullptr);
+}
+
+extern "C" int gtm_score(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count, int32_t *out)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_range(m, ds, n_types, first, count));
+    if (count == 0) return GTM_OK;
+    if (!out) return fail(GTM_ERR_ARG, "class_sums_out is null");
+    int *dev;
+    GTM_TRY(dev_alloc(&dev, (size_t)count * m->dm.K));
+    int st = gtm_score_device(m, ds, n_types, first, count, dev);
+    cudaError_t e = cudaSuccess;
+    if (st == GTM_OK) {
+        e = cudaMemcpyAsync(out, dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    }
+    cudaFree(dev);
+    if (st != GTM_OK) return st;
+    GTM_CU(e);
+    return GTM_OK;
+}
+
+extern "C" int gtm_transform(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
+                             int32_t *clause_out, int32_t *sums_out)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_range(m, ds, n_types, first, count));
+    if (count == 0) return GTM_OK;
+    int *sums_dev = nullptr, *co_dev = nullptr;
+    GTM_TRY(dev_alloc(&sums_dev, (size_t)count * m->dm.K));
+    int st = dev_alloc(&co_dev, (size_t)count * m->dm.C);
+    if (st == GTM_OK) st = launch_score_general(m, ds, n_types, first, count, sums_dev, co_dev);
+    cudaError_t e = cudaSuccess;
+    if (st == GTM_OK && sums_out) e = cudaMemcpyAsync(sums_out, sums_dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (st == GTM_OK && e == cudaSuccess && clause_out) e = cudaMemcpyAsync(clause_out, co_dev, (size_t)count * m->dm.C * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    cudaFree(sums_dev); cudaFree(co_dev);
+    if (st != GTM_OK) return st;
+    GTM_CU(e);
+    return GTM_OK;
+}
+
+// --------------------------------------------------------------------------------------------- learning
+static int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
+                      int epochs, int eval_only)
+{
+    const DevModel &d = m->dm;
+    DevGraphs g = ds->dg;
+    g.n_types = n_types;
+    EvalScratch sc = ds->fit_sc;
+    FitArgs a;
+    a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
+    a.partial = m->partial; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
+    a.barrier = m->barrier; a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
+    a.class_sum_tap = m->class_sum_tap;
+    const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
+    GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
+    GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
+    if (d.D > 1) {
+        GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
+        GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
+    }
+    DevModel dm = d;
+    void *args[] = {&dm, &g, &sc, &a, &eval_only};
+    const size_t smem = 2 * (size_t)d.K * sizeof(int);
+    const void *fn = d.SB <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>;
+    GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
+    int err = 0;
+    GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    if (err) return fail(GTM_ERR_TIMEOUT, "a grid barrier of the learning kernel gave up waiting");
+    return GTM_OK;
+}
+
+extern "C" int gtm_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int32_t *Y, int64_t first, int64_t count, int epochs)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_range(m, ds, n_types, first, count));
+    if (!Y) return fail(GTM_ERR_ARG, "encoded_Y is null");
+    if (epochs < 0) return fail(GTM_ERR_ARG, "epochs must not be negative");
+    if (count == 0 || epochs == 0) return GTM_OK;
+    const size_t need = (size_t)ds->n_graphs * m->dm.K;
+    if (ds->Y_capacity < need) {
+        cudaFree(ds->Y); ds->Y = nullptr; ds->Y_capacity = 0;
+        GTM_TRY(dev_alloc(&ds->Y, need));
+        ds->Y_capacity = need;
+    }
+    GTM_CU(cudaMemcpyAsync(ds->Y + (size_t)first * m->dm.K, Y + (size_t)first * m->dm.K,
+                           (size_t)count * m->dm.K * sizeof(int), cudaMemcpyHostToDevice, m->stream));
+    m->lists_dirty = true;
+    return launch_fit(m, ds, n_types, ds->Y, first, count, epochs, 0);
+}
+
+// ------------------------------------------------------------------------------------------------- taps
+extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, int64_t graph, int path,
+                                  uint32_t *cno_out, uint32_t *msg_out, int32_t *n_inc_out, int32_t *class_sum_out)
+{
+    GTM_TRY(bind(m));
+    GTM_TRY(check_range(m, ds, n_types, graph, 1));
+    const DevModel &d = m->dm;
+    std::vector<u32> nn(1), ni(1);
+    GTM_CU(cudaMemcpy(nn.data(), ds->dg.n_nodes + graph, sizeof(u32), cudaMemcpyDeviceToHost));
+    const int n = (int)nn[0], words = (n + 31) / 32;
+    if (path == 1) {
+        GTM_TRY(launch_fit(m, ds, n_types, nullptr, graph, 1, 1, 1));
+        if (cno_out)
+            for (int l = 0; l < d.D; ++l)
+                GTM_CU(cudaMemcpy2D(cno_out + (size_t)l * d.C * words, words * sizeof(u32),
+                                    ds->fit_sc.cno + (size_t)l * d.C * ds->NC, ds->NC * sizeof(u32),
+                                    words * sizeof(u32), d.C, cudaMemcpyDeviceToHost));
+        if (msg_out && d.D > 1) {
+            u32 *tmp;
+            GTM_TRY(dev_alloc(&tmp, (size_t)n * d.M));
+            for (int l = 0; l < d.D - 1; ++l) {
+                expand_messages_kernel<<<64, 256, 0, m->stream>>>(ds->P_pair[0] + (size_t)l * ds->max_nodes * d.MW, tmp, n, d.MS, d.MW, d.M);
+                cudaMemcpyAsync(msg_out + (size_t)l * n * d.M, tmp, (size_t)n * d.M * sizeof(u32), cudaMemcpyDeviceToHost, m->stream);
+            }
+            cudaError_t e = cudaStreamSynchronize(m->stream);
+            cudaFree(tmp);
+            GTM_CU(e);
+        }
+        if (n_inc_out) GTM_CU(cudaMemcpy(n_inc_out, ds->fit_sc.n_inc, (size_t)d.C * sizeof(int), cudaMemcpyDeviceToHost));
+        if (class_sum_out) GTM_CU(cudaMemcpy(class_sum_out, m->class_sum_tap, (size_t)d.K * sizeof(int), cudaMemcpyDeviceToHost));
+        return GTM_OK;
+    }
+    if (path == 0) {
+        // general scoring kernel with a one-CTA grid and every layer kept (scratch of the learning kernel)
+        DevGraphs g = ds->dg;
+        g.n_types = n_types;
+        int *sums;
+        GTM_TRY(dev_alloc(&sums, (size_t)d.K));
+        ScoreArgs a;
+        a.first = graph; a.count = 1; a.class_sums = sums; a.clause_outputs = nullptr;
+        a.cno_stride = a.P_stride = a.ninc_stride = 0;
+        EvalScratch sc = ds->fit_sc;
+        sc.P = ds->P_pair[0];
+        score_graphs_kernel<<<1, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
+        cudaError_t e = cudaStreamSynchronize(m->stream);
+        if (e == cudaSuccess && class_sum_out) e = cudaMemcpy(class_sum_out, sums, (size_t)d.K * sizeof(int), cudaMemcpyDeviceToHost);
+        cudaFree(sums);
+        GTM_CU(e);
+        if (cno_out)
+            for (int l = 0; l < d.D; ++l)
+                GTM_CU(cudaMemcpy2D(cno_out + (size_t)l * d.C * words, words * sizeof(u32),
+                                    ds->fit_sc.cno + (size_t)l * d.C * ds->NC, ds->NC * sizeof(u32),
+                                    words * sizeof(u32), d.C, cudaMemcpyDeviceToHost));
+        if (msg_out && d.D > 1) {
+            u32 *tmp;
+            GTM_TRY(dev_alloc(&tmp, (size_t)n * d.M));
+            for (int l = 0; l < d.D - 1; ++l) {
+                expand_messages_kernel<<<64, 256, 0, m->stream>>>(ds->P_pair[0] + (size_t)l * ds->max_nodes * d.MW, tmp, n, d.MS, d.MW, d.M);
+                cudaMemcpyAsync(msg_out + (size_t)l * n * d.M, tmp, (size_t)n * d.M * sizeof(u32), cudaMemcpyDeviceToHost, m->stream);
+            }
+            e = cudaStreamSynchronize(m->stream);
+            cudaFree(tmp);
+            GTM_CU(e);
+        }
+        if (n_inc_out) GTM_CU(cudaMemcpy(n_inc_out, ds->fit_sc.n_inc, (size_t)d.C * sizeof(int), cudaMemcpyDeviceToHost));
+        return GTM_OK;
+    }
+    return fail(GTM_ERR_ARG, "path must be 0 (scoring kernel) or 1 (learning kernel)");
+}
+
+extern "C" int gtm_debug_last_feedback(gtm_model *m, int32_t *clause_node_out, int32_t *update_out)
+{
+    GTM_TRY(bind(m));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    if (clause_node_out) GTM_CU(cudaMemcpy(clause_node_out, m->clause_node, (size_t)m->dm.C * sizeof(int), cudaMemcpyDeviceToHost));
+    if (update_out) GTM_CU(cudaMemcpy(update_out, m->update, (size_t)m->dm.K * m->dm.C * sizeof(int), cudaMemcpyDeviceToHost));
+    return GTM_OK;
+}

@@ -1,0 +1,209 @@
+// Device-side building blocks shared by the scoring and learning kernels: parameter blocks, the per-clause
+// Philox4x32-10 draw streams, bit-sliced automaton arithmetic and the per-layer clause evaluation.
+//
+// Internal layouts (device memory):
+//   ta[layer]   uint32[C][SB][W]   automaton planes of a clause are contiguous; plane SB-1 is the include mask;
+//                                  W = ceil(literals/32) for layer 0, ceil(2*message_size/32) for layers >= 1.
+//                                  (The reference keeps uint32[C][W][SB]: kernels.py:58,437.  Converted at the ABI.)
+//   weights     int32[K][C]        as the reference (kernels.py:312).
+//   hv          uint32[C][MB]      message hypervectors (kernels.py:567).
+//   cno         uint32[slots][C][NC]  node-output bits per layer, bit v%32 of word v/32 (kernels.py:463-465);
+//                                  only the bits of existing nodes are ever set.
+//   P           uint32[D-1][max_nodes][MW]  POSITIVE half of the message literals of every node, MW =
+//                                  ceil(message_size/32).  The reference materialises both halves
+//                                  (kernels.py:544-545,582-583,613); here the negated half is derived on the
+//                                  fly as the complement (msg_word).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gtm {
+
+typedef uint32_t u32;
+typedef uint64_t u64;
+
+constexpr int kMaxDepth = 16;
+constexpr int kMaxStateBits = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+struct DevModel {
+    int C, K, literals, SB, boost, T, max_included, MS, MB, D;
+    int L0, M, MW;             // words: layer-0 literals, message literals (both halves), positive message half
+    u32 lit_mask, msg_mask;    // valid bits of the last literal word (FILTER / MESSAGE_FILTER, kernels.py:37-47)
+    float s[kMaxDepth];
+    double q_keep;             // 1.0*Q/max(1, CLASSES-1)   (kernels.py:384)
+    u32 *ta[kMaxDepth];
+    int *weights;
+    const u32 *hv;
+    u64 *draw_pos;             // [C] draws consumed per clause stream
+    const u32 *recorded;       // optional [C][recorded_len]
+    u64 recorded_len;
+    u32 seed_lo, seed_hi;
+};
+
+struct DevGraphs {
+    const u32 *X, *node_type, *degree, *edge_index, *edge, *node_index, *n_nodes;
+    int n_types;
+};
+
+// Per-"context" scratch: one for the learning kernel, one per CTA for the scoring kernel.
+struct EvalScratch {
+    u32 *cno;       // [cno_slots][C][NC]
+    u32 *P;         // [D-1][max_nodes][MW]
+    int *n_inc;     // [C]
+    int NC;         // row stride of cno in words
+    int cno_slots;  // D (every layer kept) or 2 (ping-pong)
+    int max_nodes;
+};
+
+// ------------------------------------------------------------------------------------------------ Philox
+__device__ __forceinline__ void philox4x32_10(u32 c0, u32 c1, u32 c2, u32 c3, u32 k0, u32 k1, u32 out[4])
+{
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const u32 lo0 = 0xD2511F53u * c0, hi0 = __umulhi(0xD2511F53u, c0);
+        const u32 lo1 = 0xCD9E8D57u * c2, hi1 = __umulhi(0xCD9E8D57u, c2);
+        c0 = hi1 ^ c1 ^ k0; c1 = lo1;
+        c2 = hi0 ^ c3 ^ k1; c3 = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// Draw i of the stream of clause c: component (i & 3) of Philox(counter = (i>>2, i>>34, c, 0)), or the recorded word.
+__device__ __forceinline__ u32 draw_at(const DevModel &m, int clause, u64 i)
+{
+    if (m.recorded) return m.recorded[(u64)clause * m.recorded_len + i % m.recorded_len];
+    u32 o[4];
+    philox4x32_10((u32)(i >> 2), (u32)(i >> 34), (u32)clause, 0u, m.seed_lo, m.seed_hi, o);
+    const u32 sel = (u32)i & 3u;
+    return sel == 0 ? o[0] : sel == 1 ? o[1] : sel == 2 ? o[2] : o[3];
+}
+
+// (0, 1] mapping of curand_uniform: x * 2^-32 + 2^-33 in float (the product is exact, so one rounding either way).
+__device__ __forceinline__ float to_uniform(u32 x)
+{
+    return __fadd_rn(__fmul_rn((float)x, 2.3283064365386963e-10f), 1.1641532182693481e-10f);
+}
+
+// ------------------------------------------------------------------------------------- message literal words
+// Word w of a node's message literal vector in the reference's layout (2*MS literals: first the MS message bits,
+// then their complements, zero padding; kernels.py:544-545,607-613), from the node's positive bits Prow[MW].
+__device__ __forceinline__ u32 msg_word(const u32 *Prow, int w, int MS, int MW)
+{
+    if ((MS & 31) == 0) return w < MW ? Prow[w] : ~Prow[w - MW];
+    const int lo = 32 * w;
+    u32 r = 0;
+    if (lo < MS) {
+        u32 p = Prow[w];
+        if (lo + 32 > MS) p &= (1u << (MS - lo)) - 1u;
+        r = p;
+    }
+    if (lo + 32 > MS && lo < 2 * MS) {
+        const int l0 = lo > MS ? lo : MS;              // first negated literal inside this word
+        const int off = l0 - MS;                       // its bit index in Prow
+        const int hi = lo + 32 < 2 * MS ? lo + 32 : 2 * MS;
+        const int cnt = hi - l0;
+        u32 a = Prow[off >> 5] >> (off & 31);
+        if ((off & 31) && (off >> 5) + 1 < MW) a |= Prow[(off >> 5) + 1] << (32 - (off & 31));
+        a = ~a;
+        if (cnt < 32) a &= (1u << cnt) - 1u;
+        r |= a << (l0 - lo);
+    }
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------- clause evaluation
+// One warp evaluates clause `c` at layer `d` over all nodes of graph e (lanes = the 32 nodes of a node word) and
+// writes cno[slot(d)][c][*].  Layer 0 tests the node's literal row, layer d >= 1 the node's message row ANDed
+// with the node's bit of layer d-1 (kernels.py:407-530).  Returns the OR of the words written (warp-uniform).
+// When `scatter` is set, every true node sends the clause's hypervector bits along its out-edges into P[d]
+// (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
+__device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const DevGraphs &g, const EvalScratch &sc,
+                                                 int c, int d, int n, int base, int lane, bool scatter)
+{
+    const int W = d == 0 ? m.L0 : m.M;
+    const u32 *inc = m.ta[d] + ((size_t)c * m.SB + (m.SB - 1)) * W;
+    const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
+    const int slot = sc.cno_slots == 2 ? (d & 1) : d;
+    const int pslot = sc.cno_slots == 2 ? ((d - 1) & 1) : d - 1;
+    u32 *out = sc.cno + ((size_t)slot * m.C + c) * sc.NC;
+    const u32 *prev = d > 0 ? sc.cno + ((size_t)pslot * m.C + c) * sc.NC : nullptr;
+    const u32 my_type = (u32)(c % g.n_types);
+
+    // include count of this layer (kernels.py:251-277); lanes stride over words
+    int cnt = 0;
+    for (int w = lane; w < W; w += 32) cnt += __popc(inc[w] & (w == W - 1 ? last_mask : kFull));
+    cnt = __reduce_add_sync(kFull, cnt);
+    if (lane == 0) sc.n_inc[c] = (d == 0 ? 0 : sc.n_inc[c]) + cnt;
+
+    const int words = (n + 31) >> 5;
+    u32 any = 0;
+    for (int j = 0; j < words; ++j) {
+        const int v = j * 32 + lane;
+        bool ok = v < n;
+        if (d > 0) {
+            const u32 pw = prev[j];
+            if (pw == 0) { if (lane == 0) out[j] = 0; continue; }       // uniform: nothing can stay true
+            ok = ok && ((pw >> lane) & 1u);
+        }
+        ok = ok && g.node_type[base + (ok ? v : 0)] == my_type;
+        if (__any_sync(kFull, ok)) {
+            const u32 *row = d == 0 ? g.X + (size_t)(base + (v < n ? v : 0)) * W
+                                    : sc.P + ((size_t)(d - 1) * sc.max_nodes + (v < n ? v : 0)) * m.MW;
+            for (int w = 0; w < W; ++w) {
+                u32 iw = inc[w];   // plain load: the learning kernel rewrites these planes
+                if (w == W - 1) iw &= last_mask;
+                if (iw == 0) continue;                                   // uniform
+                const u32 x = d == 0 ? row[w] : msg_word(row, w, m.MS, m.MW);
+                ok = ok && ((iw & ~x) == 0);
+                if (!__any_sync(kFull, ok)) break;                       // warp-ballot early exit
+            }
+        }
+        const u32 word = __ballot_sync(kFull, ok);
+        if (lane == 0) out[j] = word;
+        any |= word;
+        if (scatter && ok) {
+            const u32 e0 = g.edge_index[base + v], deg = g.degree[base + v];
+            u32 *Pd = sc.P + (size_t)d * sc.max_nodes * m.MW;
+            for (u32 k = 0; k < deg; ++k) {
+                const u32 dst = g.edge[2 * (size_t)(e0 + k)], t = g.edge[2 * (size_t)(e0 + k) + 1];
+                if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
+                for (int b = 0; b < m.MB; ++b) {
+                    const u32 bit = (u32)(((u64)m.hv[(size_t)c * m.MB + b] + t) % (u32)m.MS);
+                    atomicOr(Pd + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
+                }
+            }
+        }
+    }
+    return any;
+}
+
+// ------------------------------------------------------------------------------------- bit-sliced automata
+// +1 / -1 with saturation on the automata flagged in `active`; p[b] is plane b of one 32-automaton word
+// (kernels.py:55-96).  MAXSB is a compile-time bound so that the planes stay in registers.
+template <int MAXSB>
+__device__ __forceinline__ void automata_inc(u32 (&p)[MAXSB], int SB, u32 active)
+{
+    u32 carry = active;
+#pragma unroll
+    for (int b = 0; b < MAXSB; ++b)
+        if (b < SB) { const u32 nx = p[b] & carry; p[b] ^= carry; carry = nx; }
+#pragma unroll
+    for (int b = 0; b < MAXSB; ++b)
+        if (b < SB) p[b] |= carry;
+}
+
+template <int MAXSB>
+__device__ __forceinline__ void automata_dec(u32 (&p)[MAXSB], int SB, u32 active)
+{
+    u32 borrow = active;
+#pragma unroll
+    for (int b = 0; b < MAXSB; ++b)
+        if (b < SB) { const u32 nx = ~p[b] & borrow; p[b] ^= borrow; borrow = nx; }
+#pragma unroll
+    for (int b = 0; b < MAXSB; ++b)
+        if (b < SB) p[b] &= ~borrow;
+}
+
+}  // namespace gtm

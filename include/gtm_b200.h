@@ -1,0 +1,154 @@
+/* gtm_b200.h — C ABI of the B200-native Graph Tsetlin Machine engine (libgtm_b200.so).
+ *
+ * This is the seam at which the reference (cair/GraphTsetlinMachine) talks to PyCUDA
+ * (GraphTsetlinMachine/tm.py: SourceModule/get_function/prepared_call, cuda.mem_alloc, memcpy_htod/dtoh,
+ * Context.synchronize).  Every entry point names the reference interface it replaces.
+ *
+ * Conventions
+ *  - Plain C types only; handles are opaque.  Host pointers are borrowed for the duration of the call.
+ *  - Every function returns a gtm_status (0 = OK).  gtm_last_error() gives the message of the calling
+ *    thread's last failure.  No exception or exit() crosses this boundary.
+ *  - Calls are synchronous on return unless stated otherwise.  A model handle is not thread-safe.
+ *  - Array layouts at the boundary are the reference's (see each function); the engine's internal layouts
+ *    differ and are converted on the device.
+ */
+#ifndef GTM_B200_H
+#define GTM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GTM_MAX_DEPTH 16
+#define GTM_MAX_STATE_BITS 32
+
+typedef enum gtm_status {
+    GTM_OK = 0,
+    GTM_ERR_ARG = 1,         /* bad argument / unsupported size */
+    GTM_ERR_CUDA = 2,        /* a CUDA runtime call failed      */
+    GTM_ERR_OOM = 3,         /* device or host allocation failed */
+    GTM_ERR_TIMEOUT = 4,     /* a bounded device-side wait (grid barrier) gave up */
+    GTM_ERR_STATE = 5        /* call order violated (e.g. score before any state was set) */
+} gtm_status;
+
+/* Hyper-parameters.  Mirrors the constants the reference bakes into its kernels at JIT time
+ * (tm.py:438-464) plus the constructor arguments of CommonTsetlinMachine (tm.py:39-55). */
+typedef struct gtm_config {
+    int32_t number_of_clauses;            /* CLAUSES */
+    int32_t number_of_outputs;            /* CLASSES */
+    int32_t number_of_literals;           /* LITERALS = 2 * hypervector_size */
+    int32_t number_of_state_bits;         /* STATE_BITS (1..32) */
+    int32_t boost_true_positive_feedback; /* BOOST_TRUE_POSITIVE_FEEDBACK */
+    int32_t T;                            /* THRESHOLD */
+    int32_t max_included_literals;        /* MAX_INCLUDED_LITERALS */
+    int32_t message_size;                 /* MESSAGE_SIZE */
+    int32_t message_bits;                 /* MESSAGE_BITS */
+    int32_t depth;                        /* number of layers; 1 = no message passing (tm.py:62) */
+    int32_t device;                       /* CUDA device ordinal */
+    int32_t reserved;
+    double q;                             /* Q, already rounded the way the reference's "%f" format does */
+    float s[GTM_MAX_DEPTH];               /* specificity per layer (tm.py:63-66) */
+    uint64_t seed;                        /* key of the per-clause Philox4x32-10 draw streams */
+} gtm_config;
+
+/* A graph set in the array layout produced by GraphTsetlinMachine/graphs.py (Graphs): */
+typedef struct gtm_graphs_view {
+    const uint32_t *X;                          /* [total_nodes][ceil(literals/32)]  graphs.py:112      */
+    const uint32_t *node_type;                  /* [total_nodes]                     graphs.py:107      */
+    const uint32_t *number_of_graph_node_edges; /* [total_nodes] out-degrees         graphs.py:108      */
+    const uint32_t *edge_index;                 /* [total_nodes] CSR row starts      graphs.py:110,128  */
+    const uint32_t *edge;                       /* [total_edges][2] (dst local id, edge type) graphs.py:129 */
+    const uint32_t *node_index;                 /* [number_of_graphs] first node     graphs.py:101      */
+    const uint32_t *number_of_graph_nodes;      /* [number_of_graphs]                graphs.py:38       */
+    int64_t number_of_graphs;
+    int64_t total_nodes;
+    int64_t total_edges;
+    int32_t max_number_of_graph_nodes;
+    int32_t reserved;
+} gtm_graphs_view;
+
+typedef struct gtm_model gtm_model;
+typedef struct gtm_dataset gtm_dataset;
+
+/* Library --------------------------------------------------------------------------------------------- */
+const char *gtm_version(void);
+const char *gtm_last_error(void);
+int gtm_device_count(int *count_out);
+
+/* Model life cycle.  Replaces tm.py:437-513 (_init_gpu_kernels: no JIT here, sizes are run-time values) and
+ * tm.py:110-124 (allocate_gpu_memory). */
+int gtm_create(const gtm_config *config, gtm_model **model_out);
+int gtm_destroy(gtm_model *model);
+
+/* All device work of a model is issued on this CUDA stream (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream, which is also the default). */
+int gtm_set_stream(gtm_model *model, void *cuda_stream);
+
+/* Replaces the `prepare` launch of tm.py:518,525 (kernels.py:638-664) and, when reset_message_layers != 0,
+ * the `prepare_message_ta_state` launches of tm.py:520-521 (kernels.py:622-636): weights +-1 from one draw
+ * per (clause, class), every automaton one step below the include boundary. */
+int gtm_init_state(gtm_model *model, int reset_message_layers);
+
+/* Tsetlin-automaton state of one layer in the reference's layout uint32[CLAUSES][chunks][STATE_BITS]
+ * (layer 0: tm.py:111,283-284; layer d >= 1 = message_ta_state[d-1]: tm.py:113-115,319-323,406-408). */
+int gtm_set_ta_state(gtm_model *model, int layer, const uint32_t *ta_state);
+int gtm_get_ta_state(gtm_model *model, int layer, uint32_t *ta_state_out);
+
+/* Clause weights int32[CLASSES][CLAUSES] (tm.py:117,285-286,409). */
+int gtm_set_weights(gtm_model *model, const int32_t *clause_weights);
+int gtm_get_weights(gtm_model *model, int32_t *clause_weights_out);
+
+/* Message hypervectors uint32[CLAUSES][MESSAGE_BITS] (tm.py:123-124). */
+int gtm_set_hypervectors(gtm_model *model, const uint32_t *hypervectors);
+
+/* Random draws.  The engine has one counter-based stream per clause in place of the reference's one XORWOW
+ * state per launched thread (tm.py:36; kernels.py:199,228,329,369,643).  Positions are the number of draws
+ * each clause has consumed.  Recorded draws (uint32[CLAUSES][draws_per_clause], read modulo
+ * draws_per_clause) replace the Philox output; pass NULL to go back to Philox.  The buffer is copied. */
+int gtm_set_draw_positions(gtm_model *model, const uint64_t *positions);
+int gtm_get_draw_positions(gtm_model *model, uint64_t *positions_out);
+int gtm_set_recorded_draws(gtm_model *model, const uint32_t *draws, uint64_t draws_per_clause);
+
+/* Graph sets on the device.  Replaces the uploads and scratch allocations of tm.py:528-555 (_init_fit) and
+ * tm.py:759-784 (_score_init).  Signature caching stays with the caller. */
+int gtm_dataset_create(gtm_model *model, const gtm_graphs_view *graphs, gtm_dataset **dataset_out);
+int gtm_dataset_destroy(gtm_dataset *dataset);
+
+/* Replaces the per-graph loop of tm.py:786-812 (_score): raw, unclamped class sums int32[count][CLASSES] for
+ * graphs [first, first+count).  number_of_node_types is graphs.number_of_node_types() at call time
+ * (tm.py:587).  gtm_score copies the result to host memory; gtm_score_device leaves it in device memory at
+ * class_sums_device and returns without synchronising (work is queued on the model's stream). */
+int gtm_score(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
+              int32_t *class_sums_out);
+int gtm_score_device(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first,
+                     int64_t count, int32_t *class_sums_device);
+
+/* Replaces the learning loop of tm.py:668-747 (_fit): `epochs` passes over graphs [first, first+count) in
+ * order; encoded_Y is int32[number_of_graphs][CLASSES] with +-T targets (tm.py:949-951), indexed by the
+ * absolute graph id. */
+int gtm_fit(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, const int32_t *encoded_Y,
+            int64_t first, int64_t count, int epochs);
+
+/* Replaces tm.py:814-851 (transform; kernels.py:671-691): clause outputs int32[count][CLAUSES] (0/1) and the
+ * class sums int32[count][CLASSES] of graphs [first, first+count).  Either output may be NULL. */
+int gtm_transform(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
+                  int32_t *clause_outputs_out, int32_t *class_sums_out);
+
+/* Differential-test taps (no counterpart call in the reference; they expose the buffers its kernels leave in
+ * device memory between launches of tm.py:563-747).
+ *  gtm_debug_evaluate: inference on one graph through the scoring kernel (path 0) or through the learning
+ *   kernel's inference phase (path 1).  cno_out: uint32[depth][CLAUSES][ceil(n/32)] node-output bits after
+ *   each layer; messages_out: uint32[depth-1][n][ceil(2*MESSAGE_SIZE/32)] packed messages (clause_X);
+ *   n_inc_out: int32[CLAUSES]; class_sum_out: int32[CLASSES].  Any output may be NULL.
+ *  gtm_debug_last_feedback: after gtm_fit, the selected node per clause int32[CLAUSES] (clause_node) and the
+ *   feedback type int32[CLASSES][CLAUSES] (class_clause_update) of the last graph processed. */
+int gtm_debug_evaluate(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t graph, int path,
+                       uint32_t *cno_out, uint32_t *messages_out, int32_t *n_inc_out, int32_t *class_sum_out);
+int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t *class_clause_update_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GTM_B200_H */
