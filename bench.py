@@ -1,0 +1,332 @@
+"""Benchmark of the Graph Tsetlin Machine hot path on B200: predict (headline) and fit throughput.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the reference's own kernels on the host cores
+
+Workload: the MNIST-shaped single-node configuration (2,500 clauses, T=3,125, s=10, 10 classes, hypervector
+128/2, depth 1) on seeded synthetic images.  A step scores one batch of graphs that is resident in device
+memory (`value`); `e2e` is the same batch scored through the public Python API from page-locked host arrays,
+host->device upload and device->host read of the class sums included.  One process per GPU; every rank scores
+its own shard of graphs (no collective on the data path), timing is the maximum over ranks.  Prints ONE JSON line.
+"""
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CLAUSES, CLASSES, T, S, HV_SIZE, HV_BITS = 2500, 10, 3125, 10.0, 128, 2
+TRAIN_GRAPHS = 60000
+UNIQUE_GRAPHS = 1 << 18          # distinct synthetic images per rank; tiled to the batch size
+BATCH_GRAPHS = 1 << 22           # graphs scored per step per GPU: X alone is 134 MB (> 126 MB of L2)
+BYTES_PER_GRAPH = 4 * 1 * 8 + 8 * 1 + 8 * 0 + 4 * CLASSES     # 4nL0 + 8n + 8E + 4K = 80
+LOP3_PER_GRAPH = CLAUSES * 1 * 8                               # C*n*L0 word tests, dense equivalent
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.2 and len(r) >= 7] or [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def build_workload(rank):
+    from graphtsetlinmachine_b200 import datasets
+
+    protos = datasets.image_prototypes(1)
+    np.random.seed(1)                                   # symbol hypervectors identical on every rank
+    train, y_train = datasets.vanilla_images(TRAIN_GRAPHS, 2, protos, HV_SIZE, HV_BITS)
+    unique, _ = datasets.vanilla_images(UNIQUE_GRAPHS, 1000 + rank, protos, init_with=train)
+    batch = datasets.replicate(unique, BATCH_GRAPHS // UNIQUE_GRAPHS)
+    return train, y_train, batch
+
+
+def cpu_reference_scorer(ta_state, weights, graphs, threads):
+    """The reference's own scoring kernels compiled for the host (oracle/_ref), one instance per thread, or the
+    C restatement when that build did not travel.  Returns (kind, callable(first, count) -> seconds)."""
+    from oracle import build_ref
+    from oracle.oracle import OracleTM
+
+    kw = dict(clauses=CLAUSES, classes=CLASSES, literals=2 * HV_SIZE, threshold=T, s=S, depth=1, max_nodes=1)
+    params = dict(classes=CLASSES, clauses=CLAUSES, literals=2 * HV_SIZE, threshold=T, max_nodes=1)
+    kind = "reference" if build_ref.build(params) is not None else "port"
+    if kind == "reference":
+        from oracle.ref_tm import RefTM as Impl
+    else:
+        Impl = OracleTM
+    workers = []
+    for _ in range(threads):
+        tm = Impl(**kw)
+        tm.ta_state[:] = ta_state.reshape(tm.ta_state.shape)
+        tm.clause_weights[:] = weights.reshape(tm.clause_weights.shape)
+        tm.set_graphs(graphs)
+        workers.append(tm)
+
+    def run(first, count):
+        per = count // threads
+        out = [None] * threads
+
+        def work(i):
+            out[i] = workers[i].score(first + i * per, per)
+
+        ts = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
+        t0 = time.perf_counter()
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return time.perf_counter() - t0, per * threads, out
+
+    return kind, run
+
+
+def trained_state_on_cpu(train, y_train):
+    """A trained state for the reference arm when no GPU run precedes it: a short fit with the C restatement."""
+    from oracle.oracle import OracleTM
+
+    tm = OracleTM(clauses=CLAUSES, classes=CLASSES, literals=2 * HV_SIZE, threshold=T, s=S, depth=1, max_nodes=1, seed=7)
+    tm.set_graphs(train)
+    tm.prepare()
+    enc = np.where(y_train[:, None] == np.arange(CLASSES)[None, :], T, -T).astype(np.int32)
+    tm.fit(enc, 0, 2000)
+    return tm.ta_state.copy(), tm.clause_weights.copy()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    from graphtsetlinmachine_b200 import datasets
+
+    protos = datasets.image_prototypes(1)
+    np.random.seed(1)
+    train, y_train = datasets.vanilla_images(TRAIN_GRAPHS, 2, protos, HV_SIZE, HV_BITS)
+    sample, _ = datasets.vanilla_images(1 << 16, 1000, protos, init_with=train)
+    ta, w = trained_state_on_cpu(train, y_train)
+    kind, run = cpu_reference_scorer(ta, w, sample, threads)
+    sec, n, _ = run(0, threads * 64)
+    per_step = max(threads * 64, min(sample.number_of_graphs, int(n / sec * 2.0) // threads * threads))
+    for _ in range(args.warmup):
+        run(0, per_step)
+    total_s, total_n = 0.0, 0
+    for _ in range(args.steps):
+        sec, n, _ = run(0, per_step)
+        total_s += sec
+        total_n += n
+    value = total_n / total_s
+    line = {
+        "impl": "reference", "metric": "predict graphs/sec (fit in `fit`)", "value": value, "unit": "graphs/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_s / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+        "config": {"workload": "vanilla MNIST-shaped single-node graphs: 2500 clauses, T=3125, s=10, 10 classes, hv 128/2, depth 1",
+                   "graphs_per_step": per_step},
+        "cpu_baseline": {"value": value, "unit": "graphs/s", "cores": threads, "kind": kind,
+                         "sample": "%d graphs per step scored by the reference kernels compiled for the host, %d threads" % (per_step, threads)},
+        "e2e": {"value": value, "unit": "graphs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    global BATCH_GRAPHS
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--batch-graphs", type=int, default=BATCH_GRAPHS)
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    args.warmup = max(args.warmup, 3) if args.impl == "engine" else args.warmup
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    BATCH_GRAPHS = max(UNIQUE_GRAPHS, args.batch_graphs // UNIQUE_GRAPHS * UNIQUE_GRAPHS)
+
+    import torch
+    import torch.distributed as dist
+
+    from graphtsetlinmachine_b200 import _lib
+    from graphtsetlinmachine_b200.tm import MultiClassGraphTsetlinMachine
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    train, y_train, batch = build_workload(rank)
+    lib = _lib.load()
+    np.random.seed(1)
+    tm = MultiClassGraphTsetlinMachine(CLAUSES, T, S, depth=1, seed=7, device=local_rank)
+
+    # ---- fit: two ordered passes over the training set (the second one is reported) ----
+    tm.fit(train, y_train, epochs=1, incremental=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tm.fit(train, y_train, epochs=1, incremental=True)
+    torch.cuda.synchronize()
+    fit_s = time.perf_counter() - t0
+    train_acc = float((tm.predict(train) == y_train).mean())
+
+    # ---- predict, batch resident in device memory ----
+    stream = torch.cuda.current_stream()
+    _lib.check(lib.gtm_set_stream(tm._model, C.c_void_p(stream.cuda_stream)))
+    tm._score_init(batch)                                    # upload once, outside the timed region
+    n = int(batch.number_of_graphs)
+    sums_dev = torch.empty((n, CLASSES), dtype=torch.int32, device="cuda")
+    nt = int(batch.number_of_node_types())
+
+    def step():
+        _lib.check(lib.gtm_score_device(tm._model, tm._test_set.handle, nt, 0, n, C.c_void_p(sums_dev.data_ptr())))
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.time()
+    start.record(stream)
+    for _ in range(args.steps):
+        step()
+    stop.record(stream)
+    barrier()
+    w1 = time.time()
+    clocks = sampler.stop(w0, w1)
+    ms = torch.tensor([start.elapsed_time(stop) / args.steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item())
+    value = world * n / (ms_per_step * 1e-3)
+    sums_host = sums_dev.cpu().numpy()
+
+    # ---- end to end through the public API: pinned host arrays in, class sums out, every step ----
+    cudart = torch.cuda.cudart()
+    pinned = [batch.X, batch.node_type, batch.number_of_graph_node_edges, batch.edge_index, batch.node_index,
+              batch.number_of_graph_nodes]
+    out_host = np.zeros((n, CLASSES), dtype=np.int32)
+    for a in pinned + [out_host]:
+        cudart.cudaHostRegister(a.ctypes.data, a.nbytes, 0)
+    h2d = int(sum(a.nbytes for a in pinned))
+    d2h = int(out_host.nbytes)
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        tm.graphs_signature_test = np.array([])              # forget the cached upload: copy the inputs again
+        tm.score(batch, out=out_host)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / e2e_steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * n / (float(e2e_ms.item()) * 1e-3)
+    assert np.array_equal(out_host, sums_host), "API result differs from the device-resident run"
+    for a in pinned + [out_host]:
+        cudart.cudaHostUnregister(a.ctypes.data)
+
+    # ---- checks against the CPU checker + CPU baseline (rank 0, N=1 only for the timing) ----
+    cpu = None
+    if rank == 0:
+        threads = os.cpu_count() or 1
+        ta, w = tm.get_state()[0], tm.get_state()[1]
+        kind, run = cpu_reference_scorer(ta, w, batch, threads)
+        sec, cnt, outs = run(0, threads * 64)
+        got = np.concatenate(outs)
+        assert np.array_equal(got, sums_host[:cnt]), "class sums differ from the CPU reference kernels"
+        if world == 1 and not args.skip_cpu_baseline:
+            per = max(threads * 64, int(cnt / sec * 3.0) // threads * threads)
+            per = min(per, n // threads * threads)
+            sec, cnt, _ = run(0, per)
+            cpu = {"value": cnt / sec, "unit": "graphs/s", "cores": threads, "kind": kind,
+                   "sample": "%d graphs of the same batch, %d host threads, reference scoring kernels compiled for the host" % (cnt, threads)}
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        achieved = BYTES_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": "predict graphs/sec (fit in `fit`)", "value": value, "unit": "graphs/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
+            "config": {"workload": "vanilla MNIST-shaped single-node graphs: 2500 clauses, T=3125, s=10, 10 classes, hv 128/2, depth 1",
+                       "graphs_per_step_per_gpu": n, "l2": "inputs larger than L2 (X = %d MB per step)" % (batch.X.nbytes >> 20),
+                       "partitioning": "graphs sharded over ranks, no collective"},
+            "e2e": {"value": e2e_value, "unit": "graphs/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_kind, "bytes_per_graph": BYTES_PER_GRAPH,
+                         "kernel": "score kernel, one launch per step",
+                         "int_ops": {"dense_lop3_per_graph": LOP3_PER_GRAPH,
+                                     "achieved_tlop3_s": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12}},
+            "cpu_baseline": cpu,
+            "fit": {"value": TRAIN_GRAPHS / fit_s, "unit": "graphs/s", "graphs": TRAIN_GRAPHS, "epoch_s": fit_s,
+                    "n_gpus": 1, "train_accuracy_after_2_epochs": train_acc,
+                    "note": "one persistent launch per epoch; wall clock around the API call incl. label upload"},
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -255,10 +255,13 @@ class CommonTsetlinMachine:
                 self._test_set.close()
             self._test_set = _Dataset(self._lib, self._model, graphs)
 
-    def _score(self, graphs):
-        """tm.py:786-812: raw class sums int32[N][outputs]; one batched launch instead of a per-graph loop."""
+    def _score(self, graphs, out=None):
+        """tm.py:786-812: raw class sums int32[N][outputs]; one batched launch instead of a per-graph loop.
+        `out` (optional, C-contiguous int32[N][outputs], e.g. page-locked) receives the result in place."""
         self._score_init(graphs)
-        class_sum = np.zeros((graphs.number_of_graphs, self.number_of_outputs), dtype=np.int32)
+        class_sum = np.zeros((graphs.number_of_graphs, self.number_of_outputs), dtype=np.int32) if out is None else out
+        assert class_sum.dtype == np.int32 and class_sum.flags.c_contiguous
+        assert class_sum.shape == (graphs.number_of_graphs, self.number_of_outputs)
         _lib.check(self._lib.gtm_score(self._model, self._test_set.handle, int(graphs.number_of_node_types()), 0,
                                        int(graphs.number_of_graphs), _ptr(class_sum)))
         return class_sum
@@ -478,8 +481,8 @@ class MultiClassGraphTsetlinMachine(CommonTsetlinMachine):
             encoded_Y[:, i] = np.where(Y == i, self.T, -self.T)
         self._fit(graphs, encoded_Y, epochs=epochs, incremental=incremental)
 
-    def score(self, graphs):
-        return self._score(graphs)
+    def score(self, graphs, out=None):
+        return self._score(graphs, out)
 
     def predict(self, graphs):
         return np.argmax(self.score(graphs), axis=1)

@@ -126,9 +126,9 @@ class RefTM:
         assert int(graphs.max_number_of_graph_nodes) <= self.max_nodes
         self._graphs = g = dict(
             X=np.ascontiguousarray(graphs.X, dtype=np.uint32),
-            node_type=np.ascontiguousarray(graphs.node_type).astype(np.int32),
-            n_edges=np.ascontiguousarray(graphs.number_of_graph_node_edges).astype(np.int32),
-            edge=np.ascontiguousarray(graphs.edge).astype(np.int32).reshape(-1, 2)
+            node_type=np.ascontiguousarray(graphs.node_type, dtype=np.uint32).view(np.int32),
+            n_edges=np.ascontiguousarray(graphs.number_of_graph_node_edges, dtype=np.uint32).view(np.int32),
+            edge=np.ascontiguousarray(graphs.edge, dtype=np.uint32).view(np.int32).reshape(-1, 2)
             if graphs.edge.size else np.zeros((1, 2), dtype=np.int32),
             node_index=np.ascontiguousarray(graphs.node_index, dtype=np.uint32),
             n_nodes=np.ascontiguousarray(graphs.number_of_graph_nodes, dtype=np.uint32),
