@@ -430,7 +430,7 @@ extern "C" int gtm_score_device(gtm_model *m, gtm_dataset *ds, int n_types, int6
     GTM_TRY(check_range(m, ds, n_types, first, count));
     if (count == 0) return GTM_OK;
     if (!sums_dev) return fail(GTM_ERR_ARG, "class_sums_device is null");
-    if (stream_supported(ds->sd)) {
+    if (stream_supported(ds->sd, n_types)) {
         GTM_TRY(refresh_lists(m));
         return stream_score(m->sm, ds->sd, m->dm, ds->dg, n_types, first, count, sums_dev, m->stream);
     }

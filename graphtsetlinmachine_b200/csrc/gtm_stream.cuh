@@ -1,21 +1,362 @@
-// Node-stream scoring path (fast path for batched inference).  Interface used by gtm_api.cu.
+// Node-stream scoring: the fast path of batched inference for depth-1 models.
+//
+// Idea.  Layer-0 clause evaluation is a per-node test, so a graph set is one long stream of nodes.  A CTA
+// takes a TILE of consecutive graphs (at most TN = 32*TNC nodes), turns the tile's literal rows into the
+// transposed form XT[literal][node word] (bit i of word j = literal of node 32j+i) in shared memory, and then
+// evaluates a clause on 32 nodes per AND: r = AND over the clause's INCLUDED literals of XT[literal][j].
+// That is popcount(include) word operations per 32 nodes instead of 32*ceil(literals/32) for the row-wise
+// test, and an empty clause costs nothing (and is true, as in kernels.py:443-460).  Included literals come
+// from per-clause lists rebuilt from the include planes whenever the automata changed.
+//
+// Votes.  Clauses are processed in blocks of CB; their node bits go to shared memory R[CB][TNC]; then one
+// thread per graph ORs the bits of its node segment and accumulates the block's weights into registers
+// (kernels.py:279-317, batched).  Class sums leave the CTA once per graph, unclamped.
+//
+// Derived model data (StreamModel): literal lists (uint16 ids, padded to a multiple of 4 with the id of an
+// all-ones row) and weights transposed to [clause][KROW].
 #pragma once
+#include <vector>
+
 #include "gtm_device.cuh"
 #include "gtm_host.cuh"
 
 namespace gtm {
 
-struct StreamModel { int unused; };
-struct StreamData { int supported; };
+constexpr int kStreamThreads = 512;
+constexpr int kStreamCB = 256;          // clauses per vote block
+constexpr int kStreamMaxK = 16;
 
-inline int stream_model_create(StreamModel *, const DevModel &) { return GTM_OK; }
-inline void stream_model_destroy(StreamModel *) {}
-inline int stream_model_refresh(StreamModel *, const DevModel &, cudaStream_t) { return GTM_OK; }
-inline int stream_data_create(StreamData *sd, const StreamModel &, const DevModel &, const DevGraphs &,
-                              const gtm_graphs_view *, int, cudaStream_t) { sd->supported = 0; return GTM_OK; }
-inline void stream_data_destroy(StreamData *) {}
-inline bool stream_supported(const StreamData &sd) { return sd.supported != 0; }
-inline int stream_score(const StreamModel &, const StreamData &, const DevModel &, const DevGraphs &, int, int64_t,
-                        int64_t, int *, cudaStream_t) { return fail(GTM_ERR_STATE, "node-stream path not built"); }
+struct StreamModel {
+    int *lit_off = nullptr;             // [C+1] offsets into lit_list (multiples of 4)
+    int *lit_cnt = nullptr;             // [C]   padded counts (scratch of the scan)
+    unsigned short *lit_list = nullptr; // padded literal ids
+    int *Wt = nullptr;                  // [C][KROW]
+    int KROW = 0;
+};
+
+struct StreamData {
+    int supported = 0;
+    int TNC = 0;                        // node words per tile
+    int n_tiles = 0;
+    int *tile_graph = nullptr;          // [n_tiles+1] first graph of every tile
+    std::vector<int> tile_graph_host;
+    int grid = 0;
+    size_t smem = 0;
+    unsigned *tile_counter = nullptr;
+    int64_t total_nodes = 0, n_graphs = 0;
+};
+
+// ------------------------------------------------------------------------------------------- list building
+__global__ void stream_count_kernel(DevModel m, int *cnt)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= m.C) return;
+    const u32 *inc = m.ta[0] + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
+    int n = 0;
+    for (int w = 0; w < m.L0; ++w) n += __popc(inc[w] & (w == m.L0 - 1 ? m.lit_mask : kFull));
+    cnt[c] = (n + 3) & ~3;
+}
+
+__global__ void stream_scan_kernel(const int *cnt, int *off, int C)
+{
+    __shared__ int s_part[1024];
+    const int per = (C + blockDim.x - 1) / blockDim.x;
+    const int lo = min(C, (int)threadIdx.x * per), hi = min(C, lo + per);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) sum += cnt[i];
+    s_part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int t = 0; t < (int)blockDim.x; ++t) { const int v = s_part[t]; s_part[t] = run; run += v; }
+        off[C] = run;
+    }
+    __syncthreads();
+    int run = s_part[threadIdx.x];
+    for (int i = lo; i < hi; ++i) { off[i] = run; run += cnt[i]; }
+}
+
+__global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *list, int *Wt, int KROW)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= m.C) return;
+    const u32 *inc = m.ta[0] + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
+    int at = off[c];
+    for (int w = 0; w < m.L0; ++w) {
+        u32 bits = inc[w] & (w == m.L0 - 1 ? m.lit_mask : kFull);
+        while (bits) {
+            const int b = __ffs(bits) - 1;
+            bits &= bits - 1;
+            list[at++] = (unsigned short)(w * 32 + b);
+        }
+    }
+    while (at < off[c + 1]) list[at++] = (unsigned short)m.literals;   // sentinel: the all-ones row
+    for (int k = 0; k < KROW; ++k) Wt[(size_t)c * KROW + k] = k < m.K ? m.weights[(size_t)k * m.C + c] : 0;
+}
+
+// -------------------------------------------------------------------------------------------------- scoring
+struct StreamArgs {
+    const int *tile_graph;
+    int tile_lo, tile_hi;               // tiles [tile_lo, tile_hi)
+    int64_t first, count;               // graphs written: [first, first+count)
+    int64_t n_graphs, total_nodes;
+    int *class_sums;                    // [count][K]
+    unsigned *tile_counter;             // dynamic tile scheduler (zeroed before launch)
+    int TNC;
+    const int *lit_off;
+    const unsigned short *lit_list;
+    const int *Wt;
+    int KROW;
+};
+
+template <int KP>
+__global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevModel m, DevGraphs g, StreamArgs a)
+{
+    extern __shared__ u32 s_dyn[];
+    const int TNC = a.TNC, TN = TNC * 32;
+    u32 *XT = s_dyn;                                   // [literals+1][TNC]
+    u32 *TMV = XT + (size_t)(m.literals + 1) * TNC;    // [n_types][TNC] valid & node type
+    u32 *R = TMV + (size_t)g.n_types * TNC;            // [CB][TNC]
+    int *Wb = (int *)(R + (size_t)kStreamCB * TNC);    // [CB][KROW]
+    __shared__ int s_tile;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kStreamThreads / 32;
+    const int KROW = a.KROW;
+
+    while (true) {
+        if (tid == 0) s_tile = a.tile_lo + (int)atomicAdd(a.tile_counter, 1u);
+        __syncthreads();
+        const int tile = s_tile;
+        if (tile >= a.tile_hi) break;
+        const int g0 = a.tile_graph[tile], g1 = a.tile_graph[tile + 1];
+        const int node0 = (int)g.node_index[g0];
+        const int node1 = g1 < a.n_graphs ? (int)g.node_index[g1] : (int)a.total_nodes;
+        const int nn = node1 - node0;
+
+        // ---- transpose the tile's literal rows: XT[32w+b][j] = ballot over the 32 nodes of word j ----
+        for (int jw = warp; jw < TNC * m.L0; jw += nwarps) {
+            const int j = jw / m.L0, w = jw % m.L0;
+            const int v = j * 32 + lane;
+            u32 x = v < nn ? g.X[(size_t)(node0 + v) * m.L0 + w] : 0u;
+            const int nbits = min(32, m.literals - 32 * w);
+            for (int b = 0; b < nbits; ++b) {
+                const u32 col = __ballot_sync(kFull, (x >> b) & 1u);
+                if (lane == (b & 31)) XT[(size_t)(32 * w + b) * TNC + j] = col;
+            }
+        }
+        for (int j = tid; j < TNC; j += kStreamThreads) XT[(size_t)m.literals * TNC + j] = kFull;
+        for (int tj = warp; tj < g.n_types * TNC; tj += nwarps) {
+            const int t = tj / TNC, j = tj % TNC;
+            const int v = j * 32 + lane;
+            const bool ok = v < nn && g.node_type[node0 + (v < nn ? v : 0)] == (u32)t;
+            const u32 col = __ballot_sync(kFull, ok);
+            if (lane == 0) TMV[tj] = col;
+        }
+
+        // ---- per-graph accumulators (graphs tid, tid+512, ... of the tile) ----
+        int acc[2][KP];
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int k = 0; k < KP; ++k) acc[s][k] = 0;
+        int seg_lo[2], seg_hi[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int gi = g0 + tid + s * kStreamThreads;
+            if (gi < g1) {
+                seg_lo[s] = (int)g.node_index[gi] - node0;
+                seg_hi[s] = seg_lo[s] + (int)g.n_nodes[gi];
+            } else {
+                seg_lo[s] = 0; seg_hi[s] = 0;
+            }
+        }
+        __syncthreads();
+
+        for (int cb0 = 0; cb0 < m.C; cb0 += kStreamCB) {
+            const int cbn = min(kStreamCB, m.C - cb0);
+            // ---- evaluation: (clause, node word) pairs over lanes; AND the transposed rows of the included literals ----
+            for (int idx = tid; idx < cbn * TNC; idx += kStreamThreads) {
+                const int cb = idx / TNC, j = idx - cb * TNC;
+                const int c = cb0 + cb;
+                u32 r = TMV[(c % g.n_types) * TNC + j];
+                const int o0 = a.lit_off[c], o1 = a.lit_off[c + 1];
+                const uint2 *lp = reinterpret_cast<const uint2 *>(a.lit_list + o0);
+                for (int q = 0; q < (o1 - o0) >> 2; ++q) {
+                    const uint2 four = lp[q];
+                    r &= XT[(size_t)(four.x & 0xffffu) * TNC + j];
+                    r &= XT[(size_t)(four.x >> 16) * TNC + j];
+                    r &= XT[(size_t)(four.y & 0xffffu) * TNC + j];
+                    r &= XT[(size_t)(four.y >> 16) * TNC + j];
+                }
+                R[idx] = r;
+            }
+            for (int i = tid; i < cbn * KROW; i += kStreamThreads) Wb[i] = a.Wt[(size_t)cb0 * KROW + i];
+            __syncthreads();
+            // ---- votes: one thread per graph, OR over its node segment, weights from shared memory ----
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                if (seg_hi[s] > seg_lo[s]) {
+                    const int wlo = seg_lo[s] >> 5, whi = (seg_hi[s] - 1) >> 5;
+                    const u32 mlo = kFull << (seg_lo[s] & 31);
+                    const u32 mhi = kFull >> (31 - ((seg_hi[s] - 1) & 31));
+                    for (int cb = 0; cb < cbn; ++cb) {
+                        const u32 *row = R + (size_t)cb * TNC;
+                        u32 any;
+                        if (wlo == whi) {
+                            any = row[wlo] & mlo & mhi;
+                        } else {
+                            any = (row[wlo] & mlo) | (row[whi] & mhi);
+                            for (int w = wlo + 1; w < whi; ++w) any |= row[w];
+                        }
+                        if (any) {
+                            const int *wr = Wb + (size_t)cb * KROW;
+#pragma unroll
+                            for (int k = 0; k < KP; ++k) acc[s][k] += wr[k];
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+        }
+
+        // ---- class sums of the tile's graphs (only those inside the requested range) ----
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int64_t gi = (int64_t)g0 + tid + s * kStreamThreads;
+            if (gi < g1 && gi >= a.first && gi < a.first + a.count) {
+                int *out = a.class_sums + (size_t)(gi - a.first) * m.K;
+#pragma unroll
+                for (int k = 0; k < KP; ++k)
+                    if (k < m.K) out[k] = acc[s][k];
+            }
+        }
+        __syncthreads();   // s_tile and the shared buffers are reused by the next tile
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+inline int stream_krow(int K) { return (K + 3) & ~3; }
+
+inline int stream_model_create(StreamModel *sm, const DevModel &d)
+{
+    if (d.D != 1 || d.K > kStreamMaxK || d.literals >= 65535) return GTM_OK;   // path not applicable
+    sm->KROW = stream_krow(d.K);
+    GTM_TRY(dev_alloc(&sm->lit_off, (size_t)d.C + 1));
+    GTM_TRY(dev_alloc(&sm->lit_cnt, (size_t)d.C));
+    GTM_TRY(dev_alloc(&sm->lit_list, (size_t)d.C * ((d.literals + 3) & ~3) + 4));
+    GTM_TRY(dev_alloc(&sm->Wt, (size_t)d.C * sm->KROW));
+    return GTM_OK;
+}
+
+inline void stream_model_destroy(StreamModel *sm)
+{
+    cudaFree(sm->lit_off); cudaFree(sm->lit_cnt); cudaFree(sm->lit_list); cudaFree(sm->Wt);
+    *sm = StreamModel();
+}
+
+inline int stream_model_refresh(StreamModel *sm, const DevModel &d, cudaStream_t s)
+{
+    if (!sm->lit_off) return GTM_OK;
+    const int blocks = (d.C + 255) / 256;
+    stream_count_kernel<<<blocks, 256, 0, s>>>(d, sm->lit_cnt);
+    stream_scan_kernel<<<1, 1024, 0, s>>>(sm->lit_cnt, sm->lit_off, d.C);
+    stream_fill_kernel<<<blocks, 256, 0, s>>>(d, sm->lit_off, sm->lit_list, sm->Wt, sm->KROW);
+    GTM_CU(cudaGetLastError());
+    return GTM_OK;
+}
+
+template <int KP>
+inline const void *stream_kernel_ptr() { return (const void *)stream_score_kernel<KP>; }
+
+inline const void *stream_kernel_for(int K)
+{
+    if (K <= 2) return stream_kernel_ptr<2>();
+    if (K <= 4) return stream_kernel_ptr<4>();
+    if (K <= 8) return stream_kernel_ptr<8>();
+    if (K <= 10) return stream_kernel_ptr<10>();
+    if (K <= 12) return stream_kernel_ptr<12>();
+    return stream_kernel_ptr<16>();
+}
+
+inline size_t stream_smem_bytes(const DevModel &d, int TNC, int n_types, int KROW)
+{
+    return ((size_t)(d.literals + 1) * TNC + (size_t)n_types * TNC + (size_t)kStreamCB * TNC) * sizeof(u32) +
+           (size_t)kStreamCB * KROW * sizeof(int);
+}
+
+constexpr int kStreamMaxTypes = 8;
+
+inline int stream_data_create(StreamData *sd, const StreamModel &sm, const DevModel &d, const DevGraphs &,
+                              const gtm_graphs_view *v, int sm_count, cudaStream_t s)
+{
+    sd->supported = 0;
+    if (!sm.lit_off) return GTM_OK;
+    // node words per tile: as many as keep the transposed literals within ~64 KB, at most 32 (2 graphs per thread)
+    int TNC = 32;
+    while (TNC > 1 && (size_t)(d.literals + 1) * TNC * sizeof(u32) > 64 * 1024) TNC >>= 1;
+    if (v->max_number_of_graph_nodes > TNC * 32) return GTM_OK;        // a graph must fit one tile
+    const size_t smem = stream_smem_bytes(d, TNC, kStreamMaxTypes, sm.KROW);
+    if (smem > 200 * 1024) return GTM_OK;
+    const void *fn = stream_kernel_for(d.K);
+    GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int per_sm = 0;
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessorWithFlags(&per_sm, fn, kStreamThreads, smem, 0));
+    if (per_sm < 1) return GTM_OK;
+
+    // greedy tiling: consecutive graphs while the node count stays within the tile
+    const int TN = TNC * 32;
+    std::vector<int> &tg = sd->tile_graph_host;
+    tg.clear();
+    tg.push_back(0);
+    int64_t used = 0;
+    for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
+        const int64_t n = v->number_of_graph_nodes[gi];
+        if (used + n > TN || (gi - tg.back()) >= 2 * kStreamThreads) { tg.push_back((int)gi); used = 0; }
+        used += n;
+    }
+    tg.push_back((int)v->number_of_graphs);
+    sd->n_tiles = (int)tg.size() - 1;
+    GTM_TRY(dev_alloc(&sd->tile_graph, tg.size()));
+    GTM_CU(cudaMemcpyAsync(sd->tile_graph, tg.data(), tg.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+    GTM_TRY(dev_alloc(&sd->tile_counter, 1));
+    sd->TNC = TNC;
+    sd->grid = sm_count * per_sm;
+    sd->smem = smem;
+    sd->total_nodes = v->total_nodes;
+    sd->n_graphs = v->number_of_graphs;
+    sd->supported = 1;
+    return GTM_OK;
+}
+
+inline void stream_data_destroy(StreamData *sd)
+{
+    cudaFree(sd->tile_graph); cudaFree(sd->tile_counter);
+    sd->tile_graph = nullptr; sd->tile_counter = nullptr; sd->supported = 0;
+}
+
+inline bool stream_supported(const StreamData &sd, int n_types) { return sd.supported != 0 && n_types <= kStreamMaxTypes; }
+
+inline int stream_score(const StreamModel &sm, const StreamData &sd, const DevModel &d, const DevGraphs &dg, int n_types,
+                        int64_t first, int64_t count, int *sums_dev, cudaStream_t s)
+{
+    DevGraphs g = dg;
+    g.n_types = n_types;
+    StreamArgs a;
+    a.tile_graph = sd.tile_graph;
+    // tiles that overlap [first, first+count)
+    const std::vector<int> &tg = sd.tile_graph_host;
+    int lo = (int)(std::upper_bound(tg.begin(), tg.end(), (int)first) - tg.begin()) - 1;
+    int hi = (int)(std::lower_bound(tg.begin(), tg.end(), (int)(first + count)) - tg.begin());
+    a.tile_lo = lo; a.tile_hi = hi;
+    a.first = first; a.count = count; a.n_graphs = sd.n_graphs; a.total_nodes = sd.total_nodes;
+    a.class_sums = sums_dev; a.tile_counter = sd.tile_counter; a.TNC = sd.TNC;
+    a.lit_off = sm.lit_off; a.lit_list = sm.lit_list; a.Wt = sm.Wt; a.KROW = sm.KROW;
+    GTM_CU(cudaMemsetAsync(sd.tile_counter, 0, sizeof(unsigned), s));
+    const int grid = std::max(1, std::min(sd.grid, hi - lo));
+    DevModel dm = d;
+    void *args[] = {&dm, &g, &a};
+    GTM_CU(cudaLaunchKernel(stream_kernel_for(d.K), dim3(grid), dim3(kStreamThreads), args,
+                            stream_smem_bytes(d, sd.TNC, n_types, sm.KROW), s));
+    return GTM_OK;
+}
 
 }  // namespace gtm

@@ -179,3 +179,39 @@ def test_errors_through_the_abi(engine_lib):
     assert e.value.status == 1
     assert tm.score(3, 0).shape == (0, kw["classes"])     # empty range is fine
     tm.close()
+
+
+@pytest.mark.parametrize("shape", ["single_node", "small_graphs_types", "big_graphs", "odd_literals_two_classes", "wide"])
+def test_node_stream_scoring(engine_lib, shape):
+    """Depth-1 scoring goes through the node-stream kernel (tiles of graphs, transposed literals, included-literal
+    lists).  Class sums must equal the CPU checker's and the general kernel's (reached through transform), for whole
+    sets spanning many tiles and for sub-ranges that start and end inside tiles."""
+    rng = np.random.default_rng(23)
+    np.random.seed(23)
+    if shape == "single_node":
+        mk, gk, n = dict(clauses=300, classes=10, literals=256, threshold=80, s=6.0), dict(hv_size=128, fixed_nodes=1, max_nodes=1, max_props=40, symbols=60), 2500
+    elif shape == "small_graphs_types":
+        mk, gk, n = dict(clauses=150, classes=3, literals=64, threshold=40, s=3.0), dict(hv_size=32, max_nodes=9, node_types=3), 700
+    elif shape == "big_graphs":
+        mk, gk, n = dict(clauses=90, classes=4, literals=96, threshold=40, s=3.0), dict(hv_size=48, max_nodes=400, node_types=2, max_degree=0), 40
+    elif shape == "odd_literals_two_classes":
+        mk, gk, n = dict(clauses=77, classes=2, literals=42, threshold=30, s=2.0, max_included=5), dict(hv_size=21, max_nodes=40), 300
+    else:
+        mk, gk, n = dict(clauses=64, classes=16, literals=4096, threshold=30, s=9.0), dict(hv_size=2048, max_nodes=20, symbols=200, max_props=30), 150
+    graphs = random_graphs(n, rng, **gk)
+    encY = encode_labels(rng.integers(0, mk["classes"], size=n), mk["classes"], mk["threshold"])
+    kw = dict(mk, depth=1, seed=5, max_nodes=gk["max_nodes"])
+    a, b = OracleTM(**kw), EngineTM(**kw)
+    for tm in (a, b):
+        tm.set_graphs(graphs)
+        tm.prepare()
+    assert np.array_equal(a.score(), b.score()), "fresh model"
+    for _ in range(2):
+        a.fit(encY)
+        b.fit(encY)
+        want = a.score()
+        assert np.array_equal(want, b.score()), "node-stream kernel"
+        assert np.array_equal(want, b.transform()[1]), "general kernel"
+    for first, count in [(1, 1), (n // 3, n // 2), (n - 5, 5), (0, n - 1)]:
+        assert np.array_equal(want[first:first + count], b.score(first, count)), "sub-range"
+    b.close()
