@@ -46,6 +46,7 @@ PROTOTYPES = {
     "gtm_create": [C.POINTER(Config), C.POINTER(C.c_void_p)],
     "gtm_destroy": [C.c_void_p],
     "gtm_set_stream": [C.c_void_p, C.c_void_p],
+    "gtm_set_option": [C.c_void_p, C.c_char_p, C.c_int],
     "gtm_init_state": [C.c_void_p, C.c_int],
     "gtm_set_ta_state": [C.c_void_p, C.c_int, C.c_void_p],
     "gtm_get_ta_state": [C.c_void_p, C.c_int, C.c_void_p],
@@ -64,6 +65,7 @@ PROTOTYPES = {
     "gtm_debug_evaluate": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
                            C.c_void_p, C.c_void_p],
     "gtm_debug_last_feedback": [C.c_void_p, C.c_void_p, C.c_void_p],
+    "gtm_debug_fit_phase_cycles": [C.c_void_p, C.c_void_p],
 }
 
 _lib = None

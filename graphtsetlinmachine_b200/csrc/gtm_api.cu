@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cmath>
 #include <cstring>
 #include <new>
 #include <string>
@@ -27,8 +28,12 @@ struct gtm_model {
     u32 *recorded = nullptr;
     // learning-kernel buffers
     int fit_grid = 0, fit_block = 512;
-    int *partial = nullptr, *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
+    int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
+    unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
+    int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
+    int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel
     unsigned *barrier = nullptr;
+    unsigned long long *phase_cycles = nullptr;
     // node-stream scoring: derived include lists (rebuilt when the automata changed)
     StreamModel sm;
     bool lists_dirty = true;
@@ -60,9 +65,22 @@ static int bind(gtm_model *m)
     return GTM_OK;
 }
 
+// largest float that is <= d
+static float float_round_down(double d)
+{
+    float f = (float)d;
+    if ((double)f > d) f = nextafterf(f, -INFINITY);
+    return f;
+}
+
 static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 static u32 tail_mask(int bits) { return (bits % 32) ? ~(0xffffffffu << (bits % 32)) : 0xffffffffu; }
 static int layer_words(const gtm_model *m, int layer) { return layer == 0 ? m->dm.L0 : m->dm.M; }
+static u32 *layer_planes(const gtm_model *m, int layer)
+{
+    const DevModel &d = m->dm;
+    return layer == 0 ? d.ta0 : d.tam + (size_t)(layer - 1) * d.C * d.SB * d.M;
+}
 
 // --------------------------------------------------------------------------------------------- library
 extern "C" const char *gtm_version(void) { return "gtm_b200 0.1 (sm_100a)"; }
@@ -108,6 +126,8 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     d.lit_mask = tail_mask(d.literals); d.msg_mask = tail_mask(2 * d.MS);
     for (int i = 0; i < kMaxDepth; ++i) d.s[i] = cfg->s[i];
     d.q_keep = 1.0 * cfg->q / (double)std::max(1, d.K - 1);
+    d.q_keep_f = float_round_down(d.q_keep);
+    for (int i = 0; i < kMaxDepth; ++i) d.p_mask[i] = cfg->s[i] > 0.0f ? float_round_down(1.0 / (double)cfg->s[i]) : 1.0f;
     d.seed_lo = (u32)cfg->seed; d.seed_hi = (u32)(cfg->seed >> 32);
 
     cudaDeviceProp prop;
@@ -115,7 +135,8 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     m->sm_count = prop.multiProcessorCount;
 
     int st = GTM_OK;
-    for (int l = 0; l < d.D && st == GTM_OK; ++l) st = dev_alloc(&d.ta[l], (size_t)d.C * d.SB * (l == 0 ? d.L0 : d.M));
+    st = dev_alloc(&d.ta0, (size_t)d.C * d.SB * d.L0);
+    if (st == GTM_OK) st = dev_alloc(&d.tam, (size_t)std::max(1, d.D - 1) * d.C * d.SB * d.M);
     u32 *hv = nullptr;
     if (st == GTM_OK) st = dev_alloc(&d.weights, (size_t)d.K * d.C);
     if (st == GTM_OK) st = dev_alloc(&hv, (size_t)d.C * d.MB);
@@ -125,6 +146,7 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     if (st == GTM_OK) st = dev_alloc(&m->class_sum_tap, (size_t)d.K);
     if (st == GTM_OK) st = dev_alloc(&m->barrier, 1);
     if (st == GTM_OK) st = dev_alloc(&m->error, 1);
+    if (st == GTM_OK) st = dev_alloc(&m->phase_cycles, 8);
     if (st != GTM_OK) { gtm_destroy(m); return st; }
     d.hv = hv;
     cudaMemset(hv, 0, (size_t)d.C * d.MB * sizeof(u32));
@@ -133,14 +155,14 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
 
     // learning grid: all CTAs must be co-resident (cooperative launch); no more warps than clauses
     int per_sm = 0;
-    size_t smem = 2 * (size_t)d.K * sizeof(int);
+    size_t smem = 4 * (size_t)d.K * sizeof(int);
     cudaError_t e = d.SB <= 8
         ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<8>, m->fit_block, smem)
         : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<32>, m->fit_block, smem);
     if (e != cudaSuccess || per_sm < 1) { gtm_destroy(m); return fail(GTM_ERR_CUDA, "learning kernel does not fit on this device: %s", cudaGetErrorString(e)); }
     const int warps_per_cta = m->fit_block / 32;
     m->fit_grid = std::max(1, std::min(m->sm_count * std::min(per_sm, 2), (d.C + warps_per_cta - 1) / warps_per_cta));
-    st = dev_alloc(&m->partial, 2 * (size_t)m->fit_grid * d.K);
+    st = dev_alloc(&m->exchange, 2 * (size_t)(2 * m->sm_count) * d.K);
     if (st == GTM_OK) st = stream_model_create(&m->sm, d);
     if (st != GTM_OK) { gtm_destroy(m); return fail(st, "device allocation failed"); }
     *out = m;
@@ -151,10 +173,10 @@ extern "C" int gtm_destroy(gtm_model *m)
 {
     if (!m) return GTM_OK;
     cudaSetDevice(m->cfg.device);
-    for (int l = 0; l < kMaxDepth; ++l) cudaFree(m->dm.ta[l]);
+    cudaFree(m->dm.ta0); cudaFree(m->dm.tam);
     cudaFree(m->dm.weights); cudaFree((void *)m->dm.hv); cudaFree(m->dm.draw_pos); cudaFree(m->recorded);
-    cudaFree(m->partial); cudaFree(m->error); cudaFree(m->clause_node); cudaFree(m->update);
-    cudaFree(m->class_sum_tap); cudaFree(m->barrier);
+    cudaFree(m->exchange); cudaFree(m->error); cudaFree(m->clause_node); cudaFree(m->update);
+    cudaFree(m->class_sum_tap); cudaFree(m->barrier); cudaFree(m->phase_cycles);
     stream_model_destroy(&m->sm);
     delete m;
     return GTM_OK;
@@ -167,6 +189,15 @@ extern "C" int gtm_set_stream(gtm_model *m, void *stream)
     return GTM_OK;
 }
 
+extern "C" int gtm_set_option(gtm_model *m, const char *name, int value)
+{
+    GTM_TRY(bind(m));
+    if (!name) return fail(GTM_ERR_ARG, "option name is null");
+    if (!strcmp(name, "fit_kernel") && value >= 0 && value <= 2) { m->opt_fit_kernel = value; return GTM_OK; }
+    if (!strcmp(name, "score_kernel") && value >= 0 && value <= 2) { m->opt_score_kernel = value; return GTM_OK; }
+    return fail(GTM_ERR_ARG, "unknown option '%s' or value %d out of range", name, value);
+}
+
 extern "C" int gtm_init_state(gtm_model *m, int reset_message_layers)
 {
     GTM_TRY(bind(m));
@@ -175,7 +206,7 @@ extern "C" int gtm_init_state(gtm_model *m, int reset_message_layers)
     for (int l = 0; l < d.D; ++l) {
         if (l > 0 && !reset_message_layers) break;
         const size_t total = (size_t)d.C * d.SB * layer_words(m, l);
-        init_planes_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(d.ta[l], d.C, d.SB, layer_words(m, l));
+        init_planes_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(layer_planes(m, l), d.C, d.SB, layer_words(m, l));
     }
     GTM_CU(cudaGetLastError());
     GTM_CU(cudaStreamSynchronize(m->stream));
@@ -202,7 +233,7 @@ extern "C" int gtm_set_ta_state(gtm_model *m, int layer, const uint32_t *ta)
     GTM_TRY(dev_alloc(&tmp, total));
     cudaError_t e = cudaMemcpyAsync(tmp, ta, total * sizeof(u32), cudaMemcpyHostToDevice, m->stream);
     if (e == cudaSuccess) {
-        planes_from_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(tmp, d.ta[layer], d.C, d.SB, W);
+        planes_from_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(tmp, layer_planes(m, layer), d.C, d.SB, W);
         e = cudaStreamSynchronize(m->stream);
     }
     cudaFree(tmp);
@@ -222,7 +253,7 @@ extern "C" int gtm_get_ta_state(gtm_model *m, int layer, uint32_t *out)
     const size_t total = (size_t)d.C * d.SB * W;
     u32 *tmp;
     GTM_TRY(dev_alloc(&tmp, total));
-    planes_to_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(d.ta[layer], tmp, d.C, d.SB, W);
+    planes_to_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(layer_planes(m, layer), tmp, d.C, d.SB, W);
     cudaError_t e = cudaMemcpyAsync(out, tmp, total * sizeof(u32), cudaMemcpyDeviceToHost, m->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     cudaFree(tmp);
@@ -324,6 +355,18 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s));
     GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s));
     GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s));
+    {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows)
+        std::vector<u32> e0((size_t)v->number_of_graphs), ne((size_t)v->number_of_graphs);
+        for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
+            const u32 nb = v->node_index[gi], nn = v->number_of_graph_nodes[gi];
+            e0[gi] = v->edge_index[nb];
+            const u32 last = nb + nn - 1;
+            ne[gi] = v->edge_index[last] + v->number_of_graph_node_edges[last] - e0[gi];
+        }
+        GTM_TRY(upload(ds, &ds->dg.graph_edge0, e0.data(), e0.size(), s));
+        GTM_TRY(upload(ds, &ds->dg.graph_edges, ne.data(), ne.size(), s));
+        GTM_CU(cudaStreamSynchronize(s));   // the vectors go out of scope
+    }
     ds->dg.n_types = 1;
 
     // learning scratch
@@ -430,7 +473,9 @@ extern "C" int gtm_score_device(gtm_model *m, gtm_dataset *ds, int n_types, int6
     GTM_TRY(check_range(m, ds, n_types, first, count));
     if (count == 0) return GTM_OK;
     if (!sums_dev) return fail(GTM_ERR_ARG, "class_sums_device is null");
-    if (stream_supported(ds->sd, n_types)) {
+    if (m->opt_score_kernel == 2 && !stream_supported(ds->sd, n_types))
+        return fail(GTM_ERR_ARG, "the node-stream scoring kernel does not cover this model / graph set");
+    if (m->opt_score_kernel != 1 && stream_supported(ds->sd, n_types)) {
         GTM_TRY(refresh_lists(m));
         return stream_score(m->sm, ds->sd, m->dm, ds->dg, n_types, first, count, sums_dev, m->stream);
     }
@@ -478,6 +523,35 @@ extern "C" int gtm_transform(gtm_model *m, gtm_dataset *ds, int n_types, int64_t
 }
 
 // --------------------------------------------------------------------------------------------- learning
+constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
+
+// Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0; size_t smem = 0; };
+
+static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
+{
+    const DevModel &d = m->dm;
+    ResidentPlan plan;
+    const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+    const int warps = kResidentThreads / 32;
+    int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
+    words = (words + 3) & ~3;
+    for (int per_sm = 2; per_sm >= 1; --per_sm) {
+        int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
+        const int cpb = (d.C + grid - 1) / grid;
+        grid = (d.C + cpb - 1) / cpb;
+        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) + (size_t)cpb * words * sizeof(u32);
+        if (smem > 200 * 1024) continue;
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
+        if ((long long)occ * m->sm_count < grid) continue;
+        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.smem = smem;
+        return plan;
+    }
+    return plan;
+}
+
 static int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
                       int epochs, int eval_only)
 {
@@ -486,26 +560,42 @@ static int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_d
     g.n_types = n_types;
     EvalScratch sc = ds->fit_sc;
     FitArgs a;
+    memset(&a, 0, sizeof a);
     a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
-    a.partial = m->partial; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
+    a.exchange = m->exchange; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
+    a.max_nodes = ds->max_nodes;
     a.barrier = m->barrier; a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
     a.class_sum_tap = m->class_sum_tap;
+    a.phase_cycles = m->phase_cycles;
+    a.NC = ds->NC;
     const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
     GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
     GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
+    GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
     if (d.D > 1) {
         GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
         GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
     }
     DevModel dm = d;
-    void *args[] = {&dm, &g, &sc, &a, &eval_only};
-    const size_t smem = 2 * (size_t)d.K * sizeof(int);
-    const void *fn = d.SB <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>;
-    GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
+    ResidentPlan plan;
+    if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds);
+    if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
+        return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
+    if (plan.grid > 0) {
+        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words;
+        void *args[] = {&dm, &g, &a};
+        const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(plan.grid), dim3(kResidentThreads), args, plan.smem, m->stream));
+    } else {
+        void *args[] = {&dm, &g, &sc, &a, &eval_only};
+        const size_t smem = 4 * (size_t)d.K * sizeof(int);
+        const void *fn = d.SB <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>;
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
+    }
     int err = 0;
     GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
     GTM_CU(cudaStreamSynchronize(m->stream));
-    if (err) return fail(GTM_ERR_TIMEOUT, "a grid barrier of the learning kernel gave up waiting");
+    if (err) return fail(GTM_ERR_TIMEOUT, "a bounded wait of the learning kernel (grid barrier or vote exchange) gave up");
     return GTM_OK;
 }
 
@@ -596,6 +686,15 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         return GTM_OK;
     }
     return fail(GTM_ERR_ARG, "path must be 0 (scoring kernel) or 1 (learning kernel)");
+}
+
+extern "C" int gtm_debug_fit_phase_cycles(gtm_model *m, uint64_t *cycles_out)
+{
+    GTM_TRY(bind(m));
+    if (!cycles_out) return fail(GTM_ERR_ARG, "cycles_out is null");
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    GTM_CU(cudaMemcpy(cycles_out, m->phase_cycles, 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    return GTM_OK;
 }
 
 extern "C" int gtm_debug_last_feedback(gtm_model *m, int32_t *clause_node_out, int32_t *update_out)

@@ -2,7 +2,7 @@
 // Philox4x32-10 draw streams, bit-sliced automaton arithmetic and the per-layer clause evaluation.
 //
 // Internal layouts (device memory):
-//   ta[layer]   uint32[C][SB][W]   automaton planes of a clause are contiguous; plane SB-1 is the include mask;
+//   ta0 / tam   uint32[C][SB][W] per layer: automaton planes of a clause are contiguous; plane SB-1 is the include mask;
 //                                  W = ceil(literals/32) for layer 0, ceil(2*message_size/32) for layers >= 1.
 //                                  (The reference keeps uint32[C][W][SB]: kernels.py:58,437.  Converted at the ABI.)
 //   weights     int32[K][C]        as the reference (kernels.py:312).
@@ -32,7 +32,13 @@ struct DevModel {
     u32 lit_mask, msg_mask;    // valid bits of the last literal word (FILTER / MESSAGE_FILTER, kernels.py:37-47)
     float s[kMaxDepth];
     double q_keep;             // 1.0*Q/max(1, CLASSES-1)   (kernels.py:384)
-    u32 *ta[kMaxDepth];
+    // The reference compares float uniforms with double thresholds (`u <= 1.0/s`, `u > 1.0*Q/...`).  For a float u
+    // and a double d, u <= d  <=>  u <= rd(d) and u > d  <=>  u > rd(d), rd = round towards -inf to float, so the
+    // hot loops compare floats and stay exact.
+    float p_mask[kMaxDepth];   // rd(1.0 / s[layer])
+    float q_keep_f;            // rd(q_keep)
+    u32 *ta0;                  // layer 0 planes            [C][SB][L0]
+    u32 *tam;                  // message-layer planes      [D-1][C][SB][M]
     int *weights;
     const u32 *hv;
     u64 *draw_pos;             // [C] draws consumed per clause stream
@@ -43,8 +49,34 @@ struct DevModel {
 
 struct DevGraphs {
     const u32 *X, *node_type, *degree, *edge_index, *edge, *node_index, *n_nodes;
+    const u32 *graph_edge0, *graph_edges;   // per graph: first edge row and number of edge rows (derived at upload)
     int n_types;
 };
+
+// One graph as the evaluation sees it: either pointers into the uploaded arrays or into a shared-memory copy.
+struct GraphView {
+    const u32 *X;        // literal rows, row v at X + v*L0
+    const u32 *type;     // [n] node types
+    const u32 *degree;   // [n] out-degrees
+    const u32 *eidx;     // [n] CSR row starts (absolute edge rows)
+    const u32 *edge;     // edge rows (dst, type); row r of the graph set is at edge + 2*(r - e_off)
+    u32 e_off;
+    int n;
+};
+
+__device__ __forceinline__ GraphView global_graph(const DevGraphs &g, int64_t e, int L0)
+{
+    GraphView v;
+    const u32 base = g.node_index[e];
+    v.n = (int)g.n_nodes[e];
+    v.X = g.X + (size_t)base * L0;
+    v.type = g.node_type + base;
+    v.degree = g.degree + base;
+    v.eidx = g.edge_index + base;
+    v.edge = g.edge;
+    v.e_off = 0;
+    return v;
+}
 
 // Per-"context" scratch: one for the learning kernel, one per CTA for the scoring kernel.
 struct EvalScratch {
@@ -114,30 +146,43 @@ __device__ __forceinline__ u32 msg_word(const u32 *Prow, int w, int MS, int MW)
 }
 
 // ------------------------------------------------------------------------------------------- clause evaluation
-// One warp evaluates clause `c` at layer `d` over all nodes of graph e (lanes = the 32 nodes of a node word) and
-// writes cno[slot(d)][c][*].  Layer 0 tests the node's literal row, layer d >= 1 the node's message row ANDed
-// with the node's bit of layer d-1 (kernels.py:407-530).  Returns the OR of the words written (warp-uniform).
-// When `scatter` is set, every true node sends the clause's hypervector bits along its out-edges into P[d]
-// (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
-__device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const DevGraphs &g, const EvalScratch &sc,
-                                                 int c, int d, int n, int base, int lane, bool scatter)
+// Where one clause's state lives.  The general kernels point these at global memory, the state-resident learning
+// kernel at shared memory; the arithmetic is the same code either way.
+struct ClauseView {
+    u32 *ta0;             // this clause's planes of layer 0: [SB][L0]; plane SB-1 = include mask
+    u32 *tam;             // planes of message layer 1: [SB][M]; layer l >= 1 sits (l-1)*tam_stride words further
+    size_t tam_stride;
+    __device__ __forceinline__ u32 *ta(int l) const { return l == 0 ? ta0 : tam + (size_t)(l - 1) * tam_stride; }
+    int *wgt;             // weight of class k at wgt[k * wstride]
+    int wstride;
+    u64 *pos;             // draws consumed by the clause's stream
+    int *n_inc;           // include count summed over layers (kernels.py:440,502)
+    const u32 *hv;        // [MB] message hypervector of the clause
+};
+
+// One warp evaluates a clause at layer `d` over all nodes of a graph (lanes = the 32 nodes of a node word) and
+// writes the node-output words out[0..ceil(n/32)).  Layer 0 tests the node's literal row, layer d >= 1 the node's
+// message row ANDed with the node's bit of layer d-1 in `prev` (kernels.py:407-530).  Returns the OR of the words
+// written (warp-uniform).  When `Pscatter` is given, every true node sends the clause's hypervector bits along
+// its out-edges into it (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
+__device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphView &gv, int n_types, const ClauseView &cv,
+                                                 int c, int d, const u32 *prev, u32 *out, const u32 *Pread, u32 *Pscatter,
+                                                 int lane)
 {
+    const int n = gv.n;
     const int W = d == 0 ? m.L0 : m.M;
-    const u32 *inc = m.ta[d] + ((size_t)c * m.SB + (m.SB - 1)) * W;
+    const u32 *inc = cv.ta(d) + (size_t)(m.SB - 1) * W;
     const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
-    const int slot = sc.cno_slots == 2 ? (d & 1) : d;
-    const int pslot = sc.cno_slots == 2 ? ((d - 1) & 1) : d - 1;
-    u32 *out = sc.cno + ((size_t)slot * m.C + c) * sc.NC;
-    const u32 *prev = d > 0 ? sc.cno + ((size_t)pslot * m.C + c) * sc.NC : nullptr;
-    const u32 my_type = (u32)(c % g.n_types);
+    const u32 my_type = (u32)(c % n_types);
 
     // include count of this layer (kernels.py:251-277); lanes stride over words
     int cnt = 0;
     for (int w = lane; w < W; w += 32) cnt += __popc(inc[w] & (w == W - 1 ? last_mask : kFull));
     cnt = __reduce_add_sync(kFull, cnt);
-    if (lane == 0) sc.n_inc[c] = (d == 0 ? 0 : sc.n_inc[c]) + cnt;
+    if (lane == 0) *cv.n_inc = (d == 0 ? 0 : *cv.n_inc) + cnt;
 
     const int words = (n + 31) >> 5;
+    const bool wide = d == 0 && (W & 3) == 0;     // literal rows are 16-byte aligned: 128-bit loads
     u32 any = 0;
     for (int j = 0; j < words; ++j) {
         const int v = j * 32 + lane;
@@ -147,31 +192,42 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const DevGra
             if (pw == 0) { if (lane == 0) out[j] = 0; continue; }       // uniform: nothing can stay true
             ok = ok && ((pw >> lane) & 1u);
         }
-        ok = ok && g.node_type[base + (ok ? v : 0)] == my_type;
+        ok = ok && gv.type[ok ? v : 0] == my_type;
         if (__any_sync(kFull, ok)) {
-            const u32 *row = d == 0 ? g.X + (size_t)(base + (v < n ? v : 0)) * W
-                                    : sc.P + ((size_t)(d - 1) * sc.max_nodes + (v < n ? v : 0)) * m.MW;
-            for (int w = 0; w < W; ++w) {
-                u32 iw = inc[w];   // plain load: the learning kernel rewrites these planes
-                if (w == W - 1) iw &= last_mask;
-                if (iw == 0) continue;                                   // uniform
-                const u32 x = d == 0 ? row[w] : msg_word(row, w, m.MS, m.MW);
-                ok = ok && ((iw & ~x) == 0);
-                if (!__any_sync(kFull, ok)) break;                       // warp-ballot early exit
+            const int vv = v < n ? v : 0;
+            if (wide) {
+                const uint4 *row = reinterpret_cast<const uint4 *>(gv.X + (size_t)vv * W);
+                for (int w4 = 0; w4 < W; w4 += 4) {
+                    u32 i0 = inc[w4], i1 = inc[w4 + 1], i2 = inc[w4 + 2], i3 = inc[w4 + 3];
+                    if (w4 + 4 == W) i3 &= last_mask;
+                    if ((i0 | i1 | i2 | i3) == 0) continue;                  // uniform
+                    const uint4 x = row[w4 >> 2];
+                    ok = ok && (((i0 & ~x.x) | (i1 & ~x.y) | (i2 & ~x.z) | (i3 & ~x.w)) == 0);
+                    if (!__any_sync(kFull, ok)) break;                       // warp-ballot early exit
+                }
+            } else {
+                const u32 *row = d == 0 ? gv.X + (size_t)vv * W : Pread + (size_t)vv * m.MW;
+                for (int w = 0; w < W; ++w) {
+                    u32 iw = inc[w];
+                    if (w == W - 1) iw &= last_mask;
+                    if (iw == 0) continue;                                   // uniform
+                    const u32 x = d == 0 ? row[w] : msg_word(row, w, m.MS, m.MW);
+                    ok = ok && ((iw & ~x) == 0);
+                    if (!__any_sync(kFull, ok)) break;
+                }
             }
         }
         const u32 word = __ballot_sync(kFull, ok);
         if (lane == 0) out[j] = word;
         any |= word;
-        if (scatter && ok) {
-            const u32 e0 = g.edge_index[base + v], deg = g.degree[base + v];
-            u32 *Pd = sc.P + (size_t)d * sc.max_nodes * m.MW;
+        if (Pscatter && ok) {
+            const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
             for (u32 k = 0; k < deg; ++k) {
-                const u32 dst = g.edge[2 * (size_t)(e0 + k)], t = g.edge[2 * (size_t)(e0 + k) + 1];
+                const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
                 if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
                 for (int b = 0; b < m.MB; ++b) {
-                    const u32 bit = (u32)(((u64)m.hv[(size_t)c * m.MB + b] + t) % (u32)m.MS);
-                    atomicOr(Pd + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
+                    const u32 bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                    atomicOr(Pscatter + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
                 }
             }
         }

@@ -51,7 +51,7 @@ __global__ void stream_count_kernel(DevModel m, int *cnt)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= m.C) return;
-    const u32 *inc = m.ta[0] + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
+    const u32 *inc = m.ta0 + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
     int n = 0;
     for (int w = 0; w < m.L0; ++w) n += __popc(inc[w] & (w == m.L0 - 1 ? m.lit_mask : kFull));
     cnt[c] = (n + 3) & ~3;
@@ -80,7 +80,7 @@ __global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *l
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= m.C) return;
-    const u32 *inc = m.ta[0] + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
+    const u32 *inc = m.ta0 + ((size_t)c * m.SB + (m.SB - 1)) * m.L0;
     int at = off[c];
     for (int w = 0; w < m.L0; ++w) {
         u32 bits = inc[w] & (w == m.L0 - 1 ? m.lit_mask : kFull);
@@ -113,7 +113,7 @@ template <int KP>
 __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevModel m, DevGraphs g, StreamArgs a)
 {
     extern __shared__ u32 s_dyn[];
-    const int TNC = a.TNC, TN = TNC * 32;
+    const int TNC = a.TNC;
     u32 *XT = s_dyn;                                   // [literals+1][TNC]
     u32 *TMV = XT + (size_t)(m.literals + 1) * TNC;    // [n_types][TNC] valid & node type
     u32 *R = TMV + (size_t)g.n_types * TNC;            // [CB][TNC]

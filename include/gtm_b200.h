@@ -86,6 +86,12 @@ int gtm_destroy(gtm_model *model);
  * default stream, which is also the default). */
 int gtm_set_stream(gtm_model *model, void *cuda_stream);
 
+/* Kernel selection (the reference has one code path; its only launch knobs are grid/block, tm.py:53-54).
+ *   "fit_kernel":   0 = automatic, 1 = learning kernel with state in global memory, 2 = state-resident kernel
+ *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel
+ * Forcing a kernel that cannot serve the model makes the next fit / score call fail with GTM_ERR_ARG. */
+int gtm_set_option(gtm_model *model, const char *name, int value);
+
 /* Replaces the `prepare` launch of tm.py:518,525 (kernels.py:638-664) and, when reset_message_layers != 0,
  * the `prepare_message_ta_state` launches of tm.py:520-521 (kernels.py:622-636): weights +-1 from one draw
  * per (clause, class), every automaton one step below the include boundary. */
@@ -147,6 +153,10 @@ int gtm_transform(gtm_model *model, gtm_dataset *dataset, int number_of_node_typ
 int gtm_debug_evaluate(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t graph, int path,
                        uint32_t *cno_out, uint32_t *messages_out, int32_t *n_inc_out, int32_t *class_sum_out);
 int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t *class_clause_update_out);
+
+/* Profiling tap (no counterpart in the reference): SM clock cycles that CTA 0 of the last gtm_fit launch spent in
+ * its four phases, uint64[4] = {clause evaluation, waiting at grid barriers, summing vote partials, feedback}. */
+int gtm_debug_fit_phase_cycles(gtm_model *model, uint64_t *cycles_out);
 
 #ifdef __cplusplus
 }

@@ -42,10 +42,11 @@ def test_engine_matches_golden(engine_lib, name):
     tm.close()
 
 
+@pytest.mark.parametrize("fit_kernel", [1, 2], ids=["state_in_global_memory", "state_resident"])
 @pytest.mark.parametrize("name", sorted(CASES))
-def test_engine_matches_checker_step_by_step(engine_lib, name):
+def test_engine_matches_checker_step_by_step(engine_lib, name, fit_kernel):
     kw, graphs, encY, epochs = make_case(name, seed=200 + sorted(CASES).index(name))
-    a, b = OracleTM(**kw), EngineTM(**kw)
+    a, b = OracleTM(**kw), EngineTM(**kw, options={"fit_kernel": fit_kernel})
     for tm in (a, b):
         tm.set_graphs(graphs)
         tm.prepare()
@@ -130,8 +131,9 @@ def test_state_round_trip_and_load(engine_lib):
     b.close()
 
 
+@pytest.mark.parametrize("fit_kernel", [1, 0], ids=["state_in_global_memory", "automatic"])
 @pytest.mark.parametrize("shape", ["wide_literals", "many_clauses", "big_graphs", "many_classes"])
-def test_larger_shapes(engine_lib, shape):
+def test_larger_shapes(engine_lib, shape, fit_kernel):
     """Sizes that exercise loops the small cases do not: more than 32 automaton words per clause, more clauses
     than warps in the learning grid, graphs spanning many node words, more classes than lanes."""
     rng = np.random.default_rng(17)
@@ -153,7 +155,7 @@ def test_larger_shapes(engine_lib, shape):
     ms, mb = mk.get("message_size", 256), mk.get("message_bits", 2)
     hv = np.stack([rng.choice(ms, size=mb, replace=False) for _ in range(mk["clauses"])]).astype(np.uint32)
     kw = dict(mk, hypervectors=hv, seed=3, max_nodes=gk["max_nodes"])
-    a, b = OracleTM(**kw), EngineTM(**kw)
+    a, b = OracleTM(**kw), EngineTM(**kw, options={"fit_kernel": fit_kernel})
     for tm in (a, b):
         tm.set_graphs(graphs)
         tm.prepare()

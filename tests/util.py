@@ -51,7 +51,7 @@ class EngineTM:
 
     def __init__(self, *, clauses, classes, literals, threshold, s, depth=1, message_size=256, message_bits=2,
                  max_included=None, boost=1, state_bits=8, q=1.0, max_nodes=1, hypervectors=None, seed=1,
-                 recorded=None, device=0):
+                 recorded=None, device=0, options=None):
         self.lib = lib = _lib.load()
         self.C, self.K, self.SB, self.depth = clauses, classes, state_bits, depth
         self.literals, self.message_size = literals, message_size
@@ -74,6 +74,8 @@ class EngineTM:
         if recorded is not None:
             rec = np.ascontiguousarray(recorded, dtype=np.uint32)
             _lib.check(lib.gtm_set_recorded_draws(self.model, _ptr(rec), rec.shape[1]))
+        for name, value in (options or {}).items():
+            _lib.check(lib.gtm_set_option(self.model, name.encode(), int(value)))
         self.ds = C.c_void_p()
         self.graphs = None
 
