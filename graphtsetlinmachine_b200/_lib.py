@@ -60,6 +60,7 @@ PROTOTYPES = {
     "gtm_dataset_destroy": [C.c_void_p],
     "gtm_score": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_score_device": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
+    "gtm_score_static_scratch": [C.c_void_p, C.POINTER(GraphsView), C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_fit": [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int],
     "gtm_transform": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p],
     "gtm_debug_evaluate": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,

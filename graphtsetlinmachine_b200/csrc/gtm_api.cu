@@ -705,3 +705,69 @@ extern "C" int gtm_debug_last_feedback(gtm_model *m, int32_t *clause_node_out, i
     if (update_out) GTM_CU(cudaMemcpy(update_out, m->update, (size_t)m->dm.K * m->dm.C * sizeof(int), cudaMemcpyDeviceToHost));
     return GTM_OK;
 }
+
+// ------------------------------------------------------------------------- scoring with built-in scratch
+// Scratch of gtm_score_static_scratch: lives in the library image, so every GPU that loads the library holds these
+// GTM_STATIC_SCRATCH_BYTES until the process exits.  In host code the name below is only a stand-in for the
+// symbol, not a device address; the address is looked up once per device (g_static_scratch_addr).
+static __device__ __align__(256) unsigned int g_static_scratch[GTM_STATIC_SCRATCH_BYTES / sizeof(unsigned int)];
+static unsigned int *g_static_scratch_addr[64];
+
+extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, int n_types, int64_t first, int64_t count,
+                                        int32_t *sums_dev)
+{
+    GTM_TRY(bind(m));
+    if (!v) return fail(GTM_ERR_ARG, "device_graphs is null");
+    if (!m->has_state) return fail(GTM_ERR_STATE, "model has no state: call gtm_init_state or gtm_set_ta_state first");
+    if (n_types < 1) return fail(GTM_ERR_ARG, "number_of_node_types must be positive");
+    if (first < 0 || count < 0 || first + count > v->number_of_graphs)
+        return fail(GTM_ERR_ARG, "graph range [%lld, %lld) outside the set of %lld graphs", (long long)first,
+                    (long long)(first + count), (long long)v->number_of_graphs);
+    if (count == 0) return GTM_OK;
+    if (!sums_dev || !v->X || !v->node_type || !v->number_of_graph_node_edges || !v->edge_index || !v->node_index ||
+        !v->number_of_graph_nodes || (v->total_edges > 0 && !v->edge))
+        return fail(GTM_ERR_ARG, "device arrays must not be null");
+    if (v->max_number_of_graph_nodes < 1) return fail(GTM_ERR_ARG, "max_number_of_graph_nodes must be positive");
+    const int dev = m->cfg.device;
+    if (dev >= 64) return fail(GTM_ERR_ARG, "device ordinal %d beyond the 64 this entry point keeps an address for", dev);
+
+    const DevModel &d = m->dm;
+    const int NC = words_for(v->max_number_of_graph_nodes);
+    const size_t cno_words = (size_t)2 * d.C * NC;
+    const size_t p_words = (size_t)std::max(1, d.D - 1) * v->max_number_of_graph_nodes * d.MW;
+    const size_t per_cta = cno_words + p_words + (size_t)d.C;                       // words of scratch one CTA needs
+    const size_t capacity = GTM_STATIC_SCRATCH_BYTES / sizeof(unsigned int);
+    if (per_cta > capacity)
+        return fail(GTM_ERR_ARG,
+                    "model and graph sizes need %zu bytes of scratch per thread block; the built-in scratch holds %u bytes "
+                    "(use gtm_dataset_create + gtm_score_device for this size)", per_cta * sizeof(unsigned int),
+                    (unsigned)GTM_STATIC_SCRATCH_BYTES);
+
+    // first call on this device: resolve the device address of the built-in array (this device is current)
+    if (!g_static_scratch_addr[dev]) {
+        unsigned int *addr = nullptr;
+        GTM_CU(cudaGetSymbolAddress((void **)&addr, g_static_scratch));
+        g_static_scratch_addr[dev] = addr;
+    }
+    unsigned int *scratch_base = g_static_scratch_addr[dev];
+
+    const int64_t fit_ctas = (int64_t)(capacity / per_cta);
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(count, fit_ctas), (int64_t)m->sm_count * 4));
+
+    DevGraphs g;
+    memset(&g, 0, sizeof g);
+    g.X = v->X; g.node_type = v->node_type; g.degree = v->number_of_graph_node_edges; g.edge_index = v->edge_index;
+    g.edge = v->edge; g.node_index = v->node_index; g.n_nodes = v->number_of_graph_nodes;
+    g.n_types = n_types;
+    EvalScratch sc;
+    sc.cno = scratch_base;
+    sc.P = scratch_base + cno_words;
+    sc.n_inc = reinterpret_cast<int *>(scratch_base + cno_words + p_words);
+    sc.NC = NC; sc.cno_slots = 2; sc.max_nodes = v->max_number_of_graph_nodes;
+    ScoreArgs a;
+    a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr;
+    a.cno_stride = a.P_stride = a.ninc_stride = per_cta;                             // one contiguous slice per CTA
+    score_graphs_kernel<<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
+    GTM_CU(cudaGetLastError());
+    return GTM_OK;
+}

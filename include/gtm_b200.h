@@ -131,6 +131,31 @@ int gtm_score(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, 
 int gtm_score_device(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first,
                      int64_t count, int32_t *class_sums_device);
 
+/* Scoring for callers that must not allocate device memory.  NO COUNTERPART IN THE REFERENCE (it allocates per graph
+ * set with cuda.mem_alloc, tm.py:759-784).
+ *
+ * Who needs it: a host program that hands this library a GPU it manages itself -- all device memory reserved up
+ * front in its own pool, or a serving loop whose latency budget rules out cudaMalloc/cudaFree (both serialise the
+ * device) -- and therefore keeps graph sets and results in buffers it owns.  gtm_dataset_create and gtm_score
+ * allocate (copies of the graph set, per-block scratch, a result buffer); this entry point allocates nothing:
+ *  - device_graphs holds DEVICE pointers to the caller's copies of the graph arrays (same layouts as the host view);
+ *  - class_sums_device is the caller's device buffer int32[count][CLASSES];
+ *  - the scratch the scoring kernel needs (node-output words, message rows, include counts per thread block) is a
+ *    GTM_STATIC_SCRATCH_BYTES array built into the library image; every GPU that loads the library holds it until
+ *    the process exits.
+ * It runs the general scoring kernel (any depth), queues the work on the model's stream and returns without
+ * synchronising, like gtm_score_device, and gives the same class sums.
+ * Limits: the scratch of ONE thread block, 4*(2*CLAUSES*ceil(max_nodes/32) + max(1,depth-1)*max_nodes*
+ * ceil(MESSAGE_SIZE/32) + CLAUSES) bytes, must fit in GTM_STATIC_SCRATCH_BYTES, otherwise GTM_ERR_ARG (nothing is
+ * launched); fewer thread blocks run concurrently the larger that figure is.  Device ordinals 0..63.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) -- make that first call
+ * before any stream capture.  All calls share the one array and find the previous call's contents in it (the
+ * kernel clears what it needs zeroed); two calls whose kernels overlap on the GPU, on any streams or models of the
+ * same device, race on it -- serialise them. */
+#define GTM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int gtm_score_static_scratch(gtm_model *model, const gtm_graphs_view *device_graphs, int number_of_node_types,
+                             int64_t first, int64_t count, int32_t *class_sums_device);
+
 /* Replaces the learning loop of tm.py:668-747 (_fit): `epochs` passes over graphs [first, first+count) in
  * order; encoded_Y is int32[number_of_graphs][CLASSES] with +-T targets (tm.py:949-951), indexed by the
  * absolute graph id. */
