@@ -1,0 +1,69 @@
+"""Graph-sharded scoring over several GPUs of one box: one process per GPU, no collective on the data path.
+
+Graphs are independent at inference, so rank ``r`` scores a contiguous range of graphs balanced by node count and
+the per-rank class sums (disjoint rows of ``int32[N][K]``) are gathered at the end.  ``torch.distributed`` supplies
+the process group (NCCL on GPUs, gloo in the CPU tests); the scoring itself is whatever ``score_range`` does —
+``GraphShardScorer`` uses the engine, the tests plug in a CPU function.
+"""
+
+import numpy as np
+
+__all__ = ["balanced_ranges", "gather_rows", "GraphShardScorer"]
+
+
+def balanced_ranges(number_of_graph_nodes, parts):
+    """``parts`` contiguous (first, count) graph ranges whose node totals are as even as a prefix cut allows.
+    Ranges may be empty when there are fewer graphs than parts."""
+    nodes = np.asarray(number_of_graph_nodes, dtype=np.int64)
+    n = len(nodes)
+    prefix = np.concatenate([[0], np.cumsum(nodes)])
+    cuts = [0]
+    for p in range(1, parts):
+        target = prefix[-1] * p / parts
+        cut = int(np.searchsorted(prefix, target, side="left"))
+        cuts.append(min(max(cut, cuts[-1]), n))
+    cuts.append(n)
+    return [(cuts[p], cuts[p + 1] - cuts[p]) for p in range(parts)]
+
+
+def gather_rows(local_rows, counts, group=None):
+    """All ranks contribute ``local_rows`` (``[counts[rank]][K]`` int32, numpy); every rank gets the rows of all ranks
+    in rank order.  Uses a padded all_gather so that it works on every backend."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    K = local_rows.shape[1]
+    longest = max(counts) if counts else 0
+    device = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    mine = torch.zeros((longest, K), dtype=torch.int32, device=device)
+    if counts[rank]:
+        mine[:counts[rank]] = torch.from_numpy(np.ascontiguousarray(local_rows, dtype=np.int32)).to(device)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine, group=group)
+    return np.concatenate([parts[r][:counts[r]].cpu().numpy() for r in range(world)], axis=0)
+
+
+class GraphShardScorer:
+    """``score(graphs)`` over all ranks of the default process group.  Every rank holds the same model and the same
+    ``graphs`` object; each uploads and scores only its own range (``graphs[first:first+count]``)."""
+
+    def __init__(self, tm, group=None):
+        self.tm = tm
+        self.group = group
+
+    def score(self, graphs):
+        import torch.distributed as dist
+
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        ranges = balanced_ranges(graphs.number_of_graph_nodes, world)
+        first, count = ranges[rank]
+        if count:
+            local = self.tm.score(graphs[first:first + count])
+        else:
+            local = np.zeros((0, self.tm.number_of_outputs), dtype=np.int32)
+        return gather_rows(local, [c for _, c in ranges], self.group)
+
+    def predict(self, graphs):
+        return np.argmax(self.score(graphs), axis=1)
