@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libgtm_b200.so")
+LIB_PATH = os.environ.get("GTM_B200_LIB", os.path.join(HERE, "libgtm_b200.so"))   # override: an alternative build of the library
 
 GTM_MAX_DEPTH = 16
 STATUS = {0: "GTM_OK", 1: "GTM_ERR_ARG", 2: "GTM_ERR_CUDA", 3: "GTM_ERR_OOM", 4: "GTM_ERR_TIMEOUT", 5: "GTM_ERR_STATE"}

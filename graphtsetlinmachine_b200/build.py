@@ -10,11 +10,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgtm_b200.so")
-SOURCES = [os.path.join(HERE, "csrc", "gtm_api.cu")]
-NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
-]
+SOURCES = [os.path.join(HERE, "csrc", f) for f in ("gtm_api.cu", "gtm_fit_global.cu", "gtm_fit_resident.cu", "gtm_stream.cu")]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
 def _stale():
@@ -30,13 +27,26 @@ def build(force=False, verbose=False):
     if not force and not _stale():
         return LIB_PATH
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH + ".tmp"] + SOURCES
-    res = subprocess.run(cmd, capture_output=True, text=True)
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    # one object per translation unit, compiled side by side, then one link
+    jobs = []
+    for src in SOURCES:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        jobs.append((obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    log = ""
+    for obj, proc in jobs:
+        out, err = proc.communicate()
+        log += err
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + out[-2000:] + err[-6000:])
+    res = subprocess.run([nvcc, "-shared", "-o", LIB_PATH + ".tmp"] + [obj for obj, _ in jobs], capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout[-2000:] + res.stderr[-6000:])
+        raise RuntimeError("link failed:\n" + res.stdout[-2000:] + res.stderr[-6000:])
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
     if verbose:
-        print(res.stderr)
+        print(log)
     return LIB_PATH
 
 

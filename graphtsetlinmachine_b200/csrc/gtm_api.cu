@@ -12,51 +12,8 @@
 #include <string>
 #include <vector>
 
-#include "gtm_host.cuh"
+#include "gtm_handles.h"
 #include "gtm_kernels.cuh"
-#include "gtm_stream.cuh"
-
-using namespace gtm;
-
-// ---------------------------------------------------------------------------------------------- handles
-struct gtm_model {
-    gtm_config cfg;
-    DevModel dm;
-    cudaStream_t stream = nullptr;
-    int sm_count = 0;
-    bool has_state = false;
-    u32 *recorded = nullptr;
-    // learning-kernel buffers
-    int fit_grid = 0, fit_block = 512;
-    int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
-    unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
-    int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
-    int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel
-    unsigned *barrier = nullptr;
-    unsigned long long *phase_cycles = nullptr;
-    // node-stream scoring: derived include lists (rebuilt when the automata changed)
-    StreamModel sm;
-    bool lists_dirty = true;
-};
-
-struct gtm_dataset {
-    gtm_model *model;
-    DevGraphs dg;
-    int64_t n_graphs, total_nodes, total_edges;
-    int max_nodes, NC;
-    std::vector<void *> owned;
-    // learning scratch (every layer kept) and its message ping-pong
-    EvalScratch fit_sc;
-    u32 *P_pair[2] = {nullptr, nullptr};
-    // scoring scratch of the general path: one slice per CTA
-    EvalScratch score_sc;
-    size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
-    int score_grid = 0;
-    int *Y = nullptr;
-    size_t Y_capacity = 0;
-    // node-stream scoring
-    StreamData sd;
-};
 
 static int bind(gtm_model *m)
 {
@@ -154,14 +111,8 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     cudaMemset(d.weights, 0, (size_t)d.K * d.C * sizeof(int));
 
     // learning grid: all CTAs must be co-resident (cooperative launch); no more warps than clauses
-    int per_sm = 0;
-    size_t smem = 4 * (size_t)d.K * sizeof(int);
-    cudaError_t e = d.SB <= 8
-        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<8>, m->fit_block, smem)
-        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_kernel<32>, m->fit_block, smem);
-    if (e != cudaSuccess || per_sm < 1) { gtm_destroy(m); return fail(GTM_ERR_CUDA, "learning kernel does not fit on this device: %s", cudaGetErrorString(e)); }
-    const int warps_per_cta = m->fit_block / 32;
-    m->fit_grid = std::max(1, std::min(m->sm_count * std::min(per_sm, 2), (d.C + warps_per_cta - 1) / warps_per_cta));
+    st = fit_grid_for_global_state(d, m->sm_count, m->fit_block, &m->fit_grid);
+    if (st != GTM_OK) { gtm_destroy(m); return st; }
     st = dev_alloc(&m->exchange, 2 * (size_t)(2 * m->sm_count) * d.K);
     if (st == GTM_OK) st = stream_model_create(&m->sm, d);
     if (st != GTM_OK) { gtm_destroy(m); return fail(st, "device allocation failed"); }
@@ -523,82 +474,6 @@ extern "C" int gtm_transform(gtm_model *m, gtm_dataset *ds, int n_types, int64_t
 }
 
 // --------------------------------------------------------------------------------------------- learning
-constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
-
-// Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0; size_t smem = 0; };
-
-static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
-{
-    const DevModel &d = m->dm;
-    ResidentPlan plan;
-    const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
-    const int warps = kResidentThreads / 32;
-    int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
-    words = (words + 3) & ~3;
-    for (int per_sm = 2; per_sm >= 1; --per_sm) {
-        int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
-        const int cpb = (d.C + grid - 1) / grid;
-        grid = (d.C + cpb - 1) / cpb;
-        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) + (size_t)cpb * words * sizeof(u32);
-        if (smem > 200 * 1024) continue;
-        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
-        int occ = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
-        if ((long long)occ * m->sm_count < grid) continue;
-        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.smem = smem;
-        return plan;
-    }
-    return plan;
-}
-
-static int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
-                      int epochs, int eval_only)
-{
-    const DevModel &d = m->dm;
-    DevGraphs g = ds->dg;
-    g.n_types = n_types;
-    EvalScratch sc = ds->fit_sc;
-    FitArgs a;
-    memset(&a, 0, sizeof a);
-    a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
-    a.exchange = m->exchange; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
-    a.max_nodes = ds->max_nodes;
-    a.barrier = m->barrier; a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
-    a.class_sum_tap = m->class_sum_tap;
-    a.phase_cycles = m->phase_cycles;
-    a.NC = ds->NC;
-    const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
-    GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
-    GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
-    GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
-    if (d.D > 1) {
-        GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
-        GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
-    }
-    DevModel dm = d;
-    ResidentPlan plan;
-    if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds);
-    if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
-        return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
-    if (plan.grid > 0) {
-        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words;
-        void *args[] = {&dm, &g, &a};
-        const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
-        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(plan.grid), dim3(kResidentThreads), args, plan.smem, m->stream));
-    } else {
-        void *args[] = {&dm, &g, &sc, &a, &eval_only};
-        const size_t smem = 4 * (size_t)d.K * sizeof(int);
-        const void *fn = d.SB <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>;
-        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
-    }
-    int err = 0;
-    GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
-    GTM_CU(cudaStreamSynchronize(m->stream));
-    if (err) return fail(GTM_ERR_TIMEOUT, "a bounded wait of the learning kernel (grid barrier or vote exchange) gave up");
-    return GTM_OK;
-}
-
 extern "C" int gtm_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int32_t *Y, int64_t first, int64_t count, int epochs)
 {
     GTM_TRY(bind(m));

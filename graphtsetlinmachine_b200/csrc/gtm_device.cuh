@@ -235,18 +235,44 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
     return any;
 }
 
+// View of clause c in the global-memory state.
+__device__ __forceinline__ ClauseView global_view(const DevModel &m, int *n_inc, int c)
+{
+    ClauseView cv;
+    cv.ta0 = m.ta0 + (size_t)c * m.SB * m.L0;
+    cv.tam_stride = (size_t)m.C * m.SB * m.M;
+    cv.tam = m.tam + (size_t)c * m.SB * m.M;
+    cv.wgt = m.weights + c;
+    cv.wstride = m.C;
+    cv.pos = m.draw_pos + c;
+    cv.n_inc = n_inc + c;
+    cv.hv = m.hv + (size_t)c * m.MB;
+    return cv;
+}
+
+__device__ __forceinline__ u32 *cno_row(const EvalScratch &sc, int C, int d, int c)
+{
+    const int slot = sc.cno_slots == 2 ? (d & 1) : d;
+    return sc.cno + ((size_t)slot * C + c) * sc.NC;
+}
+
 // ------------------------------------------------------------------------------------- bit-sliced automata
 // +1 / -1 with saturation on the automata flagged in `active`; p[b] is plane b of one 32-automaton word
 // (kernels.py:55-96).  MAXSB is a compile-time bound so that the planes stay in registers.
+// Planes of up to 8 state bits stay in registers (loops fully unrolled, predicated on b < SB); wider automata
+// take run-time loops over an indexed array (rare, slower, keeps the code small).
+template <int MAXSB>
+__device__ __forceinline__ int plane_bound(int SB) { return MAXSB <= 8 ? MAXSB : SB; }
+
 template <int MAXSB>
 __device__ __forceinline__ void automata_inc(u32 (&p)[MAXSB], int SB, u32 active)
 {
     u32 carry = active;
 #pragma unroll
-    for (int b = 0; b < MAXSB; ++b)
+    for (int b = 0; b < plane_bound<MAXSB>(SB); ++b)
         if (b < SB) { const u32 nx = p[b] & carry; p[b] ^= carry; carry = nx; }
 #pragma unroll
-    for (int b = 0; b < MAXSB; ++b)
+    for (int b = 0; b < plane_bound<MAXSB>(SB); ++b)
         if (b < SB) p[b] |= carry;
 }
 
@@ -255,10 +281,10 @@ __device__ __forceinline__ void automata_dec(u32 (&p)[MAXSB], int SB, u32 active
 {
     u32 borrow = active;
 #pragma unroll
-    for (int b = 0; b < MAXSB; ++b)
+    for (int b = 0; b < plane_bound<MAXSB>(SB); ++b)
         if (b < SB) { const u32 nx = ~p[b] & borrow; p[b] ^= borrow; borrow = nx; }
 #pragma unroll
-    for (int b = 0; b < MAXSB; ++b)
+    for (int b = 0; b < plane_bound<MAXSB>(SB); ++b)
         if (b < SB) p[b] &= ~borrow;
 }
 

@@ -1,0 +1,353 @@
+// Device code shared by the two learning kernels: vote exchange, grid barrier, per-clause feedback.
+#pragma once
+#include <climits>
+
+#include "gtm_device.cuh"
+
+namespace gtm {
+
+// ------------------------------------------------------------------------------------------------ learning
+struct FitArgs {
+    const int *Y;           // [N][K] +-T targets, absolute graph ids
+    int64_t first, count;
+    int epochs;
+    unsigned long long *exchange;   // [2][gridDim.x][K] (vote partial << 32 | step tag), ping-pong by graph parity
+    u32 *P_pair[2];         // message buffers, ping-pong by graph parity ([D-1][max_nodes][MW] each)
+    int max_nodes;
+    unsigned *barrier;      // monotonically increasing arrival counter (zeroed before launch)
+    int *error;             // set to 1 when a bounded wait gave up
+    int *clause_node;       // [C]    tap: selected node of the last graph (kernels.py:347-349)
+    int *update;            // [K][C] feedback type (kernels.py:385-387)
+    int *class_sum_tap;     // [K]    class sums of the last graph
+    unsigned long long *phase_cycles;   // [4] SM cycles CTA 0 spent in: evaluation, barriers, vote exchange, feedback
+    // state-resident kernel only
+    int clauses_per_cta;
+    int clause_words;       // shared-memory words per clause
+    int NC;                 // node words of the largest graph
+};
+
+constexpr unsigned kSpinLimit = 1u << 22;
+
+// Grid-wide barrier over co-resident CTAs (cooperative launch).  The arrival counter only grows; arrival is a
+// release, the poll an acquire, so no separate fences are needed.  The wait is bounded: after kSpinLimit polls
+// the CTA raises *error and gives up.  Returns false once any CTA gave up.
+__device__ __forceinline__ bool grid_barrier(unsigned *counter, unsigned target, int *error)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+        unsigned spins = 0;
+        while (true) {
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            if (seen >= target) break;
+            if (*(volatile int *)error) break;
+            if (++spins > kSpinLimit) { atomicExch(error, 1); break; }
+        }
+    }
+    __syncthreads();
+    return *(volatile int *)error == 0;
+}
+
+// Class sums of one graph from per-CTA vote partials, in one round: every CTA publishes its K partials as 64-bit
+// words that carry the step tag next to the value (an aligned 8-byte store is single-copy atomic, so a reader that
+// sees the tag sees the value), then every CTA reads all gridDim.x*K words, eight independent loads per thread in
+// flight, re-polling only words whose tag is still old.  Slots alternate by graph parity: a slot is rewritten two
+// steps later, which its owner can only reach after every CTA has read the current step.
+// Call with s_sum complete (after a __syncthreads); leaves totals in s_total, clears s_sum.  Bounded polls.
+__device__ __forceinline__ bool exchange_class_sums(unsigned long long *slots, int par, u32 tag, int *s_sum, int *s_total,
+                                                    int K, int *error, int *tap)
+{
+    volatile unsigned long long *all = slots + (size_t)par * gridDim.x * K;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        all[(size_t)blockIdx.x * K + k] = ((unsigned long long)(u32)s_sum[k] << 32) | tag;
+        s_sum[k] = 0;
+        s_total[k] = 0;
+    }
+    __syncthreads();
+    const int total = (int)gridDim.x * K;
+    for (int t0 = threadIdx.x; t0 < total; t0 += 8 * blockDim.x) {
+        unsigned long long v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = t0 + j * blockDim.x;
+            v[j] = t < total ? all[t] : (unsigned long long)tag;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = t0 + j * blockDim.x;
+            if (t >= total) continue;
+            unsigned spins = 0;
+            while ((u32)v[j] != tag) {
+                if (++spins > kSpinLimit || *(volatile int *)error) { atomicExch(error, 1); break; }
+                v[j] = all[t];
+            }
+            atomicAdd(&s_total[t % K], (int)(u32)(v[j] >> 32));
+        }
+    }
+    __syncthreads();
+    if (tap && blockIdx.x == 0)
+        for (int k = threadIdx.x; k < K; k += blockDim.x) tap[k] = s_total[k];
+    return *(volatile int *)error == 0;
+}
+
+// Four consecutive draws of a clause stream: Philox block `block` (draws 4*block .. 4*block+3), or the
+// recorded words at those positions.
+__device__ __forceinline__ void draw4_at(const DevModel &m, int clause, u64 block, u32 out[4])
+{
+    if (m.recorded) {
+        const u32 *rec = m.recorded + (u64)clause * m.recorded_len;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = rec[(4 * block + i) % m.recorded_len];
+        return;
+    }
+    philox4x32_10((u32)block, (u32)(block >> 32), (u32)clause, 0u, m.seed_lo, m.seed_hi, out);
+}
+
+// One round of Bernoulli bits for Type I masks.  Lane l takes Philox block `first_block + 32*round + l`, i.e.
+// 4 consecutive draws; the warp's 128 outcomes are packed, in draw order, into 4 words returned in every lane:
+// bit t of the packed stream = [uniform(draw 4*first_block + 128*round + t) <= p]  (kernels.py:158-162 makes
+// bit b of a word's mask from the word's b-th draw; the caller aligns words to the stream with a funnel shift).
+__device__ __forceinline__ u32 bernoulli_nibbles(const DevModel &m, int clause, u64 block, float p, int lane)
+{
+    u32 o[4];
+    draw4_at(m, clause, block, o);
+    u32 nib = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) nib |= (to_uniform(o[i]) <= p ? 1u : 0u) << i;
+    return nib << (4 * (lane & 7));
+}
+
+__device__ __forceinline__ void bernoulli_round(const DevModel &m, int clause, u64 first_block, int round, float p,
+                                                int lane, u32 (&words)[4])
+{
+    const u32 mine = __reduce_or_sync(0xffu << (lane & 24), bernoulli_nibbles(m, clause, first_block + (u64)round * 32 + lane, p, lane));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) words[i] = __shfl_sync(kFull, mine, 8 * i);
+}
+
+constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of up to 8 positive classes x 32 words + 1
+
+// Type I / II feedback of one clause on one layer (kernels.py:98-183), all classes in order.  The warp owns
+// the clause; lanes hold one automaton word each (planes in registers).  `upd_lo` holds the feedback type of
+// class `lane` (classes 0..31); further classes are read back from `update`.  Layers of at most 32 words take the
+// packed Bernoulli words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds
+// in flight per step; wider layers generate them class by class.  Returns the draws consumed.
+template <int MAXSB>
+__device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
+                                              bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
+                                              u64 pos0, int lane, u32 *pack)
+{
+    const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
+    const float p = m.p_mask[layer];
+    const bool all_ones = p >= 1.0f;         // every uniform is <= 1
+    const u64 first_block = pos0 >> 2;
+    const int shift = (int)(pos0 & 3);       // the layer's first draw sits `shift` bits into the packed stream
+    int positives = 0;
+
+    for (int g0 = 0; g0 < W; g0 += 32) {
+        const int w = g0 + lane;
+        const bool mine = w < W;
+        const int wend = min(W, g0 + 32);
+        u32 pl[MAXSB];
+#pragma unroll
+        for (int b = 0; b < plane_bound<MAXSB>(SB); ++b) pl[b] = (b < SB && mine) ? ta[(size_t)b * W + w] : 0u;
+        u32 x = 0;
+        if (mine && clause_true) x = row_is_msg ? msg_word(row, w, m.MS, m.MW) : row[w];
+        int rank = 0, cached = -1;
+        bool dirty = false;
+        u32 sw[4] = {0, 0, 0, 0};
+        for (int kb = 0; kb < m.K; kb += 32) {
+            const int vals = kb == 0 ? upd_lo : (kb + lane < m.K ? update[(size_t)(kb + lane) * m.C + c] : 0);
+            const int kn = min(32, m.K - kb);
+            const u32 posmask = __ballot_sync(kFull, vals > 0 && lane < kn);
+            for (int k8 = 0; k8 < kn; k8 += 8) {
+                const int npos8 = __popc((posmask >> k8) & 0xffu);
+                const bool packed = W <= 32 && npos8 > 0 && !all_ones;
+                if (packed) {
+                    // packed-stream words rank*W .. (rank+npos8)*W [+1 when the stream is not word-aligned]
+                    const int j0 = rank * W, j1 = (rank + npos8) * W - (shift ? 0 : 1);
+                    __syncwarp();
+                    for (int q = j0 >> 2; q <= j1 >> 2; q += 2) {
+                        const u32 na = bernoulli_nibbles(m, c, first_block + (u64)q * 32 + lane, p, lane);
+                        const u32 nb = bernoulli_nibbles(m, c, first_block + (u64)(q + 1) * 32 + lane, p, lane);
+                        const u32 wa = __reduce_or_sync(0xffu << (lane & 24), na);
+                        const u32 wb = __reduce_or_sync(0xffu << (lane & 24), nb);
+                        if ((lane & 7) == 0) {
+                            const int ja = 4 * q + (lane >> 3) - j0, jb = ja + 4;
+                            if (ja >= 0 && ja <= j1 - j0) pack[ja] = wa;
+                            if (jb >= 0 && jb <= j1 - j0) pack[jb] = wb;
+                        }
+                    }
+                    __syncwarp();
+                }
+                int local = 0;
+                for (int kk = k8; kk < min(kn, k8 + 8); ++kk) {
+                    const int u = __shfl_sync(kFull, vals, kk);
+                    if (u > 0) {
+                        u32 mask = kFull;
+                        if (packed) {
+                            const u32 lo = mine ? pack[local * W + lane] : 0u;
+                            const u32 hi = (mine && shift) ? pack[local * W + lane + 1] : 0u;
+                            mask = __funnelshift_r(lo, hi, shift);
+                            ++local;
+                        } else if (!all_ones) {
+                            const int j0 = rank * W + g0;                        // packed-stream word of lane 0's mask
+                            const int j1 = rank * W + wend - (shift ? 0 : 1);    // last packed word needed
+                            u32 lo = 0, hi = 0;
+                            for (int q = j0 >> 2; q <= j1 >> 2; ++q) {
+                                if (q != cached) { bernoulli_round(m, c, first_block, q, p, lane, sw); cached = q; }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int rel = 4 * q + i - j0;
+                                    if (rel == lane) lo = sw[i];
+                                    if (rel - 1 == lane) hi = sw[i];
+                                }
+                            }
+                            mask = __funnelshift_r(lo, hi, shift);
+                        }
+                        if (clause_true && within_budget) {
+                            automata_inc<MAXSB>(pl, SB, m.boost == 1 ? x : (x & ~mask));
+                            automata_dec<MAXSB>(pl, SB, ~x & mask);
+                        } else {
+                            automata_dec<MAXSB>(pl, SB, mask);
+                        }
+                        ++rank;
+                        dirty = true;
+                    } else if (u < 0 && clause_true) {
+                        u32 include = 0;
+#pragma unroll
+                        for (int b = 0; b < plane_bound<MAXSB>(SB); ++b) if (b == SB - 1) include = pl[b];
+                        automata_inc<MAXSB>(pl, SB, ~x & ~include);
+                        dirty = true;
+                    }
+                }
+            }
+        }
+        positives = rank;
+        if (mine && dirty) {
+#pragma unroll
+            for (int b = 0; b < plane_bound<MAXSB>(SB); ++b) if (b < SB) ta[(size_t)b * W + w] = pl[b];
+        }
+    }
+    return (u64)positives * W * 32;
+}
+
+// Per-class quantities of the feedback decision that do not depend on the clause (kernels.py:373-384): computed
+// once per CTA and graph.  target = +1 / -1; thr = rd(1.0 * |y - clamp(sum)| / (2T)) as a float (see DevModel).
+__device__ __forceinline__ void class_decision_inputs(const DevModel &m, const int *s_total, const int *y, int *s_target,
+                                                      float *s_thr)
+{
+    for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
+        int sum = s_total[k];
+        sum = sum > m.T ? m.T : (sum < -m.T ? -m.T : sum);
+        const int yk = y[k];
+        s_target[k] = 1 - 2 * (sum > yk);
+        s_thr[k] = __double2float_rd(1.0 * abs(yk - sum) / (double)(2 * m.T));
+    }
+}
+
+// Everything after the class sums for one clause (kernels.py:319-405 then :185-242), in the draw order of the
+// reference: node selection, per-class decisions (+ weight move), layer-0 automata, message-layer automata.
+// Lane-parallel throughout: node words, classes (16 per pass: both possible uniforms of every class are drawn at
+// once, lanes 0..31 = the pass's next 32 draws, and a short uniform scan replays the reference's short-circuit
+// order on them) and automaton words are spread over lanes; nothing per class goes through global memory.
+// `bits` = the clause's node-output words of the last layer; `P` = message rows [D-1][max_nodes][MW].
+template <int MAXSB>
+__device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
+                                                const FitArgs &a, const u32 *bits, const u32 *P, const int *s_target,
+                                                const float *s_thr, int c, int lane, u32 *pack)
+{
+    const int words = (gv.n + 31) >> 5;
+    u64 pos = *cv.pos;
+    const int n_inc = *cv.n_inc;
+
+    // 1. one true node, uniformly: the (draw % count)-th set bit in ascending node order
+    int count = 0;
+    for (int j = lane; j < words; j += 32) count += __popc(bits[j]);
+    count = __reduce_add_sync(kFull, count);
+    int chosen = -1;
+    if (count > 0) {
+        int rank = count == 1 ? 0 : (int)(draw_at(m, c, pos) % (u32)count);   // x % 1 == 0 whatever the draw
+        ++pos;
+        for (int jb = 0; jb < words; jb += 32) {
+            const u32 wd = jb + lane < words ? bits[jb + lane] : 0u;
+            const int pc = __popc(wd);
+            int incl = pc;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += t;
+            }
+            const int total = __shfl_sync(kFull, incl, 31);
+            if (rank < total) {
+                const u32 has = __ballot_sync(kFull, rank >= incl - pc && rank < incl);
+                const int src = __ffs(has) - 1;
+                const u32 swd = __shfl_sync(kFull, wd, src);
+                const int before = __shfl_sync(kFull, incl - pc, src);
+                chosen = (jb + src) * 32 + (int)__fns(swd, 0, rank - before + 1);
+                break;
+            }
+            rank -= total;
+        }
+    }
+    const bool clause_true = chosen != -1;
+
+    // 2. feedback type per class + weight move
+    int upd_lo = 0;
+    for (int kb = 0; kb < m.K; kb += 16) {
+        const int kn = min(16, m.K - kb);
+        const float uni = to_uniform(draw_at(m, c, pos + lane));     // only the first (at most 2*kn) are consumed
+        int wgt = 0, sign = 1;
+        if (lane < kn) {
+            wgt = cv.wgt[(size_t)(kb + lane) * cv.wstride];
+            sign = (wgt >= 0) - (wgt < 0);
+        }
+        int used = 0;
+        for (int kk = 0; kk < kn; ++kk) {
+            const int t = s_target[kb + kk];
+            bool skip = false;
+            if (t == -1) skip = __shfl_sync(kFull, uni, used++) > m.q_keep_f;
+            if (!skip) skip = __shfl_sync(kFull, uni, used++) > s_thr[kb + kk];
+            const int upd = skip ? 0 : t * __shfl_sync(kFull, sign, kk);
+            if (lane == kk) {
+                if (upd > 0 && clause_true && abs(wgt) < INT_MAX) wgt += sign;
+                else if (upd < 0 && clause_true) wgt -= sign;
+                a.update[(size_t)(kb + kk) * m.C + c] = upd;
+                if (upd != 0 && clause_true) cv.wgt[(size_t)(kb + kk) * cv.wstride] = wgt;
+            }
+            if (kb + kk < 32 && lane == kb + kk) upd_lo = upd;
+        }
+        pos += used;
+    }
+    if (m.K > 32) __syncwarp();   // classes beyond 31 are read back from a.update
+
+    // 3./4. automata of every layer
+    const bool within = n_inc <= m.max_included;
+    const int node = clause_true ? chosen : 0;
+#pragma unroll 1
+    for (int d = 0; d < m.D; ++d) {
+        const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * a.max_nodes + node) * m.MW;
+        pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), upd_lo, a.update, clause_true, within, row, d > 0, pos, lane, pack);
+    }
+    if (lane == 0) {
+        *cv.pos = pos;
+        a.clause_node[c] = chosen;
+    }
+}
+
+// Message rows of the OTHER parity are cleared for the graph after this one: every warp has finished the previous
+// graph (the last reader), and the next writer comes after the remaining synchronisations of this graph.
+__device__ __forceinline__ void clear_next_messages(const DevModel &m, const DevGraphs &g, const FitArgs &a, int par,
+                                                    int64_t i, int64_t e)
+{
+    const size_t gthread = blockIdx.x * (size_t)blockDim.x + threadIdx.x, gthreads = (size_t)gridDim.x * blockDim.x;
+    const int64_t nxt = i + 1 < a.count ? e + 1 : a.first;
+    const size_t rows = (size_t)g.n_nodes[nxt] * m.MW;
+    for (int dd = 0; dd < m.D - 1; ++dd)
+        for (size_t t = gthread; t < rows; t += gthreads) a.P_pair[par ^ 1][(size_t)dd * a.max_nodes * m.MW + t] = 0;
+}
+
+#define GTM_LAP(acc) do { if (timer) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)
+
+}  // namespace gtm

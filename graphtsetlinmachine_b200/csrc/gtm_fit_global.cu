@@ -1,0 +1,90 @@
+// Learning kernel with the model state in global memory (any model size; also the debug path).
+#include "../../include/gtm_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "gtm_handles.h"
+#include "gtm_fit.cuh"
+
+namespace gtm {
+
+// Persistent learning kernel, state in global memory: the whole grid works on one graph at a time (online
+// learning is sequential over graphs, tm.py:668-747); warps own clauses (clause c belongs to global warp c mod
+// #warps for the whole launch, so automata and weights of a clause are only ever touched by one warp).  Per
+// graph: layer evaluations separated by grid barriers (messages mix all clauses), one exchange of per-CTA vote
+// partials, then clause-local feedback.  Serves any model size; also the debug path that keeps every layer.
+template <int MAXSB>
+__global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, EvalScratch sc, FitArgs a, int eval_only)
+{
+    extern __shared__ int s_mem[];   // [K] running partial, [K] totals, [K] targets, [K] thresholds
+    int *s_sum = s_mem, *s_total = s_mem + m.K, *s_target = s_mem + 2 * m.K;
+    float *s_thr = reinterpret_cast<float *>(s_mem + 3 * m.K);
+    __shared__ u32 s_pack[16][kPackWords];
+    const int lane = threadIdx.x & 31;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const size_t layer_words = (size_t)a.max_nodes * m.MW;
+    unsigned arrivals = 0;
+
+    for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
+    __syncthreads();
+    const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
+    long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t0 = clock64(), t1;
+
+    u64 step = 0;
+    for (int ep = 0; ep < a.epochs; ++ep) {
+        for (int64_t i = 0; i < a.count; ++i, ++step) {
+            const int64_t e = a.first + i;
+            const int par = (int)(step & 1);
+            const GraphView gv = global_graph(g, e, m.L0);
+            u32 *P = a.P_pair[par];
+
+            for (int d = 0; d < m.D; ++d) {
+                const bool last = d == m.D - 1;
+                if (d > 0) {
+                    GTM_LAP(t_eval);
+                    arrivals += gridDim.x;
+                    if (!grid_barrier(a.barrier, arrivals, a.error)) return;
+                    GTM_LAP(t_bar);
+                    if (d == 1) clear_next_messages(m, g, a, par, i, e);
+                }
+                for (int c = gwarp; c < m.C; c += nwarps) {
+                    const ClauseView cv = global_view(m, sc.n_inc, c);
+                    const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                                                      cno_row(sc, m.C, d, c), d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
+                                                      last ? nullptr : P + (size_t)d * layer_words, lane);
+                    if (last && any)
+                        for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], m.weights[(size_t)k * m.C + c]);
+                }
+            }
+            __syncthreads();
+            GTM_LAP(t_eval);
+            if (!exchange_class_sums(a.exchange, par, (u32)step + 1u, s_sum, s_total, m.K, a.error, a.class_sum_tap)) return;
+            GTM_LAP(t_tot);
+            if (!eval_only) {
+                class_decision_inputs(m, s_total, a.Y + (size_t)e * m.K, s_target, s_thr);
+                __syncthreads();
+                for (int c = gwarp; c < m.C; c += nwarps) {
+                    const ClauseView cv = global_view(m, sc.n_inc, c);
+                    clause_feedback<MAXSB>(m, gv, cv, a, cno_row(sc, m.C, m.D - 1, c), P, s_target, s_thr, c, lane,
+                                           s_pack[threadIdx.x >> 5]);
+                }
+            }
+            __syncthreads();   // s_total is rewritten by the next graph
+            GTM_LAP(t_fb);
+        }
+    }
+    if (timer) {
+        a.phase_cycles[0] = (unsigned long long)t_eval; a.phase_cycles[1] = (unsigned long long)t_bar;
+        a.phase_cycles[2] = (unsigned long long)t_tot; a.phase_cycles[3] = (unsigned long long)t_fb;
+    }
+}
+
+#undef GTM_LAP
+
+}  // namespace gtm
+
+const void *fit_global_kernel(int state_bits) { return state_bits <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>; }

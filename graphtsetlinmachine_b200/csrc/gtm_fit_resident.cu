@@ -1,0 +1,300 @@
+// State-resident learning kernel and the launch logic of both learning kernels.
+#include "../../include/gtm_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "gtm_handles.h"
+#include "gtm_fit.cuh"
+
+const void *fit_global_kernel(int state_bits);   // gtm_fit_global.cu
+
+namespace gtm {
+
+// Staging limits of the state-resident kernel: a graph is copied to shared memory one step ahead when it has at
+// most kStageNodes nodes, kStageRowWords literal words and kStageEdges edge rows; larger graphs are read in place.
+constexpr int kStageNodes = 256, kStageRowWords = 1536, kStageEdges = 512;
+constexpr int kStageWords = kStageRowWords + 3 * kStageNodes + 2 * kStageEdges;
+
+__device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global_src)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global_src) : "memory");
+}
+
+// State-resident learning kernel.  Same schedule as fit_kernel, but everything a clause owns lives in the shared
+// memory of the CTA that owns the clause for the whole launch: automaton planes of every layer, weights, message
+// hypervector, draw counter, include count and the node-output words.  The graph of the NEXT step (rows, node
+// types, CSR slice, targets) is copied into shared memory with cp.async while the current step runs, and the
+// sizes of the step after that are fetched too, so that no step starts with a chain of dependent global loads.
+// Per graph the remaining global traffic is the vote exchange and, for depth > 1, the message rows.
+// State is loaded at the start of the launch and written back at its end.
+//   shared memory: [K] vote partial | [K] totals | [2][K] targets | [3][4] graph sizes | [2] staged graphs |
+//                  per owned clause: clause_words words =
+//                  draw counter (2) | include count (1) | pad (1) | weights [K] | hypervector [MB] | node words [2][NC] | planes
+template <int MAXSB>
+__global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGraphs g, FitArgs a)
+{
+    extern __shared__ __align__(16) int s_mem[];
+    const int KP = (m.K + 3) & ~3;
+    int *s_sum = s_mem, *s_total = s_mem + KP, *s_y = s_mem + 2 * KP;      // s_y: [2][KP]
+    int *s_target = s_mem + 4 * KP;
+    float *s_thr = reinterpret_cast<float *>(s_mem + 5 * KP);
+    int *s_size = s_mem + 6 * KP;                                           // [3][4]: n, first node, first edge row, edge rows
+    u32 *s_stage = reinterpret_cast<u32 *>(s_size + 12);                    // [2][kStageWords]
+    u32 *s_pack = s_stage + 2 * kStageWords;                                // [12][kPackWords]
+    u32 *s_clauses = s_pack + 12 * kPackWords;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int c_lo = blockIdx.x * a.clauses_per_cta, c_hi = min(m.C, c_lo + a.clauses_per_cta);
+    const size_t layer_words = (size_t)a.max_nodes * m.MW;
+    const int NC = a.NC;
+    const u64 steps = (u64)a.epochs * (u64)a.count;
+    unsigned arrivals = 0;
+
+    auto view_of = [&](int c) {
+        u32 *basep = s_clauses + (size_t)(c - c_lo) * a.clause_words;
+        ClauseView cv;
+        cv.pos = reinterpret_cast<u64 *>(basep);
+        cv.n_inc = reinterpret_cast<int *>(basep + 2);
+        cv.wgt = reinterpret_cast<int *>(basep + 4);
+        cv.wstride = 1;
+        cv.hv = basep + 4 + m.K;
+        cv.ta0 = basep + 4 + m.K + m.MB + 2 * NC;
+        cv.tam = cv.ta0 + (size_t)m.SB * m.L0;
+        cv.tam_stride = (size_t)m.SB * m.M;
+        return cv;
+    };
+    auto node_words = [&](int c, int d) { return s_clauses + (size_t)(c - c_lo) * a.clause_words + 4 + m.K + m.MB + (d & 1) * NC; };
+    // graphs of the current step and of the two steps after it (wrapping at the end of every epoch)
+    int64_t e_cur = a.first, e_nxt = a.count > 1 ? a.first + 1 : a.first;
+    int64_t e_nxt2 = a.count > 2 ? a.first + 2 : (a.count == 2 ? a.first : a.first);
+    auto advance = [&](int64_t e) { return e + 1 < a.first + a.count ? e + 1 : a.first; };
+    auto fits = [&](const int *sz) { return sz[0] <= kStageNodes && sz[0] * m.L0 <= kStageRowWords && sz[3] <= kStageEdges; };
+    // sizes of the graph of step st -> s_size[st % 3]   (four independent loads)
+    auto fetch_sizes = [&](u64 st, int64_t e) {
+        if (threadIdx.x < 4 && st < steps) {
+            const u32 *src = threadIdx.x == 0 ? g.n_nodes : threadIdx.x == 1 ? g.node_index : threadIdx.x == 2 ? g.graph_edge0 : g.graph_edges;
+            async_copy_word(reinterpret_cast<u32 *>(s_size + (int)((u32)st % 3u) * 4 + threadIdx.x), src + e);
+        }
+    };
+    // graph of step st (sizes already in s_size[st % 3]) -> s_stage[st & 1], targets -> s_y[st & 1]
+    auto fetch_graph = [&](u64 st, int64_t e) {
+        if (st >= steps) return;
+        for (int k = threadIdx.x; k < m.K; k += blockDim.x)
+            async_copy_word(reinterpret_cast<u32 *>(s_y + (st & 1) * KP + k), reinterpret_cast<const u32 *>(a.Y + (size_t)e * m.K + k));
+        const int *sz = s_size + (int)((u32)st % 3u) * 4;
+        if (!fits(sz)) return;
+        const int n = sz[0], base = sz[1], e0 = sz[2], ne = sz[3];
+        u32 *st_x = s_stage + (st & 1) * kStageWords, *st_t = st_x + kStageRowWords, *st_d = st_t + kStageNodes,
+            *st_i = st_d + kStageNodes, *st_e = st_i + kStageNodes;
+        for (int t = threadIdx.x; t < n * m.L0; t += blockDim.x) async_copy_word(st_x + t, g.X + (size_t)base * m.L0 + t);
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            async_copy_word(st_t + t, g.node_type + base + t);
+            async_copy_word(st_d + t, g.degree + base + t);
+            async_copy_word(st_i + t, g.edge_index + base + t);
+        }
+        for (int t = threadIdx.x; t < 2 * ne; t += blockDim.x) async_copy_word(st_e + t, g.edge + 2 * (size_t)e0 + t);
+    };
+    auto wait_copies = [&]() { asm volatile("cp.async.wait_all;" ::: "memory"); };
+
+    // ---- state in ----
+    for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+        ClauseView cv = view_of(c);
+        if (lane == 0) { *cv.pos = m.draw_pos[c]; *cv.n_inc = 0; }
+        for (int k = lane; k < m.K; k += 32) cv.wgt[k] = m.weights[(size_t)k * m.C + c];
+        for (int b = lane; b < m.MB; b += 32) const_cast<u32 *>(cv.hv)[b] = m.hv[(size_t)c * m.MB + b];
+        for (int l = 0; l < m.D; ++l) {
+            const int total = m.SB * (l == 0 ? m.L0 : m.M);
+            const u32 *src = l == 0 ? m.ta0 + (size_t)c * total : m.tam + ((size_t)(l - 1) * m.C + c) * total;
+            u32 *dst = cv.ta(l);
+            for (int t = lane; t < total; t += 32) dst[t] = src[t];
+        }
+    }
+    for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
+    fetch_sizes(0, e_cur);
+    fetch_sizes(1, e_nxt);
+    wait_copies();
+    __syncthreads();
+    fetch_graph(0, e_cur);
+    wait_copies();
+    __syncthreads();
+    const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
+    long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t_x0 = 0, t_x1 = 0, t_x2 = 0, t_x3 = 0, t0 = clock64(), t1;
+
+    int slot3 = 0;   // step % 3
+    for (u64 step = 0; step < steps; ++step) {
+        const int64_t e = e_cur;
+        const int64_t i = e - a.first;
+        const int par = (int)(step & 1);
+        const int *sz = s_size + slot3 * 4;
+        GraphView gv;
+        gv.n = sz[0];
+        if (fits(sz)) {
+            const u32 *st_x = s_stage + par * kStageWords;
+            gv.X = st_x; gv.type = st_x + kStageRowWords; gv.degree = gv.type + kStageNodes; gv.eidx = gv.degree + kStageNodes;
+            gv.edge = gv.eidx + kStageNodes; gv.e_off = (u32)sz[2];
+        } else {
+            const int base = sz[1];
+            gv.X = g.X + (size_t)base * m.L0; gv.type = g.node_type + base; gv.degree = g.degree + base;
+            gv.eidx = g.edge_index + base; gv.edge = g.edge; gv.e_off = 0;
+        }
+        u32 *P = a.P_pair[par];
+        const int *y = s_y + par * KP;
+        GTM_LAP(t_x0);
+        fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
+        fetch_sizes(step + 2, e_nxt2);
+        GTM_LAP(t_x1);
+
+        for (int d = 0; d < m.D; ++d) {
+            const bool last = d == m.D - 1;
+            if (d > 0) {
+                GTM_LAP(t_eval);
+                arrivals += gridDim.x;
+                if (!grid_barrier(a.barrier, arrivals, a.error)) return;
+                GTM_LAP(t_bar);
+                if (d == 1) clear_next_messages(m, g, a, par, i, e);
+            }
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
+                                                  d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
+                                                  last ? nullptr : P + (size_t)d * layer_words, lane);
+                if (last && any)
+                    for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
+            }
+        }
+        GTM_LAP(t_x2);
+        __syncthreads();
+        GTM_LAP(t_eval);
+        if (!exchange_class_sums(a.exchange, par, (u32)step + 1u, s_sum, s_total, m.K, a.error, a.class_sum_tap)) return;
+        GTM_LAP(t_tot);
+        class_decision_inputs(m, s_total, y, s_target, s_thr);
+        __syncthreads();
+        for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+            const ClauseView cv = view_of(c);
+            clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords);
+        }
+        GTM_LAP(t_x3);
+        wait_copies();
+        __syncthreads();   // next step's graph is complete; s_total and this step's stage buffer may be reused
+        GTM_LAP(t_fb);
+        e_cur = e_nxt; e_nxt = e_nxt2; e_nxt2 = advance(e_nxt2);
+        slot3 = slot3 == 2 ? 0 : slot3 + 1;
+    }
+
+    // ---- state out ----
+    for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+        ClauseView cv = view_of(c);
+        if (lane == 0) m.draw_pos[c] = *cv.pos;
+        for (int k = lane; k < m.K; k += 32) m.weights[(size_t)k * m.C + c] = cv.wgt[k];
+        for (int l = 0; l < m.D; ++l) {
+            const int total = m.SB * (l == 0 ? m.L0 : m.M);
+            u32 *dst = l == 0 ? m.ta0 + (size_t)c * total : m.tam + ((size_t)(l - 1) * m.C + c) * total;
+            const u32 *src = cv.ta(l);
+            for (int t = lane; t < total; t += 32) dst[t] = src[t];
+        }
+    }
+    if (timer) {
+        a.phase_cycles[0] = (unsigned long long)t_eval; a.phase_cycles[1] = (unsigned long long)t_bar;
+        a.phase_cycles[2] = (unsigned long long)t_tot; a.phase_cycles[3] = (unsigned long long)t_fb;
+        a.phase_cycles[4] = (unsigned long long)t_x0; a.phase_cycles[5] = (unsigned long long)t_x1;
+        a.phase_cycles[6] = (unsigned long long)t_x2; a.phase_cycles[7] = (unsigned long long)t_x3;
+    }
+}
+#undef GTM_LAP
+
+}  // namespace gtm
+
+
+int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *grid_out)
+{
+    int per_sm = 0;
+    const size_t smem = 4 * (size_t)d.K * sizeof(int);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_global_kernel(d.SB), block, smem);
+    if (e != cudaSuccess || per_sm < 1)
+        return fail(GTM_ERR_CUDA, "learning kernel does not fit on this device: %s", cudaGetErrorString(e));
+    const int warps_per_cta = block / 32;
+    *grid_out = std::max(1, std::min(sm_count * std::min(per_sm, 2), (d.C + warps_per_cta - 1) / warps_per_cta));
+    return GTM_OK;
+}
+
+static int words_for(int bits) { return (bits - 1) / 32 + 1; }
+
+constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
+
+// Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0; size_t smem = 0; };
+
+static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
+{
+    const DevModel &d = m->dm;
+    ResidentPlan plan;
+    const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+    const int warps = kResidentThreads / 32;
+    int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
+    words = (words + 3) & ~3;
+    for (int per_sm = 2; per_sm >= 1; --per_sm) {
+        int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
+        const int cpb = (d.C + grid - 1) / grid;
+        grid = (d.C + cpb - 1) / cpb;
+        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) + (size_t)cpb * words * sizeof(u32);
+        if (smem > 200 * 1024) continue;
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
+        if ((long long)occ * m->sm_count < grid) continue;
+        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.smem = smem;
+        return plan;
+    }
+    return plan;
+}
+
+int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
+                      int epochs, int eval_only)
+{
+    const DevModel &d = m->dm;
+    DevGraphs g = ds->dg;
+    g.n_types = n_types;
+    EvalScratch sc = ds->fit_sc;
+    FitArgs a;
+    memset(&a, 0, sizeof a);
+    a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
+    a.exchange = m->exchange; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
+    a.max_nodes = ds->max_nodes;
+    a.barrier = m->barrier; a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
+    a.class_sum_tap = m->class_sum_tap;
+    a.phase_cycles = m->phase_cycles;
+    a.NC = ds->NC;
+    const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
+    GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
+    GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
+    GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
+    if (d.D > 1) {
+        GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
+        GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
+    }
+    DevModel dm = d;
+    ResidentPlan plan;
+    if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds);
+    if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
+        return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
+    if (plan.grid > 0) {
+        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words;
+        void *args[] = {&dm, &g, &a};
+        const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(plan.grid), dim3(kResidentThreads), args, plan.smem, m->stream));
+    } else {
+        void *args[] = {&dm, &g, &sc, &a, &eval_only};
+        const size_t smem = 4 * (size_t)d.K * sizeof(int);
+        const void *fn = fit_global_kernel(d.SB);
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
+    }
+    int err = 0;
+    GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    if (err) return fail(GTM_ERR_TIMEOUT, "a bounded wait of the learning kernel (grid barrier or vote exchange) gave up");
+    return GTM_OK;
+}
+

@@ -1,0 +1,55 @@
+// Handle types behind the opaque pointers of the C ABI; shared by the translation units of the library.
+#pragma once
+#include <vector>
+
+#include "gtm_device.cuh"
+#include "gtm_host.cuh"
+#include "gtm_stream.h"
+
+using namespace gtm;
+
+// ---------------------------------------------------------------------------------------------- handles
+struct gtm_model {
+    gtm_config cfg;
+    DevModel dm;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    bool has_state = false;
+    u32 *recorded = nullptr;
+    // learning-kernel buffers
+    int fit_grid = 0, fit_block = 512;
+    int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
+    unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
+    int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
+    int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel
+    unsigned *barrier = nullptr;
+    unsigned long long *phase_cycles = nullptr;
+    // node-stream scoring: derived include lists (rebuilt when the automata changed)
+    StreamModel sm;
+    bool lists_dirty = true;
+};
+
+struct gtm_dataset {
+    gtm_model *model;
+    DevGraphs dg;
+    int64_t n_graphs, total_nodes, total_edges;
+    int max_nodes, NC;
+    std::vector<void *> owned;
+    // learning scratch (every layer kept) and its message ping-pong
+    EvalScratch fit_sc;
+    u32 *P_pair[2] = {nullptr, nullptr};
+    // scoring scratch of the general path: one slice per CTA
+    EvalScratch score_sc;
+    size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
+    int score_grid = 0;
+    int *Y = nullptr;
+    size_t Y_capacity = 0;
+    // node-stream scoring
+    StreamData sd;
+};
+
+
+// learning kernels (gtm_fit.cu)
+int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *grid_out);
+int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count, int epochs,
+               int eval_only);

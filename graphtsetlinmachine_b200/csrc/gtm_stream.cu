@@ -8,43 +8,33 @@
 // test, and an empty clause costs nothing (and is true, as in kernels.py:443-460).  Included literals come
 // from per-clause lists rebuilt from the include planes whenever the automata changed.
 //
-// Votes.  Clauses are processed in blocks of CB; their node bits go to shared memory R[CB][TNC]; then one
-// thread per graph ORs the bits of its node segment and accumulates the block's weights into registers
-// (kernels.py:279-317, batched).  Class sums leave the CTA once per graph, unclamped.
+// A thread evaluates one clause on FOUR node words at a time (one 128-bit shared load per literal), and the
+// literal lists hold byte offsets of the rows (literal * TNC * 4), so a literal costs a shift/mask, an add, a load
+// and two 3-input ANDs for 128 nodes.
 //
-// Derived model data (StreamModel): literal lists (uint16 ids, padded to a multiple of 4 with the id of an
-// all-ones row) and weights transposed to [clause][KROW].
-#pragma once
+// Votes.  Clauses are processed in blocks of CB = 128.  Their node bits R[clause][node word] are transposed in
+// registers (32x32 bit-matrix butterflies, one per thread) into RT[clause word][node] = the 32 clause outcomes of a
+// node, and then one thread per graph ORs the words of its nodes and walks only the SET bits, adding the weight
+// rows of the clauses that fired (kernels.py:279-317, batched).  Work is proportional to the clauses that fire
+// instead of to all clauses.  Class sums stay in registers and leave the CTA once per graph, unclamped.
+//
+// Derived model data (StreamModel): literal lists (uint16 row offsets, padded to a multiple of 4 with the offset
+// of an all-ones row) and weights transposed to [clause][KROW].
+#include "../../include/gtm_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <climits>
 #include <vector>
 
-#include "gtm_device.cuh"
-#include "gtm_host.cuh"
+#include "gtm_stream.h"
 
 namespace gtm {
 
 constexpr int kStreamThreads = 512;
-constexpr int kStreamCB = 256;          // clauses per vote block
+constexpr int kStreamCB = 128;          // clauses per vote block
 constexpr int kStreamMaxK = 16;
-
-struct StreamModel {
-    int *lit_off = nullptr;             // [C+1] offsets into lit_list (multiples of 4)
-    int *lit_cnt = nullptr;             // [C]   padded counts (scratch of the scan)
-    unsigned short *lit_list = nullptr; // padded literal ids
-    int *Wt = nullptr;                  // [C][KROW]
-    int KROW = 0;
-};
-
-struct StreamData {
-    int supported = 0;
-    int TNC = 0;                        // node words per tile
-    int n_tiles = 0;
-    int *tile_graph = nullptr;          // [n_tiles+1] first graph of every tile
-    std::vector<int> tile_graph_host;
-    int grid = 0;
-    size_t smem = 0;
-    unsigned *tile_counter = nullptr;
-    int64_t total_nodes = 0, n_graphs = 0;
-};
 
 // ------------------------------------------------------------------------------------------- list building
 __global__ void stream_count_kernel(DevModel m, int *cnt)
@@ -76,7 +66,7 @@ __global__ void stream_scan_kernel(const int *cnt, int *off, int C)
     for (int i = lo; i < hi; ++i) { off[i] = run; run += cnt[i]; }
 }
 
-__global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *list, int *Wt, int KROW)
+__global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *list, int *Wt, int KROW, int TNC)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= m.C) return;
@@ -87,10 +77,10 @@ __global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *l
         while (bits) {
             const int b = __ffs(bits) - 1;
             bits &= bits - 1;
-            list[at++] = (unsigned short)(w * 32 + b);
+            list[at++] = (unsigned short)((w * 32 + b) * TNC * 4);
         }
     }
-    while (at < off[c + 1]) list[at++] = (unsigned short)m.literals;   // sentinel: the all-ones row
+    while (at < off[c + 1]) list[at++] = (unsigned short)(m.literals * TNC * 4);   // sentinel: the all-ones row
     for (int k = 0; k < KROW; ++k) Wt[(size_t)c * KROW + k] = k < m.K ? m.weights[(size_t)k * m.C + c] : 0;
 }
 
@@ -109,18 +99,45 @@ struct StreamArgs {
     int KROW;
 };
 
+__device__ __forceinline__ uint4 lds128(unsigned addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.
+__device__ __forceinline__ void transpose32(u32 (&a)[32])
+{
+    u32 mask = 0x0000ffffu;
+#pragma unroll
+    for (int j = 16; j != 0; j >>= 1, mask ^= mask << j) {
+#pragma unroll
+        for (int k = 0; k < 32; k = (k + j + 1) & ~j) {
+            const u32 t = ((a[k] >> j) ^ a[k + j]) & mask;
+            a[k] ^= t << j;
+            a[k + j] ^= t;
+        }
+    }
+}
+
+constexpr int kRTStride = 33;   // RT[cw][b * 33 + j] holds node 32j+b: conflict-free both for the writer (lanes = j) and the reader (lanes = b)
+
 template <int KP>
 __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevModel m, DevGraphs g, StreamArgs a)
 {
-    extern __shared__ u32 s_dyn[];
-    const int TNC = a.TNC;
+    extern __shared__ __align__(16) u32 s_dyn[];
+    constexpr int CW = kStreamCB / 32;                 // clause words per block
+    const int TNC = a.TNC, Q = TNC >> 2;               // node words per tile, 4-word groups
     u32 *XT = s_dyn;                                   // [literals+1][TNC]
     u32 *TMV = XT + (size_t)(m.literals + 1) * TNC;    // [n_types][TNC] valid & node type
-    u32 *R = TMV + (size_t)g.n_types * TNC;            // [CB][TNC]
-    int *Wb = (int *)(R + (size_t)kStreamCB * TNC);    // [CB][KROW]
+    u32 *R = TMV + (size_t)g.n_types * TNC;            // [CB][TNC]        node bits per clause
+    u32 *RT = R + (size_t)kStreamCB * TNC;             // [CW][32*33]      clause bits per node
+    int *Wb = (int *)(RT + (size_t)CW * 32 * kRTStride);   // [CB][KROW]
     __shared__ int s_tile;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kStreamThreads / 32;
     const int KROW = a.KROW;
+    const unsigned xt32 = (unsigned)__cvta_generic_to_shared(XT);
 
     while (true) {
         if (tid == 0) s_tile = a.tile_lo + (int)atomicAdd(a.tile_counter, 1u);
@@ -152,15 +169,13 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
             if (lane == 0) TMV[tj] = col;
         }
 
-        // ---- per-graph accumulators (graphs tid, tid+512, ... of the tile) ----
+        // ---- per-graph state: graphs tid and tid+512 of the tile ----
         int acc[2][KP];
-#pragma unroll
-        for (int s = 0; s < 2; ++s)
-#pragma unroll
-            for (int k = 0; k < KP; ++k) acc[s][k] = 0;
         int seg_lo[2], seg_hi[2];
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+#pragma unroll
+            for (int k = 0; k < KP; ++k) acc[s][k] = 0;
             const int gi = g0 + tid + s * kStreamThreads;
             if (gi < g1) {
                 seg_lo[s] = (int)g.node_index[gi] - node0;
@@ -173,44 +188,62 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
 
         for (int cb0 = 0; cb0 < m.C; cb0 += kStreamCB) {
             const int cbn = min(kStreamCB, m.C - cb0);
-            // ---- evaluation: (clause, node word) pairs over lanes; AND the transposed rows of the included literals ----
-            for (int idx = tid; idx < cbn * TNC; idx += kStreamThreads) {
-                const int cb = idx / TNC, j = idx - cb * TNC;
-                const int c = cb0 + cb;
-                u32 r = TMV[(c % g.n_types) * TNC + j];
-                const int o0 = a.lit_off[c], o1 = a.lit_off[c + 1];
-                const uint2 *lp = reinterpret_cast<const uint2 *>(a.lit_list + o0);
-                for (int q = 0; q < (o1 - o0) >> 2; ++q) {
-                    const uint2 four = lp[q];
-                    r &= XT[(size_t)(four.x & 0xffffu) * TNC + j];
-                    r &= XT[(size_t)(four.x >> 16) * TNC + j];
-                    r &= XT[(size_t)(four.y & 0xffffu) * TNC + j];
-                    r &= XT[(size_t)(four.y >> 16) * TNC + j];
+            // ---- evaluation: (clause, 4 node words) per thread; AND the transposed rows of the included literals ----
+            for (int idx = tid; idx < kStreamCB * Q; idx += kStreamThreads) {
+                const int cb = idx / Q, quad = idx - cb * Q;
+                uint4 r = make_uint4(0u, 0u, 0u, 0u);              // rows past the last clause stay empty
+                if (cb < cbn) {
+                    const int c = cb0 + cb;
+                    const unsigned xq = xt32 + quad * 16;
+                    r = *reinterpret_cast<const uint4 *>(TMV + (c % g.n_types) * TNC + quad * 4);
+                    const int o0 = a.lit_off[c], o1 = a.lit_off[c + 1];
+                    const uint2 *lp = reinterpret_cast<const uint2 *>(a.lit_list + o0);
+                    const int groups = (o1 - o0) >> 2;
+#pragma unroll 2
+                    for (int q = 0; q < groups; ++q) {
+                        const uint2 four = __ldg(lp + q);
+                        const uint4 x0 = lds128(xq + (four.x & 0xffffu));
+                        const uint4 x1 = lds128(xq + (four.x >> 16));
+                        const uint4 x2 = lds128(xq + (four.y & 0xffffu));
+                        const uint4 x3 = lds128(xq + (four.y >> 16));
+                        r.x &= x0.x & x1.x; r.y &= x0.y & x1.y; r.z &= x0.z & x1.z; r.w &= x0.w & x1.w;
+                        r.x &= x2.x & x3.x; r.y &= x2.y & x3.y; r.z &= x2.z & x3.z; r.w &= x2.w & x3.w;
+                    }
                 }
-                R[idx] = r;
+                *reinterpret_cast<uint4 *>(R + (size_t)cb * TNC + quad * 4) = r;
             }
             for (int i = tid; i < cbn * KROW; i += kStreamThreads) Wb[i] = a.Wt[(size_t)cb0 * KROW + i];
             __syncthreads();
-            // ---- votes: one thread per graph, OR over its node segment, weights from shared memory ----
+            // ---- 32 clauses x 32 nodes blocks of R, transposed in registers: warp = clause word, lane = node word ----
+            for (int blk = tid; blk < CW * TNC; blk += kStreamThreads) {
+                const int cw = blk / TNC, j = blk - cw * TNC;
+                u32 rows[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rows[i] = R[(size_t)(32 * cw + i) * TNC + j];
+                transpose32(rows);
+#pragma unroll
+                for (int b = 0; b < 32; ++b) RT[(size_t)cw * 32 * kRTStride + b * kRTStride + j] = rows[b];
+            }
+            __syncthreads();
+            // ---- votes: one thread per graph; OR of its nodes' clause words, then only the clauses that fired ----
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
-                if (seg_hi[s] > seg_lo[s]) {
-                    const int wlo = seg_lo[s] >> 5, whi = (seg_hi[s] - 1) >> 5;
-                    const u32 mlo = kFull << (seg_lo[s] & 31);
-                    const u32 mhi = kFull >> (31 - ((seg_hi[s] - 1) & 31));
-                    for (int cb = 0; cb < cbn; ++cb) {
-                        const u32 *row = R + (size_t)cb * TNC;
-                        u32 any;
-                        if (wlo == whi) {
-                            any = row[wlo] & mlo & mhi;
-                        } else {
-                            any = (row[wlo] & mlo) | (row[whi] & mhi);
-                            for (int w = wlo + 1; w < whi; ++w) any |= row[w];
-                        }
-                        if (any) {
-                            const int *wr = Wb + (size_t)cb * KROW;
+                if (seg_hi[s] <= seg_lo[s]) continue;
+                for (int cw = 0; cw < CW; ++cw) {
+                    const u32 *rt = RT + (size_t)cw * 32 * kRTStride;
+                    u32 fired = 0;
+                    for (int v = seg_lo[s]; v < seg_hi[s]; ++v) fired |= rt[(v & 31) * kRTStride + (v >> 5)];
+                    while (fired) {
+                        const int cb = 32 * cw + __ffs(fired) - 1;
+                        fired &= fired - 1;
+                        const int4 *wr = reinterpret_cast<const int4 *>(Wb + (size_t)cb * KROW);
 #pragma unroll
-                            for (int k = 0; k < KP; ++k) acc[s][k] += wr[k];
+                        for (int k4 = 0; k4 < (KP + 3) / 4; ++k4) {
+                            const int4 t = wr[k4];
+                            acc[s][4 * k4] += t.x;
+                            if (4 * k4 + 1 < KP) acc[s][4 * k4 + 1] += t.y;
+                            if (4 * k4 + 2 < KP) acc[s][4 * k4 + 2] += t.z;
+                            if (4 * k4 + 3 < KP) acc[s][4 * k4 + 3] += t.w;
                         }
                     }
                 }
@@ -236,10 +269,20 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
 // ------------------------------------------------------------------------------------------------ host side
 inline int stream_krow(int K) { return (K + 3) & ~3; }
 
-inline int stream_model_create(StreamModel *sm, const DevModel &d)
+// node words per tile: as many as keep the transposed literals within 64 KB (so that row offsets fit 16 bits),
+// at most 2*threads/32 (two graphs per thread), at least 4 (a thread evaluates 4 words at a time)
+inline int stream_tile_words(int literals)
 {
-    if (d.D != 1 || d.K > kStreamMaxK || d.literals >= 65535) return GTM_OK;   // path not applicable
+    int TNC = 2 * kStreamThreads / 32;
+    while (TNC > 4 && (size_t)(literals + 1) * TNC * sizeof(u32) > 64 * 1024) TNC >>= 1;
+    return (size_t)(literals + 1) * TNC * sizeof(u32) <= 64 * 1024 ? TNC : 0;
+}
+
+int stream_model_create(StreamModel *sm, const DevModel &d)
+{
+    if (d.D != 1 || d.K > kStreamMaxK || stream_tile_words(d.literals) == 0) return GTM_OK;   // path not applicable
     sm->KROW = stream_krow(d.K);
+    sm->TNC = stream_tile_words(d.literals);
     GTM_TRY(dev_alloc(&sm->lit_off, (size_t)d.C + 1));
     GTM_TRY(dev_alloc(&sm->lit_cnt, (size_t)d.C));
     GTM_TRY(dev_alloc(&sm->lit_list, (size_t)d.C * ((d.literals + 3) & ~3) + 4));
@@ -247,19 +290,19 @@ inline int stream_model_create(StreamModel *sm, const DevModel &d)
     return GTM_OK;
 }
 
-inline void stream_model_destroy(StreamModel *sm)
+void stream_model_destroy(StreamModel *sm)
 {
     cudaFree(sm->lit_off); cudaFree(sm->lit_cnt); cudaFree(sm->lit_list); cudaFree(sm->Wt);
     *sm = StreamModel();
 }
 
-inline int stream_model_refresh(StreamModel *sm, const DevModel &d, cudaStream_t s)
+int stream_model_refresh(StreamModel *sm, const DevModel &d, cudaStream_t s)
 {
     if (!sm->lit_off) return GTM_OK;
     const int blocks = (d.C + 255) / 256;
     stream_count_kernel<<<blocks, 256, 0, s>>>(d, sm->lit_cnt);
     stream_scan_kernel<<<1, 1024, 0, s>>>(sm->lit_cnt, sm->lit_off, d.C);
-    stream_fill_kernel<<<blocks, 256, 0, s>>>(d, sm->lit_off, sm->lit_list, sm->Wt, sm->KROW);
+    stream_fill_kernel<<<blocks, 256, 0, s>>>(d, sm->lit_off, sm->lit_list, sm->Wt, sm->KROW, sm->TNC);
     GTM_CU(cudaGetLastError());
     return GTM_OK;
 }
@@ -279,20 +322,18 @@ inline const void *stream_kernel_for(int K)
 
 inline size_t stream_smem_bytes(const DevModel &d, int TNC, int n_types, int KROW)
 {
-    return ((size_t)(d.literals + 1) * TNC + (size_t)n_types * TNC + (size_t)kStreamCB * TNC) * sizeof(u32) +
-           (size_t)kStreamCB * KROW * sizeof(int);
+    return ((size_t)(d.literals + 1) * TNC + (size_t)n_types * TNC + (size_t)kStreamCB * TNC +
+            (size_t)(kStreamCB / 32) * 32 * kRTStride) * sizeof(u32) + (size_t)kStreamCB * KROW * sizeof(int);
 }
 
 constexpr int kStreamMaxTypes = 8;
 
-inline int stream_data_create(StreamData *sd, const StreamModel &sm, const DevModel &d, const DevGraphs &,
+int stream_data_create(StreamData *sd, const StreamModel &sm, const DevModel &d, const DevGraphs &,
                               const gtm_graphs_view *v, int sm_count, cudaStream_t s)
 {
     sd->supported = 0;
     if (!sm.lit_off) return GTM_OK;
-    // node words per tile: as many as keep the transposed literals within ~64 KB, at most 32 (2 graphs per thread)
-    int TNC = 32;
-    while (TNC > 1 && (size_t)(d.literals + 1) * TNC * sizeof(u32) > 64 * 1024) TNC >>= 1;
+    const int TNC = sm.TNC;
     if (v->max_number_of_graph_nodes > TNC * 32) return GTM_OK;        // a graph must fit one tile
     const size_t smem = stream_smem_bytes(d, TNC, kStreamMaxTypes, sm.KROW);
     if (smem > 200 * 1024) return GTM_OK;
@@ -327,15 +368,15 @@ inline int stream_data_create(StreamData *sd, const StreamModel &sm, const DevMo
     return GTM_OK;
 }
 
-inline void stream_data_destroy(StreamData *sd)
+void stream_data_destroy(StreamData *sd)
 {
     cudaFree(sd->tile_graph); cudaFree(sd->tile_counter);
     sd->tile_graph = nullptr; sd->tile_counter = nullptr; sd->supported = 0;
 }
 
-inline bool stream_supported(const StreamData &sd, int n_types) { return sd.supported != 0 && n_types <= kStreamMaxTypes; }
+bool stream_supported(const StreamData &sd, int n_types) { return sd.supported != 0 && n_types <= kStreamMaxTypes; }
 
-inline int stream_score(const StreamModel &sm, const StreamData &sd, const DevModel &d, const DevGraphs &dg, int n_types,
+int stream_score(const StreamModel &sm, const StreamData &sd, const DevModel &d, const DevGraphs &dg, int n_types,
                         int64_t first, int64_t count, int *sums_dev, cudaStream_t s)
 {
     DevGraphs g = dg;
