@@ -90,6 +90,7 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     cudaDeviceProp prop;
     GTM_CU(cudaGetDeviceProperties(&prop, cfg->device));
     m->sm_count = prop.multiProcessorCount;
+    { int st0 = pool_prepare(cfg->device); if (st0 != GTM_OK) { delete m; return st0; } }
 
     int st = GTM_OK;
     st = dev_alloc(&d.ta0, (size_t)d.C * d.SB * d.L0);
@@ -280,7 +281,7 @@ template <class T>
 static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s)
 {
     T *p;
-    GTM_TRY(dev_alloc(&p, count));
+    GTM_TRY(pool_alloc(&p, count, s));
     ds->owned.push_back(p);
     if (count && host) GTM_CU(cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, s));
     *dev = p;
@@ -290,7 +291,7 @@ static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, c
 template <class T>
 static int scratch(gtm_dataset *ds, T **dev, size_t count)
 {
-    GTM_TRY(dev_alloc(dev, count));
+    GTM_TRY(pool_alloc(dev, count, ds->model->stream));
     ds->owned.push_back(*dev);
     return GTM_OK;
 }
@@ -306,7 +307,12 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s));
     GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s));
     GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s));
-    {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows)
+    if (v->total_edges == 0) {
+        u32 *zeros;
+        GTM_TRY(scratch(ds, &zeros, (size_t)v->number_of_graphs));
+        GTM_CU(cudaMemsetAsync(zeros, 0, (size_t)v->number_of_graphs * sizeof(u32), s));
+        ds->dg.graph_edge0 = ds->dg.graph_edges = zeros;
+    } else {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows)
         std::vector<u32> e0((size_t)v->number_of_graphs), ne((size_t)v->number_of_graphs);
         for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
             const u32 nb = v->node_index[gi], nn = v->number_of_graph_nodes[gi];
@@ -337,9 +343,7 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->P_stride = p_words;
     ds->ninc_stride = (size_t)d.C;
     ds->score_sc.NC = ds->NC; ds->score_sc.cno_slots = 2; ds->score_sc.max_nodes = ds->max_nodes;
-    GTM_TRY(scratch(ds, &ds->score_sc.cno, ds->cno_stride * ds->score_grid));
-    GTM_TRY(scratch(ds, &ds->score_sc.P, ds->P_stride * ds->score_grid));
-    GTM_TRY(scratch(ds, &ds->score_sc.n_inc, ds->ninc_stride * ds->score_grid));
+    ds->score_sc.cno = nullptr;   // allocated on first use of the general kernel (ensure_score_scratch)
 
     GTM_TRY(stream_data_create(&ds->sd, m->sm, d, ds->dg, v, m->sm_count, s));
     GTM_CU(cudaStreamSynchronize(s));
@@ -364,7 +368,6 @@ extern "C" int gtm_dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_da
     ds->n_graphs = v->number_of_graphs; ds->total_nodes = v->total_nodes; ds->total_edges = v->total_edges;
     ds->max_nodes = v->max_number_of_graph_nodes;
     ds->NC = words_for(ds->max_nodes);
-    memset(&ds->sd, 0, sizeof ds->sd);
     int st = dataset_build(m, v, ds);
     if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
     *out = ds;
@@ -376,7 +379,7 @@ extern "C" int gtm_dataset_destroy(gtm_dataset *ds)
     if (!ds) return GTM_OK;
     cudaSetDevice(ds->model->cfg.device);
     cudaStreamSynchronize(ds->model->stream);
-    for (void *p : ds->owned) cudaFree(p);
+    for (void *p : ds->owned) cudaFreeAsync(p, ds->model->stream);
     cudaFree(ds->Y);
     stream_data_destroy(&ds->sd);
     delete ds;
@@ -395,9 +398,19 @@ static int check_range(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first
     return GTM_OK;
 }
 
+static int ensure_score_scratch(gtm_dataset *ds)
+{
+    if (ds->score_sc.cno) return GTM_OK;
+    GTM_TRY(scratch(ds, &ds->score_sc.cno, ds->cno_stride * ds->score_grid));
+    GTM_TRY(scratch(ds, &ds->score_sc.P, ds->P_stride * ds->score_grid));
+    GTM_TRY(scratch(ds, &ds->score_sc.n_inc, ds->ninc_stride * ds->score_grid));
+    return GTM_OK;
+}
+
 static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
                                 int *sums_dev, int *clause_out_dev)
 {
+    GTM_TRY(ensure_score_scratch(ds));
     DevGraphs g = ds->dg;
     g.n_types = n_types;
     ScoreArgs a;
@@ -440,14 +453,12 @@ extern "C" int gtm_score(gtm_model *m, gtm_dataset *ds, int n_types, int64_t fir
     if (count == 0) return GTM_OK;
     if (!out) return fail(GTM_ERR_ARG, "class_sums_out is null");
     int *dev;
-    GTM_TRY(dev_alloc(&dev, (size_t)count * m->dm.K));
+    GTM_TRY(pool_alloc(&dev, (size_t)count * m->dm.K, m->stream));
     int st = gtm_score_device(m, ds, n_types, first, count, dev);
     cudaError_t e = cudaSuccess;
-    if (st == GTM_OK) {
-        e = cudaMemcpyAsync(out, dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
-    }
-    cudaFree(dev);
+    if (st == GTM_OK) e = cudaMemcpyAsync(out, dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    cudaFreeAsync(dev, m->stream);
+    if (st == GTM_OK && e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     if (st != GTM_OK) return st;
     GTM_CU(e);
     return GTM_OK;

@@ -49,3 +49,27 @@ inline int dev_alloc(T **p, size_t count)
     return GTM_OK;
 }
 
+
+// Stream-ordered allocation from the device's default memory pool, whose release threshold is raised once per
+// device so that freed blocks stay cached: graph sets and result buffers that come and go with every scoring call
+// then cost no cudaMalloc / cudaFree (both of which synchronise the device).
+inline int pool_prepare(int device)
+{
+    static bool done[64];
+    if (device < 0 || device >= 64 || done[device]) return GTM_OK;
+    cudaMemPool_t pool;
+    GTM_CU(cudaDeviceGetDefaultMemPool(&pool, device));
+    unsigned long long keep = ~0ull;
+    GTM_CU(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    done[device] = true;
+    return GTM_OK;
+}
+
+template <class T>
+inline int pool_alloc(T **p, size_t count, cudaStream_t s)
+{
+    *p = nullptr;
+    if (count == 0) count = 1;
+    GTM_CU(cudaMallocAsync((void **)p, count * sizeof(T), s));
+    return GTM_OK;
+}

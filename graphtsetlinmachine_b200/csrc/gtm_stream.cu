@@ -86,7 +86,8 @@ __global__ void stream_fill_kernel(DevModel m, const int *off, unsigned short *l
 
 // -------------------------------------------------------------------------------------------------- scoring
 struct StreamArgs {
-    const int *tile_graph;
+    const int *tile_graph;              // first graph of every tile, or NULL: every tile holds graphs_per_tile graphs
+    int graphs_per_tile;
     int tile_lo, tile_hi;               // tiles [tile_lo, tile_hi)
     int64_t first, count;               // graphs written: [first, first+count)
     int64_t n_graphs, total_nodes;
@@ -144,7 +145,8 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
         __syncthreads();
         const int tile = s_tile;
         if (tile >= a.tile_hi) break;
-        const int g0 = a.tile_graph[tile], g1 = a.tile_graph[tile + 1];
+        const int g0 = a.tile_graph ? a.tile_graph[tile] : (int)min((int64_t)tile * a.graphs_per_tile, a.n_graphs);
+        const int g1 = a.tile_graph ? a.tile_graph[tile + 1] : (int)min((int64_t)(tile + 1) * a.graphs_per_tile, a.n_graphs);
         const int node0 = (int)g.node_index[g0];
         const int node1 = g1 < a.n_graphs ? (int)g.node_index[g1] : (int)a.total_nodes;
         const int nn = node1 - node0;
@@ -343,22 +345,32 @@ int stream_data_create(StreamData *sd, const StreamModel &sm, const DevModel &d,
     GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessorWithFlags(&per_sm, fn, kStreamThreads, smem, 0));
     if (per_sm < 1) return GTM_OK;
 
-    // greedy tiling: consecutive graphs while the node count stays within the tile
+    // tiling: consecutive graphs while the node count stays within the tile (and at most two graphs per thread).
+    // Sets of single-node graphs need no table: every tile holds the same number of graphs.
     const int TN = TNC * 32;
     std::vector<int> &tg = sd->tile_graph_host;
     tg.clear();
-    tg.push_back(0);
-    int64_t used = 0;
-    for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
-        const int64_t n = v->number_of_graph_nodes[gi];
-        if (used + n > TN || (gi - tg.back()) >= 2 * kStreamThreads) { tg.push_back((int)gi); used = 0; }
-        used += n;
+    sd->tile_graph = nullptr;
+    if (v->max_number_of_graph_nodes == 1) {
+        sd->graphs_per_tile = std::min(TN, 2 * kStreamThreads);
+        sd->n_tiles = (int)((v->number_of_graphs + sd->graphs_per_tile - 1) / sd->graphs_per_tile);
+    } else {
+        sd->graphs_per_tile = 0;
+        tg.reserve((size_t)(v->total_nodes / TN) * 2 + 16);
+        tg.push_back(0);
+        int64_t used = 0;
+        for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
+            const int64_t n = v->number_of_graph_nodes[gi];
+            if (used + n > TN || (gi - tg.back()) >= 2 * kStreamThreads) { tg.push_back((int)gi); used = 0; }
+            used += n;
+        }
+        tg.push_back((int)v->number_of_graphs);
+        sd->n_tiles = (int)tg.size() - 1;
+        GTM_TRY(pool_alloc(&sd->tile_graph, tg.size(), s));
+        GTM_CU(cudaMemcpyAsync(sd->tile_graph, tg.data(), tg.size() * sizeof(int), cudaMemcpyHostToDevice, s));
     }
-    tg.push_back((int)v->number_of_graphs);
-    sd->n_tiles = (int)tg.size() - 1;
-    GTM_TRY(dev_alloc(&sd->tile_graph, tg.size()));
-    GTM_CU(cudaMemcpyAsync(sd->tile_graph, tg.data(), tg.size() * sizeof(int), cudaMemcpyHostToDevice, s));
-    GTM_TRY(dev_alloc(&sd->tile_counter, 1));
+    sd->stream = s;
+    GTM_TRY(pool_alloc(&sd->tile_counter, 1, s));
     sd->TNC = TNC;
     sd->grid = sm_count * per_sm;
     sd->smem = smem;
@@ -370,7 +382,8 @@ int stream_data_create(StreamData *sd, const StreamModel &sm, const DevModel &d,
 
 void stream_data_destroy(StreamData *sd)
 {
-    cudaFree(sd->tile_graph); cudaFree(sd->tile_counter);
+    if (sd->tile_graph) cudaFreeAsync(sd->tile_graph, sd->stream);
+    if (sd->tile_counter) cudaFreeAsync(sd->tile_counter, sd->stream);
     sd->tile_graph = nullptr; sd->tile_counter = nullptr; sd->supported = 0;
 }
 
@@ -384,9 +397,16 @@ int stream_score(const StreamModel &sm, const StreamData &sd, const DevModel &d,
     StreamArgs a;
     a.tile_graph = sd.tile_graph;
     // tiles that overlap [first, first+count)
-    const std::vector<int> &tg = sd.tile_graph_host;
-    int lo = (int)(std::upper_bound(tg.begin(), tg.end(), (int)first) - tg.begin()) - 1;
-    int hi = (int)(std::lower_bound(tg.begin(), tg.end(), (int)(first + count)) - tg.begin());
+    int lo, hi;
+    if (sd.graphs_per_tile > 0) {
+        lo = (int)(first / sd.graphs_per_tile);
+        hi = (int)((first + count + sd.graphs_per_tile - 1) / sd.graphs_per_tile);
+    } else {
+        const std::vector<int> &tg = sd.tile_graph_host;
+        lo = (int)(std::upper_bound(tg.begin(), tg.end(), (int)first) - tg.begin()) - 1;
+        hi = (int)(std::lower_bound(tg.begin(), tg.end(), (int)(first + count)) - tg.begin());
+    }
+    a.graphs_per_tile = sd.graphs_per_tile;
     a.tile_lo = lo; a.tile_hi = hi;
     a.first = first; a.count = count; a.n_graphs = sd.n_graphs; a.total_nodes = sd.total_nodes;
     a.class_sums = sums_dev; a.tile_counter = sd.tile_counter; a.TNC = sd.TNC;

@@ -20,7 +20,9 @@ struct StreamData {
     int supported = 0;
     int TNC = 0;                        // node words per tile
     int n_tiles = 0;
-    int *tile_graph = nullptr;          // [n_tiles+1] first graph of every tile
+    int *tile_graph = nullptr;          // [n_tiles+1] first graph of every tile (NULL for sets of single-node graphs)
+    int graphs_per_tile = 0;            // > 0: every tile holds this many graphs
+    cudaStream_t stream = nullptr;      // stream the pooled buffers were allocated on
     std::vector<int> tile_graph_host;
     int grid = 0;
     size_t smem = 0;
