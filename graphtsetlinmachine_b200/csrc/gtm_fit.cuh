@@ -24,6 +24,7 @@ struct FitArgs {
     int clauses_per_cta;
     int clause_words;       // shared-memory words per clause
     int NC;                 // node words of the largest graph
+    int pre_words;          // words per clause for pre-generated Type-I masks (0 = every clause generates its own)
 };
 
 constexpr unsigned kSpinLimit = 1u << 22;
@@ -130,13 +131,14 @@ constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of
 
 // Type I / II feedback of one clause on one layer (kernels.py:98-183), all classes in order.  The warp owns
 // the clause; lanes hold one automaton word each (planes in registers).  `upd_lo` holds the feedback type of
-// class `lane` (classes 0..31); further classes are read back from `update`.  Layers of at most 32 words take the
-// packed Bernoulli words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds
-// in flight per step; wider layers generate them class by class.  Returns the draws consumed.
+// class `lane` (classes 0..31); further classes are read back from `update`.  Masks come from `pre` when the CTA
+// generated the layer's packed Bernoulli words beforehand (generate_masks); otherwise layers of at most 32 words take
+// the words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds in flight per
+// step, and wider layers generate them class by class.  Returns the draws consumed.
 template <int MAXSB>
 __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
                                               bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
-                                              u64 pos0, int lane, u32 *pack)
+                                              u64 pos0, int lane, u32 *pack, const u32 *pre)
 {
     const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
     const float p = m.p_mask[layer];
@@ -163,7 +165,7 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
             const u32 posmask = __ballot_sync(kFull, vals > 0 && lane < kn);
             for (int k8 = 0; k8 < kn; k8 += 8) {
                 const int npos8 = __popc((posmask >> k8) & 0xffu);
-                const bool packed = W <= 32 && npos8 > 0 && !all_ones;
+                const bool packed = pre == nullptr && W <= 32 && npos8 > 0 && !all_ones;
                 if (packed) {
                     // packed-stream words rank*W .. (rank+npos8)*W [+1 when the stream is not word-aligned]
                     const int j0 = rank * W, j1 = (rank + npos8) * W - (shift ? 0 : 1);
@@ -186,7 +188,12 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
                     const int u = __shfl_sync(kFull, vals, kk);
                     if (u > 0) {
                         u32 mask = kFull;
-                        if (packed) {
+                        if (pre != nullptr && !all_ones) {
+                            // words generated beforehand by the whole CTA (generate_masks): pre[rank*W + w], stream-aligned
+                            const u32 lo = mine ? pre[rank * W + lane] : 0u;
+                            const u32 hi = (mine && shift) ? pre[rank * W + lane + 1] : 0u;
+                            mask = __funnelshift_r(lo, hi, shift);
+                        } else if (packed) {
                             const u32 lo = mine ? pack[local * W + lane] : 0u;
                             const u32 hi = (mine && shift) ? pack[local * W + lane + 1] : 0u;
                             mask = __funnelshift_r(lo, hi, shift);
@@ -253,14 +260,18 @@ __device__ __forceinline__ void class_decision_inputs(const DevModel &m, const i
 // once, lanes 0..31 = the pass's next 32 draws, and a short uniform scan replays the reference's short-circuit
 // order on them) and automaton words are spread over lanes; nothing per class goes through global memory.
 // `bits` = the clause's node-output words of the last layer; `P` = message rows [D-1][max_nodes][MW].
-template <int MAXSB>
-__device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
-                                                const FitArgs &a, const u32 *bits, const u32 *P, const int *s_target,
-                                                const float *s_thr, int c, int lane, u32 *pack)
+struct Decision {
+    int chosen;   // selected true node or -1
+    int upd_lo;   // feedback type of class `lane` (classes 0..31)
+    u64 pos;      // stream position after node choice and decisions = first mask draw of layer 0
+};
+
+__device__ __forceinline__ Decision clause_decide(const DevModel &m, const GraphView &gv, const ClauseView &cv,
+                                                  const FitArgs &a, const u32 *bits, const int *s_target,
+                                                  const float *s_thr, int c, int lane)
 {
     const int words = (gv.n + 31) >> 5;
     u64 pos = *cv.pos;
-    const int n_inc = *cv.n_inc;
 
     // 1. one true node, uniformly: the (draw % count)-th set bit in ascending node order
     int count = 0;
@@ -321,19 +332,54 @@ __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphVi
         pos += used;
     }
     if (m.K > 32) __syncwarp();   // classes beyond 31 are read back from a.update
+    if (lane == 0) a.clause_node[c] = chosen;
+    Decision dec;
+    dec.chosen = chosen; dec.upd_lo = upd_lo; dec.pos = pos;
+    return dec;
+}
 
-    // 3./4. automata of every layer
-    const bool within = n_inc <= m.max_included;
-    const int node = clause_true ? chosen : 0;
+// 3./4. automata of every layer.  `pre`, when given, holds the pre-generated packed words of all layers back to back
+// (layer l: npos*W_l + 1 words).
+template <int MAXSB>
+__device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView &gv, const ClauseView &cv, const FitArgs &a,
+                                             const u32 *P, const Decision &dec, int npos, int c, int lane, u32 *pack,
+                                             const u32 *pre)
+{
+    const bool clause_true = dec.chosen != -1;
+    const bool within = *cv.n_inc <= m.max_included;
+    const int node = clause_true ? dec.chosen : 0;
+    u64 pos = dec.pos;
 #pragma unroll 1
     for (int d = 0; d < m.D; ++d) {
         const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * a.max_nodes + node) * m.MW;
-        pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), upd_lo, a.update, clause_true, within, row, d > 0, pos, lane, pack);
+        pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), dec.upd_lo, a.update, clause_true, within, row, d > 0, pos, lane,
+                                     pack, pre);
+        if (pre) pre += npos * (d == 0 ? m.L0 : m.M) + 1;
     }
-    if (lane == 0) {
-        *cv.pos = pos;
-        a.clause_node[c] = chosen;
-    }
+    if (lane == 0) *cv.pos = pos;
+}
+
+template <int MAXSB>
+__device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
+                                                const FitArgs &a, const u32 *bits, const u32 *P, const int *s_target,
+                                                const float *s_thr, int c, int lane, u32 *pack)
+{
+    const Decision dec = clause_decide(m, gv, cv, a, bits, s_target, s_thr, c, lane);
+    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr);
+}
+
+// Packed Bernoulli words of one (clause, layer, round) work item, written to the clause's pre-generated area.
+// Layer l of a clause with `npos` Type-I classes needs words [0, npos*W_l + (shift ? 1 : 0)) of the stream that starts
+// at Philox block pos_l >> 2; round q yields words 4q .. 4q+3.
+__device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, int layer, u64 pos_l, int npos, int q,
+                                                    u32 *dst, int lane)
+{
+    const int W = layer == 0 ? m.L0 : m.M;
+    const int need = npos * W + ((pos_l & 3) ? 1 : 0);
+    const u32 nib = bernoulli_nibbles(m, c, (pos_l >> 2) + (u64)q * 32 + lane, m.p_mask[layer], lane);
+    const u32 word = __reduce_or_sync(0xffu << (lane & 24), nib);
+    const int j = 4 * q + (lane >> 3);
+    if ((lane & 7) == 0 && j < need) dst[j] = word;
 }
 
 // Message rows of the OTHER parity are cleared for the graph after this one: every warp has finished the previous

@@ -17,6 +17,7 @@ namespace gtm {
 // most kStageNodes nodes, kStageRowWords literal words and kStageEdges edge rows; larger graphs are read in place.
 constexpr int kStageNodes = 256, kStageRowWords = 1536, kStageEdges = 512;
 constexpr int kStageWords = kStageRowWords + 3 * kStageNodes + 2 * kStageEdges;
+constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I classes, draw position (2), work items, pad, feedback type of 32 classes
 
 __device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global_src)
 {
@@ -32,6 +33,7 @@ __device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global
 // Per graph the remaining global traffic is the vote exchange and, for depth > 1, the message rows.
 // State is loaded at the start of the launch and written back at its end.
 //   shared memory: [K] vote partial | [K] totals | [2][K] targets | [3][4] graph sizes | [2] staged graphs |
+//                  [12] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
 //                  per owned clause: clause_words words =
 //                  draw counter (2) | include count (1) | pad (1) | weights [K] | hypervector [MB] | node words [2][NC] | planes
 template <int MAXSB>
@@ -45,7 +47,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     int *s_size = s_mem + 6 * KP;                                           // [3][4]: n, first node, first edge row, edge rows
     u32 *s_stage = reinterpret_cast<u32 *>(s_size + 12);                    // [2][kStageWords]
     u32 *s_pack = s_stage + 2 * kStageWords;                                // [12][kPackWords]
-    u32 *s_clauses = s_pack + 12 * kPackWords;
+    int *s_rec = reinterpret_cast<int *>(s_pack + 12 * kPackWords);       // [clauses_per_cta][kRecWords] decisions of the step
+    int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // [clauses_per_cta + 1] (padded to even)
+    u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + ((a.clauses_per_cta + 2) & ~1));   // [clauses_per_cta][pre_words]
+    u32 *s_clauses = s_pre + (size_t)a.clauses_per_cta * a.pre_words;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = blockIdx.x * a.clauses_per_cta, c_hi = min(m.C, c_lo + a.clauses_per_cta);
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
@@ -172,9 +177,82 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         GTM_LAP(t_tot);
         class_decision_inputs(m, s_total, y, s_target, s_thr);
         __syncthreads();
-        for (int c = c_lo + warp; c < c_hi; c += nwarps) {
-            const ClauseView cv = view_of(c);
-            clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords);
+        if (a.pre_words > 0) {
+            // cooperative feedback: decisions per clause, then every (clause, layer, round) of mask generation is a work
+            // item shared by all warps of the CTA, then the automaton updates per clause
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                const Decision dec = clause_decide(m, gv, cv, a, node_words(c, m.D - 1), s_target, s_thr, c, lane);
+                const int npos = __popc(__ballot_sync(kFull, dec.upd_lo > 0));
+                int need = 0, items = 0;
+                u64 pos_l = dec.pos;
+                for (int l = 0; l < m.D; ++l) {
+                    const int W = l == 0 ? m.L0 : m.M;
+                    need += npos * W + 1;
+                    if (npos > 0 && m.p_mask[l] < 1.0f) items += (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
+                    pos_l += (u64)npos * W * 32;
+                }
+                int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
+                if (lane == 0) {
+                    rec[0] = dec.chosen; rec[1] = npos;
+                    rec[2] = (int)(u32)dec.pos; rec[3] = (int)(u32)(dec.pos >> 32);
+                    rec[4] = need <= a.pre_words ? items : -1;           // -1: does not fit, the clause generates on its own
+                }
+                rec[5 + lane] = dec.upd_lo;
+            }
+            __syncthreads();
+            if (warp == 0) {      // exclusive prefix of the work items per clause
+                int run = 0;
+                for (int cb = 0; cb < c_hi - c_lo; cb += 32) {
+                    const int it = cb + lane < c_hi - c_lo ? max(0, s_rec[(size_t)(cb + lane) * kRecWords + 4]) : 0;
+                    int incl = it;
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int t = __shfl_up_sync(kFull, incl, d);
+                        if (lane >= d) incl += t;
+                    }
+                    if (cb + lane < c_hi - c_lo) s_item_off[cb + lane] = run + incl - it;
+                    run += __shfl_sync(kFull, incl, 31);
+                }
+                if (lane == 0) s_item_off[c_hi - c_lo] = run;
+            }
+            __syncthreads();
+            {
+                const int total = s_item_off[c_hi - c_lo];
+                int ci = 0;
+                for (int i = warp; i < total; i += nwarps) {
+                    while (i >= s_item_off[ci + 1]) ++ci;
+                    const int *rec = s_rec + (size_t)ci * kRecWords;
+                    const int npos = rec[1];
+                    u64 pos_l = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                    int r = i - s_item_off[ci];
+                    u32 *dst = s_pre + (size_t)ci * a.pre_words;
+                    for (int l = 0; l < m.D; ++l) {
+                        const int W = l == 0 ? m.L0 : m.M;
+                        const int rounds = m.p_mask[l] < 1.0f ? (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2 : 0;
+                        if (r < rounds) { generate_mask_round(m, c_lo + ci, l, pos_l, npos, r, dst, lane); break; }
+                        r -= rounds;
+                        dst += npos * W + 1;
+                        pos_l += (u64)npos * W * 32;
+                    }
+                }
+            }
+            __syncthreads();
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                const int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
+                Decision dec;
+                dec.chosen = rec[0];
+                dec.pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                dec.upd_lo = rec[5 + lane];
+                clause_apply<MAXSB>(m, gv, cv, a, P, dec, rec[1], c, lane, s_pack + warp * kPackWords,
+                                    rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr);
+            }
+        } else {
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords);
+            }
         }
         GTM_LAP(t_x3);
         wait_copies();
@@ -225,7 +303,7 @@ static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0; size_t smem = 0; };
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0; size_t smem = 0; };
 
 static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
 {
@@ -235,17 +313,22 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
     const int warps = kResidentThreads / 32;
     int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
     words = (words + 3) & ~3;
+    // cooperative mask generation: layers of at most 32 words, at most 32 classes; room for 8 Type-I classes per clause
+    int pre_words = 0;
+    if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
     for (int per_sm = 2; per_sm >= 1; --per_sm) {
         int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
         const int cpb = (d.C + grid - 1) / grid;
         grid = (d.C + cpb - 1) / cpb;
-        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) + (size_t)cpb * words * sizeof(u32);
+        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) +
+                            ((size_t)cpb * kRecWords + ((cpb + 2) & ~1) + (size_t)cpb * pre_words) * sizeof(int) +
+                            (size_t)cpb * words * sizeof(u32);
         if (smem > 200 * 1024) continue;
         if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
         if ((long long)occ * m->sm_count < grid) continue;
-        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.smem = smem;
+        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
         return plan;
     }
     return plan;
@@ -281,7 +364,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
         return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
     if (plan.grid > 0) {
-        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words;
+        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
         void *args[] = {&dm, &g, &a};
         const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(plan.grid), dim3(kResidentThreads), args, plan.smem, m->stream));
