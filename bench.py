@@ -31,6 +31,9 @@ UNIQUE_GRAPHS = 1 << 18          # distinct synthetic images per rank; tiled to 
 BATCH_GRAPHS = 1 << 22           # graphs scored per step per GPU: X alone is 134 MB (> 126 MB of L2)
 BYTES_PER_GRAPH = 4 * 1 * 8 + 8 * 1 + 8 * 0 + 4 * CLASSES     # 4nL0 + 8n + 8E + 4K = 80
 LOP3_PER_GRAPH = CLAUSES * 1 * 8                               # C*n*L0 word tests, dense equivalent
+# DRAM bytes per graph of the scoring kernel from one ncu capture of a full-size launch
+# (profiles/stream_score_kernel__vanilla_mnist_4M_graphs.md: 186.75 MB read + 124.24 MB written for 4,194,304 graphs)
+NCU_DRAM_BYTES_PER_GRAPH = (186.750208e6 + 124.236288e6) / 4194304
 
 
 def peaks():
@@ -313,8 +316,11 @@ def main():
                     "steps": e2e_steps},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_kind, "bytes_per_graph": BYTES_PER_GRAPH,
-                         "kernel": "score kernel, one launch per step",
+                         "traffic": NCU_DRAM_BYTES_PER_GRAPH * n, "traffic_unit": "bytes per launch (ncu dram read+write, scaled by graphs)",
+                         "peak_source": peak_kind + " copy bandwidth (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
+                         "bytes_per_launch": BYTES_PER_GRAPH * n, "bytes_per_graph": BYTES_PER_GRAPH,
+                         "kernel": "stream_score_kernel, one launch per step",
+                         "note": "integer / shared-memory bound (ncu: shared-memory wavefronts 68 % of peak, DRAM 0.3 %), see int_ops",
                          "int_ops": {"dense_lop3_per_graph": LOP3_PER_GRAPH,
                                      "achieved_tlop3_s": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12}},
             "cpu_baseline": cpu,
