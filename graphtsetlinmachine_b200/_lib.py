@@ -61,6 +61,9 @@ PROTOTYPES = {
     "gtm_score": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_score_device": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_score_static_scratch": [C.c_void_p, C.POINTER(GraphsView), C.c_int, C.c_int64, C.c_int64, C.c_void_p],
+    "gtm_shard_range": [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)],
+    "gtm_shard_prepare": [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p],
+    "gtm_shard_connect": [C.c_void_p, C.c_void_p, C.c_void_p],
     "gtm_fit": [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int],
     "gtm_transform": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p],
     "gtm_debug_evaluate": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,

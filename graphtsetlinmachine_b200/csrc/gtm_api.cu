@@ -382,6 +382,7 @@ extern "C" int gtm_dataset_destroy(gtm_dataset *ds)
     for (void *p : ds->owned) cudaFreeAsync(p, ds->model->stream);
     cudaFree(ds->Y);
     stream_data_destroy(&ds->sd);
+    fit_comm_release(ds);
     delete ds;
     return GTM_OK;
 }

@@ -160,14 +160,22 @@ struct ClauseView {
     const u32 *hv;        // [MB] message hypervector of the clause
 };
 
+// Message buffers that receive a scatter: the local one, or the same buffer on every GPU of a clause-sharded fit
+// (peer pointers; plain atomics over NVLink).
+constexpr int kMaxRanks = 8;
+struct ScatterTargets {
+    int world;
+    u32 *base[kMaxRanks];
+};
+
 // One warp evaluates a clause at layer `d` over all nodes of a graph (lanes = the 32 nodes of a node word) and
 // writes the node-output words out[0..ceil(n/32)).  Layer 0 tests the node's literal row, layer d >= 1 the node's
 // message row ANDed with the node's bit of layer d-1 in `prev` (kernels.py:407-530).  Returns the OR of the words
-// written (warp-uniform).  When `Pscatter` is given, every true node sends the clause's hypervector bits along
-// its out-edges into it (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
+// written (warp-uniform).  When `scatter` is given, every true node sends the clause's hypervector bits along
+// its out-edges into every target buffer (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
 __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphView &gv, int n_types, const ClauseView &cv,
-                                                 int c, int d, const u32 *prev, u32 *out, const u32 *Pread, u32 *Pscatter,
-                                                 int lane)
+                                                 int c, int d, const u32 *prev, u32 *out, const u32 *Pread,
+                                                 const ScatterTargets *scatter, int lane)
 {
     const int n = gv.n;
     const int W = d == 0 ? m.L0 : m.M;
@@ -220,14 +228,15 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
         const u32 word = __ballot_sync(kFull, ok);
         if (lane == 0) out[j] = word;
         any |= word;
-        if (Pscatter && ok) {
+        if (scatter && ok) {
             const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
             for (u32 k = 0; k < deg; ++k) {
                 const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
                 if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
                 for (int b = 0; b < m.MB; ++b) {
                     const u32 bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
-                    atomicOr(Pscatter + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
+                    for (int r = 0; r < scatter->world; ++r)
+                        atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
                 }
             }
         }

@@ -25,48 +25,66 @@ struct FitArgs {
     int clause_words;       // shared-memory words per clause
     int NC;                 // node words of the largest graph
     int pre_words;          // words per clause for pre-generated Type-I masks (0 = every clause generates its own)
+    // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits
+    // and barrier arrivals go to every rank's buffers through peer pointers.  world == 1: everything is local.
+    int world, rank;
+    int c_begin, c_end;
+    u32 tag_base;           // step tags of this launch are tag_base + step + 1
+    unsigned barrier_base;  // value of the arrival counters before this launch
+    unsigned long long *exchange_peer[kMaxRanks];   // [2][world][gridDim.x][K] on every rank
+    unsigned *barrier_peer[kMaxRanks];
+    u32 *P_peer[kMaxRanks][2];
 };
 
 constexpr unsigned kSpinLimit = 1u << 22;
 
-// Grid-wide barrier over co-resident CTAs (cooperative launch).  The arrival counter only grows; arrival is a
-// release, the poll an acquire, so no separate fences are needed.  The wait is bounded: after kSpinLimit polls
-// the CTA raises *error and gives up.  Returns false once any CTA gave up.
-__device__ __forceinline__ bool grid_barrier(unsigned *counter, unsigned target, int *error)
+// Barrier over all co-resident CTAs of all ranks (cooperative launch per rank; ranks of a clause-sharded fit run the
+// same step sequence).  Every CTA adds one arrival to the counter of EVERY rank (release; system scope when peers are
+// involved) and polls its own rank's counter (acquire).  Counters only grow, `target` is compared wrap-safely.  The
+// wait is bounded: after kSpinLimit polls the CTA raises *error and gives up.  Returns false once any CTA gave up.
+__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+        if (a.world == 1) {
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier) : "memory");
+        } else {
+            for (int r = 0; r < a.world; ++r)
+                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
+        }
         unsigned spins = 0;
         while (true) {
             unsigned seen;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-            if (seen >= target) break;
-            if (*(volatile int *)error) break;
-            if (++spins > kSpinLimit) { atomicExch(error, 1); break; }
+            if (a.world == 1) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
+            else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
+            if ((int)(seen - target) >= 0) break;
+            if (*(volatile int *)a.error) break;
+            if (++spins > kSpinLimit) { atomicExch(a.error, 1); break; }
         }
     }
     __syncthreads();
-    return *(volatile int *)error == 0;
+    return *(volatile int *)a.error == 0;
 }
 
 // Class sums of one graph from per-CTA vote partials, in one round: every CTA publishes its K partials as 64-bit
-// words that carry the step tag next to the value (an aligned 8-byte store is single-copy atomic, so a reader that
-// sees the tag sees the value), then every CTA reads all gridDim.x*K words, eight independent loads per thread in
-// flight, re-polling only words whose tag is still old.  Slots alternate by graph parity: a slot is rewritten two
-// steps later, which its owner can only reach after every CTA has read the current step.
+// words that carry the step tag next to the value (an aligned 8-byte store is single-copy atomic, also through a
+// peer pointer, so a reader that sees the tag sees the value) into the slot array of EVERY rank, then reads all
+// world*gridDim.x*K words of its own rank's array, eight independent loads per thread in flight, re-polling only
+// words whose tag is still old.  Slots alternate by graph parity: a slot is rewritten two steps later, which its owner
+// can only reach after every CTA of every rank has read the current step.
 // Call with s_sum complete (after a __syncthreads); leaves totals in s_total, clears s_sum.  Bounded polls.
-__device__ __forceinline__ bool exchange_class_sums(unsigned long long *slots, int par, u32 tag, int *s_sum, int *s_total,
-                                                    int K, int *error, int *tap)
+__device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, int par, u32 tag, int *s_sum, int *s_total, int K)
 {
-    volatile unsigned long long *all = slots + (size_t)par * gridDim.x * K;
+    const size_t mine = (((size_t)par * a.world + a.rank) * gridDim.x + blockIdx.x) * K;
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        all[(size_t)blockIdx.x * K + k] = ((unsigned long long)(u32)s_sum[k] << 32) | tag;
+        const unsigned long long word = ((unsigned long long)(u32)s_sum[k] << 32) | tag;
+        for (int r = 0; r < a.world; ++r) *(volatile unsigned long long *)(a.exchange_peer[r] + mine + k) = word;
         s_sum[k] = 0;
         s_total[k] = 0;
     }
     __syncthreads();
-    const int total = (int)gridDim.x * K;
+    volatile unsigned long long *all = a.exchange + (size_t)par * a.world * gridDim.x * K;
+    const int total = a.world * (int)gridDim.x * K;
     for (int t0 = threadIdx.x; t0 < total; t0 += 8 * blockDim.x) {
         unsigned long long v[8];
 #pragma unroll
@@ -80,16 +98,16 @@ __device__ __forceinline__ bool exchange_class_sums(unsigned long long *slots, i
             if (t >= total) continue;
             unsigned spins = 0;
             while ((u32)v[j] != tag) {
-                if (++spins > kSpinLimit || *(volatile int *)error) { atomicExch(error, 1); break; }
+                if (++spins > kSpinLimit || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
                 v[j] = all[t];
             }
             atomicAdd(&s_total[t % K], (int)(u32)(v[j] >> 32));
         }
     }
     __syncthreads();
-    if (tap && blockIdx.x == 0)
-        for (int k = threadIdx.x; k < K; k += blockDim.x) tap[k] = s_total[k];
-    return *(volatile int *)error == 0;
+    if (blockIdx.x == 0)
+        for (int k = threadIdx.x; k < K; k += blockDim.x) a.class_sum_tap[k] = s_total[k];
+    return *(volatile int *)a.error == 0;
 }
 
 // Four consecutive draws of a clause stream: Philox block `block` (draws 4*block .. 4*block+3), or the

@@ -27,10 +27,20 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
     const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
-    unsigned arrivals = 0;
+    unsigned arrivals = a.barrier_base;
 
     for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
     __syncthreads();
+    if (a.world > 1 && m.D > 1) {
+        // clause-sharded start: every rank clears its own message buffers (peers will OR into them), then all ranks meet
+        const size_t words = (size_t)(m.D - 1) * a.max_nodes * m.MW;
+        for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < words; t += (size_t)gridDim.x * blockDim.x) {
+            a.P_pair[0][t] = 0;
+            a.P_pair[1][t] = 0;
+        }
+        arrivals += gridDim.x * a.world;
+        if (!grid_barrier(a, arrivals)) return;
+    }
     const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t0 = clock64(), t1;
 
@@ -46,28 +56,31 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 const bool last = d == m.D - 1;
                 if (d > 0) {
                     GTM_LAP(t_eval);
-                    arrivals += gridDim.x;
-                    if (!grid_barrier(a.barrier, arrivals, a.error)) return;
+                    arrivals += gridDim.x * a.world;
+                    if (!grid_barrier(a, arrivals)) return;
                     GTM_LAP(t_bar);
                     if (d == 1) clear_next_messages(m, g, a, par, i, e);
                 }
-                for (int c = gwarp; c < m.C; c += nwarps) {
+                ScatterTargets targets;
+                targets.world = a.world;
+                for (int r = 0; r < a.world; ++r) targets.base[r] = a.P_peer[r][par] + (size_t)d * layer_words;
+                for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
                     const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                       cno_row(sc, m.C, d, c), d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
-                                                      last ? nullptr : P + (size_t)d * layer_words, lane);
+                                                      last ? nullptr : &targets, lane);
                     if (last && any)
                         for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], m.weights[(size_t)k * m.C + c]);
                 }
             }
             __syncthreads();
             GTM_LAP(t_eval);
-            if (!exchange_class_sums(a.exchange, par, (u32)step + 1u, s_sum, s_total, m.K, a.error, a.class_sum_tap)) return;
+            if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
             GTM_LAP(t_tot);
             if (!eval_only) {
                 class_decision_inputs(m, s_total, a.Y + (size_t)e * m.K, s_target, s_thr);
                 __syncthreads();
-                for (int c = gwarp; c < m.C; c += nwarps) {
+                for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
                     clause_feedback<MAXSB>(m, gv, cv, a, cno_row(sc, m.C, m.D - 1, c), P, s_target, s_thr, c, lane,
                                            s_pack[threadIdx.x >> 5]);

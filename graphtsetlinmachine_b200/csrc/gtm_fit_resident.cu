@@ -52,11 +52,11 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + ((a.clauses_per_cta + 2) & ~1));   // [clauses_per_cta][pre_words]
     u32 *s_clauses = s_pre + (size_t)a.clauses_per_cta * a.pre_words;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int c_lo = blockIdx.x * a.clauses_per_cta, c_hi = min(m.C, c_lo + a.clauses_per_cta);
+    const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
     const int NC = a.NC;
     const u64 steps = (u64)a.epochs * (u64)a.count;
-    unsigned arrivals = 0;
+    unsigned arrivals = a.barrier_base;
 
     auto view_of = [&](int c) {
         u32 *basep = s_clauses + (size_t)(c - c_lo) * a.clause_words;
@@ -125,6 +125,16 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     fetch_graph(0, e_cur);
     wait_copies();
     __syncthreads();
+    if (a.world > 1 && m.D > 1) {
+        // clause-sharded start: every rank clears its own message buffers (peers will OR into them), then all ranks meet
+        const size_t words = (size_t)(m.D - 1) * a.max_nodes * m.MW;
+        for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < words; t += (size_t)gridDim.x * blockDim.x) {
+            a.P_pair[0][t] = 0;
+            a.P_pair[1][t] = 0;
+        }
+        arrivals += gridDim.x * a.world;
+        if (!grid_barrier(a, arrivals)) return;
+    }
     const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t_x0 = 0, t_x1 = 0, t_x2 = 0, t_x3 = 0, t0 = clock64(), t1;
 
@@ -156,16 +166,19 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             const bool last = d == m.D - 1;
             if (d > 0) {
                 GTM_LAP(t_eval);
-                arrivals += gridDim.x;
-                if (!grid_barrier(a.barrier, arrivals, a.error)) return;
+                arrivals += gridDim.x * a.world;
+                if (!grid_barrier(a, arrivals)) return;
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, g, a, par, i, e);
             }
+            ScatterTargets targets;
+            targets.world = a.world;
+            for (int r = 0; r < a.world; ++r) targets.base[r] = a.P_peer[r][par] + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
                                                   d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
-                                                  last ? nullptr : P + (size_t)d * layer_words, lane);
+                                                  last ? nullptr : &targets, lane);
                 if (last && any)
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
             }
@@ -173,7 +186,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         GTM_LAP(t_x2);
         __syncthreads();
         GTM_LAP(t_eval);
-        if (!exchange_class_sums(a.exchange, par, (u32)step + 1u, s_sum, s_total, m.K, a.error, a.class_sum_tap)) return;
+        if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
         GTM_LAP(t_tot);
         class_decision_inputs(m, s_total, y, s_target, s_thr);
         __syncthreads();
@@ -305,9 +318,10 @@ constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
 struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0; size_t smem = 0; };
 
-static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
+static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses)
 {
-    const DevModel &d = m->dm;
+    DevModel d = m->dm;
+    d.C = n_clauses;   // clauses this rank learns
     ResidentPlan plan;
     const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
     const int warps = kResidentThreads / 32;
@@ -334,50 +348,171 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds)
     return plan;
 }
 
+static int shard_size(int C, int world) { return (C + world - 1) / world; }
+
 int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
-                      int epochs, int eval_only)
+               int epochs, int eval_only)
 {
     const DevModel &d = m->dm;
+    FitComm &cm = ds->comm;
+    const bool sharded = cm.world > 1 && !eval_only;
+    if (sharded && !cm.connected) return fail(GTM_ERR_STATE, "clause sharding was prepared but the ranks are not connected (gtm_shard_connect)");
+    if (sharded && cm.broken) return fail(GTM_ERR_STATE, "an earlier sharded fit timed out; prepare and connect the ranks again");
     DevGraphs g = ds->dg;
     g.n_types = n_types;
     EvalScratch sc = ds->fit_sc;
     FitArgs a;
     memset(&a, 0, sizeof a);
     a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
-    a.exchange = m->exchange; a.P_pair[0] = ds->P_pair[0]; a.P_pair[1] = ds->P_pair[1];
     a.max_nodes = ds->max_nodes;
-    a.barrier = m->barrier; a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
+    a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
     a.class_sum_tap = m->class_sum_tap;
     a.phase_cycles = m->phase_cycles;
     a.NC = ds->NC;
     const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
-    GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
     GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
-    GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
-    if (d.D > 1) {
-        GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
-        GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
-    }
-    DevModel dm = d;
-    ResidentPlan plan;
-    if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds);
-    if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
-        return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
-    if (plan.grid > 0) {
-        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
-        void *args[] = {&dm, &g, &a};
-        const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
-        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(plan.grid), dim3(kResidentThreads), args, plan.smem, m->stream));
+
+    int grid, block;
+    size_t smem;
+    const void *fn;
+    bool resident;
+    if (sharded) {
+        a.world = cm.world; a.rank = cm.rank;
+        const int per = shard_size(d.C, cm.world);
+        a.c_begin = std::min(d.C, cm.rank * per); a.c_end = std::min(d.C, a.c_begin + per);
+        a.tag_base = cm.tag_base; a.barrier_base = cm.barrier_base;
+        for (int r = 0; r < cm.world; ++r) {
+            char *base = (char *)cm.peer_block[r];
+            a.barrier_peer[r] = (unsigned *)base;
+            a.exchange_peer[r] = (unsigned long long *)(base + cm.exchange_off);
+            a.P_peer[r][0] = (u32 *)(base + cm.P_off[0]);
+            a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
+        }
+        resident = cm.resident; grid = cm.grid;
+        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words;
+        smem = cm.smem;
     } else {
+        a.world = 1; a.rank = 0; a.c_begin = 0; a.c_end = d.C;
+        a.tag_base = 0; a.barrier_base = 0;
+        a.barrier_peer[0] = m->barrier; a.exchange_peer[0] = m->exchange;
+        a.P_peer[0][0] = ds->P_pair[0]; a.P_peer[0][1] = ds->P_pair[1];
+        GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
+        GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
+        if (d.D > 1) {
+            GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
+            GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
+        }
+        ResidentPlan plan;
+        if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds, d.C);
+        if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
+            return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
+        resident = plan.grid > 0;
+        grid = resident ? plan.grid : m->fit_grid;
+        a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
+        smem = plan.smem;
+    }
+    a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
+    a.P_pair[0] = a.P_peer[a.rank][0]; a.P_pair[1] = a.P_peer[a.rank][1];
+
+    DevModel dm = d;
+    if (resident) {
+        fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+        block = kResidentThreads;
+        if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        void *args[] = {&dm, &g, &a};
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
+    } else {
+        fn = fit_global_kernel(d.SB);
+        block = m->fit_block;
+        smem = 4 * (size_t)d.K * sizeof(int);
         void *args[] = {&dm, &g, &sc, &a, &eval_only};
-        const size_t smem = 4 * (size_t)d.K * sizeof(int);
-        const void *fn = fit_global_kernel(d.SB);
-        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(m->fit_grid), dim3(m->fit_block), args, smem, m->stream));
+        GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
+    }
+    if (sharded) {   // what the counters and tags look like after this launch (the same on every rank)
+        const unsigned long long steps = (unsigned long long)epochs * (unsigned long long)count;
+        const unsigned long long barriers = (d.D > 1 ? 1ull : 0ull) + steps * (unsigned long long)(d.D - 1);
+        cm.tag_base += (u32)steps;
+        cm.barrier_base += (unsigned)(barriers * (unsigned long long)grid * (unsigned long long)cm.world);
     }
     int err = 0;
     GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
     GTM_CU(cudaStreamSynchronize(m->stream));
-    if (err) return fail(GTM_ERR_TIMEOUT, "a bounded wait of the learning kernel (grid barrier or vote exchange) gave up");
+    if (err) {
+        if (sharded) cm.broken = true;
+        return fail(GTM_ERR_TIMEOUT, "a bounded wait of the learning kernel (grid barrier or vote exchange) gave up");
+    }
     return GTM_OK;
 }
 
+// ------------------------------------------------------------------------------------------ clause sharding
+extern "C" int gtm_shard_range(gtm_model *m, int world, int rank, int *first_clause, int *n_clauses)
+{
+    if (!m || !first_clause || !n_clauses) return fail(GTM_ERR_ARG, "null argument");
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return fail(GTM_ERR_ARG, "world must be 1..%d and rank inside it", kMaxRanks);
+    const int per = shard_size(m->dm.C, world);
+    *first_clause = std::min(m->dm.C, rank * per);
+    *n_clauses = std::min(m->dm.C, *first_clause + per) - *first_clause;
+    return GTM_OK;
+}
+
+extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int rank, unsigned char *handle_out)
+{
+    if (!m || !ds || ds->model != m || !handle_out) return fail(GTM_ERR_ARG, "null argument or dataset of another model");
+    if (world < 2 || world > kMaxRanks || rank < 0 || rank >= world) return fail(GTM_ERR_ARG, "world must be 2..%d and rank inside it", kMaxRanks);
+    GTM_CU(cudaSetDevice(m->cfg.device));
+    const DevModel &d = m->dm;
+    FitComm &cm = ds->comm;
+    if (cm.block) return fail(GTM_ERR_STATE, "clause sharding is already prepared for this graph set");
+    const int per = shard_size(d.C, world);
+    // every rank derives the same launch shape from the shard size (the last shard may be shorter; it runs the same grid)
+    ResidentPlan plan;
+    if (m->opt_fit_kernel != 1) plan = plan_resident(m, ds, per);
+    cm.resident = plan.grid > 0;
+    if (cm.resident) {
+        cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
+        cm.pre_words = plan.pre_words; cm.smem = plan.smem;
+    } else {
+        const int warps = m->fit_block / 32;
+        cm.grid = std::max(1, std::min(m->fit_grid, (per + warps - 1) / warps));
+    }
+    const size_t p_bytes = ((size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32) + 255) & ~(size_t)255;
+    cm.exchange_off = 256;
+    const size_t ex_bytes = ((size_t)2 * world * cm.grid * d.K * sizeof(unsigned long long) + 255) & ~(size_t)255;
+    cm.P_off[0] = cm.exchange_off + ex_bytes;
+    cm.P_off[1] = cm.P_off[0] + p_bytes;
+    cm.bytes = cm.P_off[1] + p_bytes;
+    GTM_CU(cudaMalloc(&cm.block, cm.bytes));
+    GTM_CU(cudaMemset(cm.block, 0, cm.bytes));
+    cm.world = world; cm.rank = rank;
+    cm.peer_block[rank] = cm.block;
+    cudaIpcMemHandle_t h;
+    GTM_CU(cudaIpcGetMemHandle(&h, cm.block));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle_out, &h, 64);
+    return GTM_OK;
+}
+
+extern "C" int gtm_shard_connect(gtm_model *m, gtm_dataset *ds, const unsigned char *handles)
+{
+    if (!m || !ds || ds->model != m || !handles) return fail(GTM_ERR_ARG, "null argument or dataset of another model");
+    FitComm &cm = ds->comm;
+    if (!cm.block) return fail(GTM_ERR_STATE, "call gtm_shard_prepare first");
+    GTM_CU(cudaSetDevice(m->cfg.device));
+    for (int r = 0; r < cm.world; ++r) {
+        if (r == cm.rank || cm.peer_block[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 64, 64);
+        GTM_CU(cudaIpcOpenMemHandle(&cm.peer_block[r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    cm.connected = true;
+    return GTM_OK;
+}
+
+void fit_comm_release(gtm_dataset *ds)
+{
+    FitComm &cm = ds->comm;
+    for (int r = 0; r < cm.world; ++r)
+        if (r != cm.rank && cm.peer_block[r]) cudaIpcCloseMemHandle(cm.peer_block[r]);
+    if (cm.block) cudaFree(cm.block);
+    cm = FitComm();
+}

@@ -29,6 +29,22 @@ struct gtm_model {
     bool lists_dirty = true;
 };
 
+// Buffers through which the learning kernels of several GPUs talk to each other when clauses are sharded over ranks
+// (one process per GPU): per rank one cudaMalloc'd block [arrival counter | vote slots | message buffers x 2], shared
+// with the other ranks through CUDA IPC.
+struct FitComm {
+    void *block = nullptr;
+    void *peer_block[kMaxRanks] = {};
+    size_t bytes = 0, exchange_off = 0, P_off[2] = {0, 0};
+    int world = 1, rank = 0, grid = 0;
+    bool resident = false;
+    int clauses_per_cta = 0, clause_words = 0, pre_words = 0;
+    size_t smem = 0;
+    bool connected = false, broken = false;
+    u32 tag_base = 0;
+    unsigned barrier_base = 0;
+};
+
 struct gtm_dataset {
     gtm_model *model;
     DevGraphs dg;
@@ -46,6 +62,8 @@ struct gtm_dataset {
     size_t Y_capacity = 0;
     // node-stream scoring
     StreamData sd;
+    // clause-sharded learning
+    FitComm comm;
 };
 
 
@@ -53,3 +71,4 @@ struct gtm_dataset {
 int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *grid_out);
 int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count, int epochs,
                int eval_only);
+void fit_comm_release(gtm_dataset *ds);

@@ -91,11 +91,14 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
         __syncthreads();
         for (int d = 0; d < m.D; ++d) {
             const bool last = d == m.D - 1;
+            ScatterTargets targets;
+            targets.world = 1;
+            targets.base[0] = sc.P + (size_t)d * layer_words;
             for (int c = warp; c < m.C; c += nwarps) {
                 const ClauseView cv = global_view(m, sc.n_inc, c);
                 const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                   cno_row(sc, m.C, d, c), d > 0 ? sc.P + (size_t)(d - 1) * layer_words : nullptr,
-                                                  last ? nullptr : sc.P + (size_t)d * layer_words, lane);
+                                                  last ? nullptr : &targets, lane);
                 if (last) {
                     if (any)
                         for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], m.weights[(size_t)k * m.C + c]);

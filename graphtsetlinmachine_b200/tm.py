@@ -142,6 +142,8 @@ class CommonTsetlinMachine:
         self._model = C.c_void_p()
         self._train_set = None
         self._test_set = None
+        self._shard_group = None      # torch.distributed group over which clauses are sharded during fit
+        self._sharded = False
 
     # ------------------------------------------------------------------------------------------ life cycle
     def __del__(self):
@@ -158,6 +160,69 @@ class CommonTsetlinMachine:
         if self._model:
             self._lib.gtm_destroy(self._model)
             self._model = C.c_void_p()
+
+    # ------------------------------------------------------------------------------ clause-sharded learning
+    def shard_clauses(self, group=None):
+        """Learn with the clauses sharded over the ranks of a ``torch.distributed`` process group, one process per
+        GPU of one box (not in the reference, which is single-GPU).  Every rank must build the model with the same
+        arguments, seed and ``numpy.random`` state, and call ``fit`` with the same graphs and labels; after every
+        ``fit`` all ranks hold the same, complete model again, so ``predict`` needs no communication.  The result is
+        bit-identical to single-GPU learning."""
+        import torch.distributed as dist
+
+        self._shard_group = group
+        self._sharded = dist.get_world_size(group) > 1
+
+    def _connect_shards(self):
+        """Exchange the IPC handles of the ranks' exchange buffers for the current training set."""
+        import torch
+        import torch.distributed as dist
+
+        world, rank = dist.get_world_size(self._shard_group), dist.get_rank(self._shard_group)
+        handle = (C.c_ubyte * 64)()
+        _lib.check(self._lib.gtm_shard_prepare(self._model, self._train_set.handle, world, rank, handle))
+        dev = "cuda" if dist.get_backend(self._shard_group) == "nccl" else "cpu"
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine, group=self._shard_group)
+        handles = np.concatenate([p.cpu().numpy() for p in parts]).astype(np.uint8)
+        _lib.check(self._lib.gtm_shard_connect(self._model, self._train_set.handle, _ptr(handles)))
+        self._train_set.shards_connected = True
+
+    def _sync_shards(self):
+        """After a sharded fit every rank owns the updated state of its clauses: gather the shards so that all ranks
+        hold the complete model (also the synchronisation point the engine requires between two sharded fits)."""
+        import torch
+        import torch.distributed as dist
+
+        group = self._shard_group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        first, count = C.c_int(), C.c_int()
+        _lib.check(self._lib.gtm_shard_range(self._model, world, rank, C.byref(first), C.byref(count)))
+        first, count = first.value, count.value
+        clauses = self.number_of_clauses
+        per = (clauses + world - 1) // world
+        dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+
+        def gather_rows(rows):           # rows: int32/int64 [clauses][cols]; returns the array with every rank's rows
+            mine = torch.zeros((per, rows.shape[1]), dtype=torch.from_numpy(rows[:1]).dtype, device=dev)
+            if count:
+                mine[:count] = torch.from_numpy(np.ascontiguousarray(rows[first:first + count])).to(dev)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            return np.concatenate([p.cpu().numpy() for p in parts], axis=0)[:clauses]
+
+        for layer in range(self.depth):
+            planes = self._download_ta(layer).view(np.int32).reshape(clauses, -1)
+            full = np.ascontiguousarray(gather_rows(planes)).view(np.uint32)
+            _lib.check(self._lib.gtm_set_ta_state(self._model, layer, _ptr(full)))
+        weights = self._download_weights().reshape(self.number_of_outputs, clauses).T
+        full_w = np.ascontiguousarray(gather_rows(np.ascontiguousarray(weights)).T, dtype=np.int32)
+        _lib.check(self._lib.gtm_set_weights(self._model, _ptr(full_w)))
+        pos = np.zeros(clauses, dtype=np.uint64)
+        _lib.check(self._lib.gtm_get_draw_positions(self._model, _ptr(pos)))
+        full_p = np.ascontiguousarray(gather_rows(pos.view(np.int64).reshape(clauses, 1))).view(np.uint64).reshape(clauses)
+        _lib.check(self._lib.gtm_set_draw_positions(self._model, _ptr(np.ascontiguousarray(full_p))))
 
     def _create_engine(self):
         """tm.py:437-513 + :110-124: the engine takes sizes at run time, so there is nothing to compile."""
@@ -236,9 +301,13 @@ class CommonTsetlinMachine:
         self._init_fit(graphs, encoded_Y, incremental)
         self.number_of_outputs_at_init = self.number_of_outputs
         y = np.ascontiguousarray(encoded_Y, dtype=np.int32)
+        if self._sharded and not getattr(self._train_set, "shards_connected", False):
+            self._connect_shards()
         _lib.check(self._lib.gtm_fit(self._model, self._train_set.handle,
                                      int(graphs.number_of_node_types()), _ptr(y), 0, int(graphs.number_of_graphs),
                                      int(epochs)))
+        if self._sharded:
+            self._sync_shards()
         self.ta_state = np.array([])
         self.clause_weights = np.array([])
         return

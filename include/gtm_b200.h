@@ -162,6 +162,22 @@ int gtm_score_static_scratch(gtm_model *model, const gtm_graphs_view *device_gra
 int gtm_fit(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, const int32_t *encoded_Y,
             int64_t first, int64_t count, int epochs);
 
+/* Clause-sharded learning over the GPUs of one box, one process per GPU (NO COUNTERPART IN THE REFERENCE, which is
+ * single-GPU).  Every rank holds the whole model and the whole graph set; during gtm_fit rank r learns clauses
+ * gtm_shard_range(world, r) and the kernels of all ranks exchange, per graph, their vote partials (and, for depth > 1,
+ * message bits and barrier arrivals) by direct stores / atomics into each other's buffers over NVLink.  Results do not
+ * depend on the number of ranks (draw streams are per clause).  Protocol, per graph set:
+ *   1. every rank: gtm_shard_prepare(model, dataset, world, rank, handle[64])   allocates the rank's buffers
+ *   2. the ranks exchange the 64-byte handles (any transport), rank order
+ *   3. every rank: gtm_shard_connect(model, dataset, handles[world][64])
+ *   4. every rank: the same sequence of gtm_fit calls (same ranges and epochs), all ranks inside each call at the same
+ *      time; AFTER every call the ranks must synchronise with each other (e.g. by gathering the updated shards:
+ *      gtm_get_ta_state / gtm_get_weights rows of gtm_shard_range, then gtm_set_* of the assembled arrays) before
+ *      the next call.  A rank that does not show up makes the others return GTM_ERR_TIMEOUT after a bounded wait. */
+int gtm_shard_range(gtm_model *model, int world, int rank, int *first_clause_out, int *number_of_clauses_out);
+int gtm_shard_prepare(gtm_model *model, gtm_dataset *dataset, int world, int rank, unsigned char *handle_out);
+int gtm_shard_connect(gtm_model *model, gtm_dataset *dataset, const unsigned char *handles);
+
 /* Replaces tm.py:814-851 (transform; kernels.py:671-691): clause outputs int32[count][CLAUSES] (0/1) and the
  * class sums int32[count][CLASSES] of graphs [first, first+count).  Either output may be NULL. */
 int gtm_transform(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
