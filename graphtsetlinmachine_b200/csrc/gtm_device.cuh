@@ -235,8 +235,9 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
                 if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
                 for (int b = 0; b < m.MB; ++b) {
                     const u32 bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
-                    for (int r = 0; r < scatter->world; ++r)
-                        atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
+                        if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
                 }
             }
         }

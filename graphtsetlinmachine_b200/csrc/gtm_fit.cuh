@@ -49,8 +49,9 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
         if (a.world == 1) {
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier) : "memory");
         } else {
-            for (int r = 0; r < a.world; ++r)
-                asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)      // constant indices: kernel parameters must not be indexed dynamically
+                if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
         }
         unsigned spins = 0;
         while (true) {
@@ -78,7 +79,9 @@ __device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, int par, u
     const size_t mine = (((size_t)par * a.world + a.rank) * gridDim.x + blockIdx.x) * K;
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
         const unsigned long long word = ((unsigned long long)(u32)s_sum[k] << 32) | tag;
-        for (int r = 0; r < a.world; ++r) *(volatile unsigned long long *)(a.exchange_peer[r] + mine + k) = word;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+            if (r < a.world) *(volatile unsigned long long *)(a.exchange_peer[r] + mine + k) = word;
         s_sum[k] = 0;
         s_total[k] = 0;
     }
@@ -156,10 +159,9 @@ constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of
 template <int MAXSB>
 __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
                                               bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
-                                              u64 pos0, int lane, u32 *pack, const u32 *pre)
+                                              u64 pos0, int lane, u32 *pack, const u32 *pre, float p)
 {
     const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
-    const float p = m.p_mask[layer];
     const bool all_ones = p >= 1.0f;         // every uniform is <= 1
     const u64 first_block = pos0 >> 2;
     const int shift = (int)(pos0 & 3);       // the layer's first draw sits `shift` bits into the packed stream
@@ -361,7 +363,7 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
 template <int MAXSB>
 __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView &gv, const ClauseView &cv, const FitArgs &a,
                                              const u32 *P, const Decision &dec, int npos, int c, int lane, u32 *pack,
-                                             const u32 *pre)
+                                             const u32 *pre, const float *p_mask)
 {
     const bool clause_true = dec.chosen != -1;
     const bool within = *cv.n_inc <= m.max_included;
@@ -371,7 +373,7 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
     for (int d = 0; d < m.D; ++d) {
         const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * a.max_nodes + node) * m.MW;
         pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), dec.upd_lo, a.update, clause_true, within, row, d > 0, pos, lane,
-                                     pack, pre);
+                                     pack, pre, p_mask[d]);
         if (pre) pre += npos * (d == 0 ? m.L0 : m.M) + 1;
     }
     if (lane == 0) *cv.pos = pos;
@@ -380,24 +382,42 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
 template <int MAXSB>
 __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
                                                 const FitArgs &a, const u32 *bits, const u32 *P, const int *s_target,
-                                                const float *s_thr, int c, int lane, u32 *pack)
+                                                const float *s_thr, int c, int lane, u32 *pack, const float *p_mask)
 {
     const Decision dec = clause_decide(m, gv, cv, a, bits, s_target, s_thr, c, lane);
-    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr);
+    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr, p_mask);
 }
 
 // Packed Bernoulli words of one (clause, layer, round) work item, written to the clause's pre-generated area.
 // Layer l of a clause with `npos` Type-I classes needs words [0, npos*W_l + (shift ? 1 : 0)) of the stream that starts
 // at Philox block pos_l >> 2; round q yields words 4q .. 4q+3.
 __device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, int layer, u64 pos_l, int npos, int q,
-                                                    u32 *dst, int lane)
+                                                    u32 *dst, int lane, float p)
 {
     const int W = layer == 0 ? m.L0 : m.M;
     const int need = npos * W + ((pos_l & 3) ? 1 : 0);
-    const u32 nib = bernoulli_nibbles(m, c, (pos_l >> 2) + (u64)q * 32 + lane, m.p_mask[layer], lane);
+    const u32 nib = bernoulli_nibbles(m, c, (pos_l >> 2) + (u64)q * 32 + lane, p, lane);
     const u32 word = __reduce_or_sync(0xffu << (lane & 24), nib);
     const int j = 4 * q + (lane >> 3);
     if ((lane & 7) == 0 && j < need) dst[j] = word;
+}
+
+// Per-layer constants and peer pointers that the kernels index at run time are copied from the kernel parameters
+// to shared memory once (constant indices here): a dynamically indexed parameter array would be spilled to local
+// memory and every access to it could miss the small L1 that is left beside the shared-memory carve-out.
+struct FitShared {
+    float p_mask[kMaxDepth];
+    u32 *P_peer[kMaxRanks][2];
+};
+
+__device__ __forceinline__ void fill_fit_shared(FitShared *fs, const DevModel &m, const FitArgs &a)
+{
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int l = 0; l < kMaxDepth; ++l) fs->p_mask[l] = m.p_mask[l];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) { fs->P_peer[r][0] = a.P_peer[r][0]; fs->P_peer[r][1] = a.P_peer[r][1]; }
+    }
 }
 
 // Message rows of the OTHER parity are cleared for the graph after this one: every warp has finished the previous
@@ -409,7 +429,7 @@ __device__ __forceinline__ void clear_next_messages(const DevModel &m, const Dev
     const int64_t nxt = i + 1 < a.count ? e + 1 : a.first;
     const size_t rows = (size_t)g.n_nodes[nxt] * m.MW;
     for (int dd = 0; dd < m.D - 1; ++dd)
-        for (size_t t = gthread; t < rows; t += gthreads) a.P_pair[par ^ 1][(size_t)dd * a.max_nodes * m.MW + t] = 0;
+        for (size_t t = gthread; t < rows; t += gthreads) (par ? a.P_pair[0] : a.P_pair[1])[(size_t)dd * a.max_nodes * m.MW + t] = 0;
 }
 
 #define GTM_LAP(acc) do { if (timer) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)

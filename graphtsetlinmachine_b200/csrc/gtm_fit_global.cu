@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     int *s_sum = s_mem, *s_total = s_mem + m.K, *s_target = s_mem + 2 * m.K;
     float *s_thr = reinterpret_cast<float *>(s_mem + 3 * m.K);
     __shared__ u32 s_pack[16][kPackWords];
+    __shared__ FitShared s_fs;
+    fill_fit_shared(&s_fs, m, a);
     const int lane = threadIdx.x & 31;
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
     const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -50,7 +52,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
             const int64_t e = a.first + i;
             const int par = (int)(step & 1);
             const GraphView gv = global_graph(g, e, m.L0);
-            u32 *P = a.P_pair[par];
+            u32 *P = par ? a.P_pair[1] : a.P_pair[0];
 
             for (int d = 0; d < m.D; ++d) {
                 const bool last = d == m.D - 1;
@@ -63,7 +65,8 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 }
                 ScatterTargets targets;
                 targets.world = a.world;
-                for (int r = 0; r < a.world; ++r) targets.base[r] = a.P_peer[r][par] + (size_t)d * layer_words;
+                #pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
                     const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
                     clause_feedback<MAXSB>(m, gv, cv, a, cno_row(sc, m.C, m.D - 1, c), P, s_target, s_thr, c, lane,
-                                           s_pack[threadIdx.x >> 5]);
+                                           s_pack[threadIdx.x >> 5], s_fs.p_mask);
                 }
             }
             __syncthreads();   // s_total is rewritten by the next graph

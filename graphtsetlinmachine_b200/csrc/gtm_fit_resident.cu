@@ -40,6 +40,8 @@ template <int MAXSB>
 __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGraphs g, FitArgs a)
 {
     extern __shared__ __align__(16) int s_mem[];
+    __shared__ FitShared s_fs;
+    fill_fit_shared(&s_fs, m, a);
     const int KP = (m.K + 3) & ~3;
     int *s_sum = s_mem, *s_total = s_mem + KP, *s_y = s_mem + 2 * KP;      // s_y: [2][KP]
     int *s_target = s_mem + 4 * KP;
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             gv.X = g.X + (size_t)base * m.L0; gv.type = g.node_type + base; gv.degree = g.degree + base;
             gv.eidx = g.edge_index + base; gv.edge = g.edge; gv.e_off = 0;
         }
-        u32 *P = a.P_pair[par];
+        u32 *P = par ? a.P_pair[1] : a.P_pair[0];
         const int *y = s_y + par * KP;
         GTM_LAP(t_x0);
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
@@ -173,7 +175,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             }
             ScatterTargets targets;
             targets.world = a.world;
-            for (int r = 0; r < a.world; ++r) targets.base[r] = a.P_peer[r][par] + (size_t)d * layer_words;
+            #pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 for (int l = 0; l < m.D; ++l) {
                     const int W = l == 0 ? m.L0 : m.M;
                     need += npos * W + 1;
-                    if (npos > 0 && m.p_mask[l] < 1.0f) items += (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
+                    if (npos > 0 && s_fs.p_mask[l] < 1.0f) items += (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
                     pos_l += (u64)npos * W * 32;
                 }
                 int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
@@ -242,8 +245,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                     u32 *dst = s_pre + (size_t)ci * a.pre_words;
                     for (int l = 0; l < m.D; ++l) {
                         const int W = l == 0 ? m.L0 : m.M;
-                        const int rounds = m.p_mask[l] < 1.0f ? (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2 : 0;
-                        if (r < rounds) { generate_mask_round(m, c_lo + ci, l, pos_l, npos, r, dst, lane); break; }
+                        const int rounds = s_fs.p_mask[l] < 1.0f ? (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2 : 0;
+                        if (r < rounds) { generate_mask_round(m, c_lo + ci, l, pos_l, npos, r, dst, lane, s_fs.p_mask[l]); break; }
                         r -= rounds;
                         dst += npos * W + 1;
                         pos_l += (u64)npos * W * 32;
@@ -259,12 +262,12 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 dec.pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
                 dec.upd_lo = rec[5 + lane];
                 clause_apply<MAXSB>(m, gv, cv, a, P, dec, rec[1], c, lane, s_pack + warp * kPackWords,
-                                    rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr);
+                                    rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr, s_fs.p_mask);
             }
         } else {
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
-                clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords);
+                clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords, s_fs.p_mask);
             }
         }
         GTM_LAP(t_x3);
