@@ -234,7 +234,8 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
                 const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
                 if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
                 for (int b = 0; b < m.MB; ++b) {
-                    const u32 bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                    u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
+                    if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
 #pragma unroll
                     for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
                         if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));

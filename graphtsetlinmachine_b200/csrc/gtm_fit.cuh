@@ -204,7 +204,10 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
                     __syncwarp();
                 }
                 int local = 0;
-                for (int kk = k8; kk < min(kn, k8 + 8); ++kk) {
+                u32 todo = (__ballot_sync(kFull, vals != 0 && lane < kn) >> k8) & 0xffu;    // classes with feedback, in order
+                while (todo) {
+                    const int kk = k8 + __ffs(todo) - 1;
+                    todo &= todo - 1;
                     const int u = __shfl_sync(kFull, vals, kk);
                     if (u > 0) {
                         u32 mask = kFull;
@@ -324,32 +327,48 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
     }
     const bool clause_true = chosen != -1;
 
-    // 2. feedback type per class + weight move
+    // 2. feedback type per class + weight move, 16 classes per pass, one class per lane.
+    //    Class k reads its first uniform at offset o_k = k + #{j < k : negative target and its first uniform kept it},
+    //    which is the reference's short-circuit order (kernels.py:384).  The offsets are the unique fixed point of that
+    //    recurrence; it is found by re-evaluating all lanes until the set of kept classes stops changing (one more
+    //    round than there are kept negative classes, usually two).
     int upd_lo = 0;
     for (int kb = 0; kb < m.K; kb += 16) {
         const int kn = min(16, m.K - kb);
         const float uni = to_uniform(draw_at(m, c, pos + lane));     // only the first (at most 2*kn) are consumed
-        int wgt = 0, sign = 1;
-        if (lane < kn) {
+        const bool mine = lane < kn;
+        int wgt = 0, sign = 1, t = 1;
+        float thr = 0.0f;
+        if (mine) {
             wgt = cv.wgt[(size_t)(kb + lane) * cv.wstride];
             sign = (wgt >= 0) - (wgt < 0);
+            t = s_target[kb + lane];
+            thr = s_thr[kb + lane];
         }
-        int used = 0;
-        for (int kk = 0; kk < kn; ++kk) {
-            const int t = s_target[kb + kk];
-            bool skip = false;
-            if (t == -1) skip = __shfl_sync(kFull, uni, used++) > m.q_keep_f;
-            if (!skip) skip = __shfl_sync(kFull, uni, used++) > s_thr[kb + kk];
-            const int upd = skip ? 0 : t * __shfl_sync(kFull, sign, kk);
-            if (lane == kk) {
-                if (upd > 0 && clause_true && abs(wgt) < INT_MAX) wgt += sign;
-                else if (upd < 0 && clause_true) wgt -= sign;
-                a.update[(size_t)(kb + kk) * m.C + c] = upd;
-                if (upd != 0 && clause_true) cv.wgt[(size_t)(kb + kk) * cv.wstride] = wgt;
-            }
-            if (kb + kk < 32 && lane == kb + kk) upd_lo = upd;
+        const u32 below = (1u << lane) - 1u;
+        u32 kept = 0, seen;
+        int off;
+        do {
+            seen = kept;
+            off = lane + __popc(kept & below);
+            const float u1 = __shfl_sync(kFull, uni, off & 31);
+            kept = __ballot_sync(kFull, mine && t == -1 && !(u1 > m.q_keep_f));
+        } while (kept != seen);
+        const float u1 = __shfl_sync(kFull, uni, off & 31);
+        const float u2 = __shfl_sync(kFull, uni, (off + 1) & 31);
+        // negative target: dropped when the first uniform exceeds q/(K-1), else decided by the second; positive
+        // target: decided by its only uniform
+        const bool skip = t == -1 ? ((u1 > m.q_keep_f) || (u2 > thr)) : (u1 > thr);
+        const int upd = (mine && !skip) ? t * sign : 0;
+        if (mine) {
+            if (upd > 0 && clause_true && abs(wgt) < INT_MAX) wgt += sign;
+            else if (upd < 0 && clause_true) wgt -= sign;
+            a.update[(size_t)(kb + lane) * m.C + c] = upd;
+            if (upd != 0 && clause_true) cv.wgt[(size_t)(kb + lane) * cv.wstride] = wgt;
         }
-        pos += used;
+        if (kb == 0) upd_lo = upd;                                    // classes 0..15 sit in lanes 0..15
+        else if (kb == 16) { const int moved = __shfl_sync(kFull, upd, lane & 15); if (lane >= 16) upd_lo = moved; }
+        pos += kn + __popc(kept);
     }
     if (m.K > 32) __syncwarp();   // classes beyond 31 are read back from a.update
     if (lane == 0) a.clause_node[c] = chosen;
@@ -366,6 +385,10 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
                                              const u32 *pre, const float *p_mask)
 {
     const bool clause_true = dec.chosen != -1;
+    if (m.K <= 32 && __ballot_sync(kFull, dec.upd_lo != 0) == 0) {      // no feedback for this clause: nothing drawn, nothing changes
+        if (lane == 0) *cv.pos = dec.pos;
+        return;
+    }
     const bool within = *cv.n_inc <= m.max_included;
     const int node = clause_true ? dec.chosen : 0;
     u64 pos = dec.pos;

@@ -50,8 +50,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     u32 *s_stage = reinterpret_cast<u32 *>(s_size + 12);                    // [2][kStageWords]
     u32 *s_pack = s_stage + 2 * kStageWords;                                // [12][kPackWords]
     int *s_rec = reinterpret_cast<int *>(s_pack + 12 * kPackWords);       // [clauses_per_cta][kRecWords] decisions of the step
-    int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // [clauses_per_cta + 1] (padded to even)
-    u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + ((a.clauses_per_cta + 2) & ~1));   // [clauses_per_cta][pre_words]
+    int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // work-item table: entries, items, then (clause, first item) pairs
+    u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + 2 * a.clauses_per_cta + 2);   // [clauses_per_cta][pre_words]
     u32 *s_clauses = s_pre + (size_t)a.clauses_per_cta * a.pre_words;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
@@ -120,6 +120,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         }
     }
     for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
+    if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }
     fetch_sizes(0, e_cur);
     fetch_sizes(1, e_nxt);
     wait_copies();
@@ -159,10 +160,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         }
         u32 *P = par ? a.P_pair[1] : a.P_pair[0];
         const int *y = s_y + par * KP;
-        GTM_LAP(t_x0);
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
         fetch_sizes(step + 2, e_nxt2);
-        GTM_LAP(t_x1);
 
         for (int d = 0; d < m.D; ++d) {
             const bool last = d == m.D - 1;
@@ -186,7 +185,6 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
             }
         }
-        GTM_LAP(t_x2);
         __syncthreads();
         GTM_LAP(t_eval);
         if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
@@ -212,36 +210,33 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 if (lane == 0) {
                     rec[0] = dec.chosen; rec[1] = npos;
                     rec[2] = (int)(u32)dec.pos; rec[3] = (int)(u32)(dec.pos >> 32);
-                    rec[4] = need <= a.pre_words ? items : -1;           // -1: does not fit, the clause generates on its own
+                    const bool fits_pre = need <= a.pre_words;
+                    rec[4] = fits_pre ? items : -1;                      // -1: does not fit, the clause generates on its own
+                    // this clause's work items take the next `items` numbers; (clause, first number) goes to the item table
+                    if (fits_pre && items > 0) {
+                        const int slot = atomicAdd(&s_item_off[0], 1);
+                        const int firsti = atomicAdd(&s_item_off[1], items);
+                        s_item_off[2 + 2 * slot] = c - c_lo;
+                        s_item_off[3 + 2 * slot] = firsti;
+                    }
                 }
                 rec[5 + lane] = dec.upd_lo;
             }
             __syncthreads();
-            if (warp == 0) {      // exclusive prefix of the work items per clause
-                int run = 0;
-                for (int cb = 0; cb < c_hi - c_lo; cb += 32) {
-                    const int it = cb + lane < c_hi - c_lo ? max(0, s_rec[(size_t)(cb + lane) * kRecWords + 4]) : 0;
-                    int incl = it;
-#pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-                        const int t = __shfl_up_sync(kFull, incl, d);
-                        if (lane >= d) incl += t;
-                    }
-                    if (cb + lane < c_hi - c_lo) s_item_off[cb + lane] = run + incl - it;
-                    run += __shfl_sync(kFull, incl, 31);
-                }
-                if (lane == 0) s_item_off[c_hi - c_lo] = run;
-            }
-            __syncthreads();
+            GTM_LAP(t_x0);
+            GTM_LAP(t_x1);
             {
-                const int total = s_item_off[c_hi - c_lo];
-                int ci = 0;
+                const int entries = s_item_off[0], total = s_item_off[1];
                 for (int i = warp; i < total; i += nwarps) {
-                    while (i >= s_item_off[ci + 1]) ++ci;
+                    int ci = 0, firsti = 0;
+                    for (int t = 0; t < entries; ++t) {                   // the entry whose range holds item i
+                        const int f = s_item_off[3 + 2 * t];
+                        if (f <= i && f >= firsti) { firsti = f; ci = s_item_off[2 + 2 * t]; }
+                    }
                     const int *rec = s_rec + (size_t)ci * kRecWords;
                     const int npos = rec[1];
                     u64 pos_l = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
-                    int r = i - s_item_off[ci];
+                    int r = i - firsti;
                     u32 *dst = s_pre + (size_t)ci * a.pre_words;
                     for (int l = 0; l < m.D; ++l) {
                         const int W = l == 0 ? m.L0 : m.M;
@@ -254,6 +249,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 }
             }
             __syncthreads();
+            if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }     // next step's item table starts empty
+            GTM_LAP(t_x2);
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 const int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
@@ -338,7 +335,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
         const int cpb = (d.C + grid - 1) / grid;
         grid = (d.C + cpb - 1) / cpb;
         const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) +
-                            ((size_t)cpb * kRecWords + ((cpb + 2) & ~1) + (size_t)cpb * pre_words) * sizeof(int) +
+                            ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
                             (size_t)cpb * words * sizeof(u32);
         if (smem > 200 * 1024) continue;
         if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
