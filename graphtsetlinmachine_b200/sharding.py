@@ -8,7 +8,7 @@ the process group (NCCL on GPUs, gloo in the CPU tests); the scoring itself is w
 
 import numpy as np
 
-__all__ = ["balanced_ranges", "gather_rows", "GraphShardScorer"]
+__all__ = ["balanced_ranges", "clause_shard", "gather_rows", "GraphShardScorer"]
 
 
 def balanced_ranges(number_of_graph_nodes, parts):
@@ -24,6 +24,14 @@ def balanced_ranges(number_of_graph_nodes, parts):
         cuts.append(min(max(cut, cuts[-1]), n))
     cuts.append(n)
     return [(cuts[p], cuts[p + 1] - cuts[p]) for p in range(parts)]
+
+
+def clause_shard(number_of_clauses, world, rank):
+    """(first clause, number of clauses) that ``rank`` learns when fit is sharded over ``world`` ranks: equal shards of
+    ``ceil(C / world)`` clauses, the last ones shorter or empty (the rule of ``gtm_shard_range`` in the C ABI)."""
+    per = (number_of_clauses + world - 1) // world
+    first = min(number_of_clauses, rank * per)
+    return first, min(number_of_clauses, first + per) - first
 
 
 def gather_rows(local_rows, counts, group=None):

@@ -9,7 +9,7 @@ import sys
 import numpy as np
 import pytest
 
-from graphtsetlinmachine_b200.sharding import balanced_ranges
+from graphtsetlinmachine_b200.sharding import balanced_ranges, clause_shard
 
 
 def test_balanced_ranges_cover_everything_in_order():
@@ -24,6 +24,16 @@ def test_balanced_ranges_cover_everything_in_order():
         if n >= 10 * parts:
             loads = [nodes[f:f + c].sum() for f, c in ranges]
             assert max(loads) <= nodes.sum() / parts + nodes.max()
+
+
+def test_clause_shards_partition_the_clauses():
+    for clauses in (1, 7, 10, 33, 2500, 20000):
+        for world in (1, 2, 3, 4, 8):
+            shards = [clause_shard(clauses, world, r) for r in range(world)]
+            assert shards[0][0] == 0 and sum(n for _, n in shards) == clauses
+            for (f0, n0), (f1, _) in zip(shards, shards[1:]):
+                assert f0 + n0 == f1 or (n0 == 0 and f1 == clauses)
+            assert max(n for _, n in shards) == (clauses + world - 1) // world
 
 
 def _worker(rank, world, port, tmpdir):
