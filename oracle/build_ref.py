@@ -120,13 +120,54 @@ def build(params, force=False, quiet=True):
     return out
 
 
+def gpu_so_path(params):
+    return os.path.join(REF_DIR, "refgpu_%s.so" % config_key(params))
+
+
+def build_gpu(params, force=False, quiet=True):
+    """The reference's kernel strings compiled with nvcc for sm_100a (its own `#include <curand_kernel.h>` stays) plus
+    ``oracle/ref_gpu_driver.inc``; returns the path or None when the checkout is absent and nothing was built earlier."""
+    p = normalise(params)
+    out = gpu_so_path(p)
+    if os.path.isfile(out) and not force:
+        return out
+    kernels_py = find_reference()
+    if kernels_py is None:
+        return None
+    spec = importlib.util.spec_from_file_location("_gtm_reference_kernels", kernels_py)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    unit = (
+        _defines(p) + mod.code_header + mod.code_update + mod.code_evaluate + mod.code_prepare
+        + mod.code_transform + mod.code_clauses + '\n#include "ref_gpu_driver.inc"\n'
+    )
+    os.makedirs(REF_DIR, exist_ok=True)
+    with tempfile.NamedTemporaryFile("w", suffix=".cu", dir=REF_DIR, delete=False) as f:
+        f.write(unit)
+        src = f.name
+    try:
+        cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-shared", "-Xcompiler", "-fPIC", "-w",
+               "-I", HERE, src, "-o", out + ".tmp"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("reference kernels failed to compile for the GPU:\n" + res.stderr[-4000:])
+        os.replace(out + ".tmp", out)
+    finally:
+        os.unlink(src)
+    if not quiet:
+        print("built", out)
+    return out
+
+
 if __name__ == "__main__":
     sys.path.insert(0, HERE)
-    from ref_configs import CONFIGS  # noqa: E402
+    from ref_configs import CONFIGS, GPU_CONFIGS  # noqa: E402
 
     missing = 0
     for name, params in CONFIGS.items():
         path = build(params, force="--force" in sys.argv, quiet=False)
+        if path is not None and name in GPU_CONFIGS:
+            build_gpu(params, force="--force" in sys.argv, quiet=False)
         if path is None:
             print("reference checkout not found; cannot build", name)
             missing += 1

@@ -19,3 +19,6 @@ CONFIGS = {
     "case_e": dict(classes=2, clauses=24, literals=42, threshold=10, max_nodes=9, message_size=33, message_bits=2,
                    max_included=3),
 }
+
+# sets that are also built for the GPU (the reference's kernels on the same B200, launched like the reference does)
+GPU_CONFIGS = ("noisy_xor", "vanilla_images", "case_b", "case_e")
