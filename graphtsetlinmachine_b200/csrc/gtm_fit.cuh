@@ -25,6 +25,8 @@ struct FitArgs {
     int clause_words;       // shared-memory words per clause
     int NC;                 // node words of the largest graph
     int pre_words;          // words per clause for pre-generated Type-I masks (0 = every clause generates its own)
+    int solo;               // one CTA learns the whole model: CTA barriers replace the grid barrier and the vote exchange
+    int p_smem_words;       // solo and depth > 1: message buffers (words per parity) live in that CTA's shared memory
     // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits
     // and barrier arrivals go to every rank's buffers through peer pointers.  world == 1: everything is local.
     int world, rank;
@@ -445,14 +447,12 @@ __device__ __forceinline__ void fill_fit_shared(FitShared *fs, const DevModel &m
 
 // Message rows of the OTHER parity are cleared for the graph after this one: every warp has finished the previous
 // graph (the last reader), and the next writer comes after the remaining synchronisations of this graph.
-__device__ __forceinline__ void clear_next_messages(const DevModel &m, const DevGraphs &g, const FitArgs &a, int par,
-                                                    int64_t i, int64_t e)
+__device__ __forceinline__ void clear_next_messages(const DevModel &m, const FitArgs &a, u32 *P_other, int next_nodes)
 {
     const size_t gthread = blockIdx.x * (size_t)blockDim.x + threadIdx.x, gthreads = (size_t)gridDim.x * blockDim.x;
-    const int64_t nxt = i + 1 < a.count ? e + 1 : a.first;
-    const size_t rows = (size_t)g.n_nodes[nxt] * m.MW;
+    const size_t rows = (size_t)next_nodes * m.MW;
     for (int dd = 0; dd < m.D - 1; ++dd)
-        for (size_t t = gthread; t < rows; t += gthreads) (par ? a.P_pair[0] : a.P_pair[1])[(size_t)dd * a.max_nodes * m.MW + t] = 0;
+        for (size_t t = gthread; t < rows; t += gthreads) P_other[(size_t)dd * a.max_nodes * m.MW + t] = 0;
 }
 
 #define GTM_LAP(acc) do { if (timer) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)

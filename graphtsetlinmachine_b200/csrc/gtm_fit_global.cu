@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                     arrivals += gridDim.x * a.world;
                     if (!grid_barrier(a, arrivals)) return;
                     GTM_LAP(t_bar);
-                    if (d == 1) clear_next_messages(m, g, a, par, i, e);
+                    if (d == 1) clear_next_messages(m, a, par ? a.P_pair[0] : a.P_pair[1], (int)g.n_nodes[i + 1 < a.count ? e + 1 : a.first]);
                 }
                 ScatterTargets targets;
                 targets.world = a.world;

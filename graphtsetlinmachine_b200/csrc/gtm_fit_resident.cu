@@ -53,6 +53,15 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // work-item table: entries, items, then (clause, first item) pairs
     u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + 2 * a.clauses_per_cta + 2);   // [clauses_per_cta][pre_words]
     u32 *s_clauses = s_pre + (size_t)a.clauses_per_cta * a.pre_words;
+    // one CTA learns the whole model: messages stay in shared memory, CTA barriers replace the grid-wide steps
+    const bool solo = a.solo != 0;
+    u32 *P_even = a.P_pair[0], *P_odd = a.P_pair[1];
+    if (a.p_smem_words > 0) {
+        P_even = s_clauses + (size_t)a.clauses_per_cta * a.clause_words;
+        P_odd = P_even + a.p_smem_words;
+        for (int t = threadIdx.x; t < 2 * a.p_smem_words; t += blockDim.x) P_even[t] = 0;
+        if (threadIdx.x == 0) { s_fs.P_peer[0][0] = P_even; s_fs.P_peer[0][1] = P_odd; }
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
@@ -158,7 +167,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             gv.X = g.X + (size_t)base * m.L0; gv.type = g.node_type + base; gv.degree = g.degree + base;
             gv.eidx = g.edge_index + base; gv.edge = g.edge; gv.e_off = 0;
         }
-        u32 *P = par ? a.P_pair[1] : a.P_pair[0];
+        u32 *P = par ? P_odd : P_even;
         const int *y = s_y + par * KP;
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
         fetch_sizes(step + 2, e_nxt2);
@@ -167,10 +176,14 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             const bool last = d == m.D - 1;
             if (d > 0) {
                 GTM_LAP(t_eval);
-                arrivals += gridDim.x * a.world;
-                if (!grid_barrier(a, arrivals)) return;
+                if (solo) {
+                    __syncthreads();
+                } else {
+                    arrivals += gridDim.x * a.world;
+                    if (!grid_barrier(a, arrivals)) return;
+                }
                 GTM_LAP(t_bar);
-                if (d == 1) clear_next_messages(m, g, a, par, i, e);
+                if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
             }
             ScatterTargets targets;
             targets.world = a.world;
@@ -187,7 +200,14 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         }
         __syncthreads();
         GTM_LAP(t_eval);
-        if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
+        if (solo) {
+            for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
+                s_total[k] = s_sum[k];
+                a.class_sum_tap[k] = s_sum[k];
+                s_sum[k] = 0;
+            }
+            __syncthreads();
+        } else if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
         GTM_LAP(t_tot);
         class_decision_inputs(m, s_total, y, s_target, s_thr);
         __syncthreads();
@@ -316,9 +336,9 @@ static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0; size_t smem = 0; };
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0; size_t smem = 0; };
 
-static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses)
+static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses, bool solo_allowed)
 {
     DevModel d = m->dm;
     d.C = n_clauses;   // clauses this rank learns
@@ -334,15 +354,25 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
         int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
         const int cpb = (d.C + grid - 1) / grid;
         grid = (d.C + cpb - 1) / cpb;
-        const size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) +
-                            ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
-                            (size_t)cpb * words * sizeof(u32);
+        size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) +
+                      ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
+                      (size_t)cpb * words * sizeof(u32);
         if (smem > 200 * 1024) continue;
+        // a model that one CTA learns alone needs no grid-wide step; its message buffers (two parities) then live in
+        // shared memory, which they must fit (messages written with atomics to global memory would need a device-scope
+        // acquire before they are read, i.e. the grid barrier)
+        const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
+        int solo = 0, p_smem_words = 0;
+        if (solo_allowed && grid == 1 && (d.D == 1 || smem + 2 * p_words * sizeof(u32) <= 96 * 1024)) {
+            solo = 1;
+            p_smem_words = (int)p_words;
+            smem += 2 * p_words * sizeof(u32);
+        }
         if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
         if ((long long)occ * m->sm_count < grid) continue;
-        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
+        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem; plan.solo = solo; plan.p_smem_words = p_smem_words;
         return plan;
     }
     return plan;
@@ -403,12 +433,13 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
         }
         ResidentPlan plan;
-        if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds, d.C);
+        if (!eval_only && m->opt_fit_kernel != 1) plan = plan_resident(m, ds, d.C, true);
         if (m->opt_fit_kernel == 2 && !eval_only && plan.grid == 0)
             return fail(GTM_ERR_ARG, "the model's state does not fit in shared memory; the state-resident learning kernel cannot run");
         resident = plan.grid > 0;
         grid = resident ? plan.grid : m->fit_grid;
         a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
+        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words;
         smem = plan.smem;
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
@@ -466,7 +497,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     const int per = shard_size(d.C, world);
     // every rank derives the same launch shape from the shard size (the last shard may be shorter; it runs the same grid)
     ResidentPlan plan;
-    if (m->opt_fit_kernel != 1) plan = plan_resident(m, ds, per);
+    if (m->opt_fit_kernel != 1) plan = plan_resident(m, ds, per, false);
     cm.resident = plan.grid > 0;
     if (cm.resident) {
         cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
