@@ -336,8 +336,18 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->fit_sc.P = ds->P_pair[0];
 
     // general scoring scratch: one slice per resident CTA
+    // depth > 1: the source-node message bits of a graph are accumulated in shared memory when they are small enough
+    // not to cost resident CTAs (flush_messages)
+    ds->score_part_words = 0;
+    ds->score_smem = (size_t)((d.K + 3) & ~3) * sizeof(int);
+    if (d.D > 1 && (size_t)ds->max_nodes * d.MW * sizeof(u32) <= 8 * 1024) {
+        ds->score_part_words = ds->max_nodes * d.MW;
+        ds->score_smem += (size_t)ds->score_part_words * sizeof(u32);
+    }
+    if (ds->score_smem > 48 * 1024)
+        GTM_CU(cudaFuncSetAttribute(score_graphs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
     int per_sm = 0;
-    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_graphs_kernel, 256, (size_t)d.K * sizeof(int)));
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_graphs_kernel, 256, ds->score_smem));
     ds->score_grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)m->sm_count * std::max(1, per_sm), v->number_of_graphs));
     ds->cno_stride = (size_t)2 * d.C * ds->NC;
     ds->P_stride = p_words;
@@ -417,8 +427,9 @@ static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int6
     ScoreArgs a;
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = clause_out_dev;
     a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
+    a.part_words = ds->score_part_words;
     const int grid = (int)std::min<int64_t>(ds->score_grid, count);
-    score_graphs_kernel<<<grid, 256, (size_t)m->dm.K * sizeof(int), m->stream>>>(m->dm, g, ds->score_sc, a);
+    score_graphs_kernel<<<grid, 256, ds->score_smem, m->stream>>>(m->dm, g, ds->score_sc, a);
     GTM_CU(cudaGetLastError());
     return GTM_OK;
 }
@@ -546,6 +557,7 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         ScoreArgs a;
         a.first = graph; a.count = 1; a.class_sums = sums; a.clause_outputs = nullptr;
         a.cno_stride = a.P_stride = a.ninc_stride = 0;
+        a.part_words = 0;
         EvalScratch sc = ds->fit_sc;
         sc.P = ds->P_pair[0];
         score_graphs_kernel<<<1, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
@@ -654,6 +666,7 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     ScoreArgs a;
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr;
     a.cno_stride = a.P_stride = a.ninc_stride = per_cta;                             // one contiguous slice per CTA
+    a.part_words = 0;
     score_graphs_kernel<<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
     GTM_CU(cudaGetLastError());
     return GTM_OK;

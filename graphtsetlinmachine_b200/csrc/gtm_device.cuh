@@ -165,8 +165,56 @@ struct ClauseView {
 constexpr int kMaxRanks = 8;
 struct ScatterTargets {
     int world;
+    u32 *local;            // CTA-local accumulation in shared memory [n][MW] of SOURCE-node bits (see flush_messages), or null
     u32 *base[kMaxRanks];
 };
+
+// Bits [32w, 32w+32) of the message vector `row` (MS bits in MW words) rotated up by t: bit j = row bit (j - t) mod MS.
+__device__ __forceinline__ u32 rotated_word(const u32 *row, int w, u32 t, int MS, int MW)
+{
+    if ((MS & 31) == 0) {
+        const u32 start = (u32)(32 * w + MS - (int)t);                 // t < MS
+        const u32 s0 = start >= (u32)MS ? start - (u32)MS : start;     // first source bit, a multiple-of-32 ring
+        const int i = (int)(s0 >> 5), sh = (int)(s0 & 31);
+        const u32 lo = row[i], hi = row[i + 1 < MW ? i + 1 : 0];
+        return __funnelshift_r(lo, hi, sh);
+    }
+    u32 out = 0;
+    for (int k = 0; k < 32; ++k) {
+        const int j = 32 * w + k;
+        if (j >= MS) break;
+        int src = j - (int)t;
+        if (src < 0) src += MS;
+        out |= ((row[src >> 5] >> (src & 31)) & 1u) << k;
+    }
+    return out;
+}
+
+// The message a node sends is the OR of the hypervector bits of the clauses that are true on it; along an edge of
+// type t it arrives rotated by t ((hv + t) mod MS, kernels.py:581).  So the clauses only mark their bits on the SOURCE
+// node in a CTA-local buffer (MB atomics per true clause-node pair, no edge walk), and once per CTA and layer this
+// routine walks the graph's edges and ORs the rotated source rows into the destination rows of every target buffer.
+// All threads of the CTA, between two CTA barriers; the local buffer is cleared by the caller afterwards.
+__device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW)
+{
+    const int items = gv.n * MW;
+    for (int i = threadIdx.x; i < items; i += blockDim.x) {
+        const int u = i / MW, w = i - u * MW;
+        const u32 *row = t.local + (size_t)u * MW;
+        const u32 e0 = gv.eidx[u] - gv.e_off, deg = gv.degree[u];
+        for (u32 k = 0; k < deg; ++k) {
+            const u32 dst = gv.edge[2 * (size_t)(e0 + k)];
+            u32 ty = gv.edge[2 * (size_t)(e0 + k) + 1];
+            if (dst >= (u32)gv.n) continue;                                // malformed edge: ignore, never fault
+            if (ty >= (u32)MS) ty %= (u32)MS;
+            const u32 v = rotated_word(row, w, ty, MS, MW);
+            if (v == 0) continue;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < t.world) atomicOr(t.base[r] + (size_t)dst * MW + w, v);
+        }
+    }
+}
 
 // One warp evaluates a clause at layer `d` over all nodes of a graph (lanes = the 32 nodes of a node word) and
 // writes the node-output words out[0..ceil(n/32)).  Layer 0 tests the node's literal row, layer d >= 1 the node's
@@ -183,9 +231,19 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
     const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
     const u32 my_type = (u32)(c % n_types);
 
-    // include count of this layer (kernels.py:251-277); lanes stride over words
+    // The layer's include words sit in lanes (word w0 + lane), fetched with one coalesced load per 32 words; layers of
+    // at most 64 words keep them in registers for all node words.  Only words with included literals are visited.
+    const bool cached = W <= 64;
+    u32 inc_a = 0, inc_b = 0;
+    if (cached) {
+        if (lane < W) inc_a = inc[lane] & (lane == W - 1 ? last_mask : kFull);
+        if (32 + lane < W) inc_b = inc[32 + lane] & (32 + lane == W - 1 ? last_mask : kFull);
+    }
+
+    // include count of this layer (kernels.py:251-277)
     int cnt = 0;
-    for (int w = lane; w < W; w += 32) cnt += __popc(inc[w] & (w == W - 1 ? last_mask : kFull));
+    if (cached) cnt = __popc(inc_a) + __popc(inc_b);
+    else for (int w = lane; w < W; w += 32) cnt += __popc(inc[w] & (w == W - 1 ? last_mask : kFull));
     cnt = __reduce_add_sync(kFull, cnt);
     if (lane == 0) *cv.n_inc = (d == 0 ? 0 : *cv.n_inc) + cnt;
 
@@ -203,25 +261,33 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
         ok = ok && gv.type[ok ? v : 0] == my_type;
         if (__any_sync(kFull, ok)) {
             const int vv = v < n ? v : 0;
-            if (wide) {
-                const uint4 *row = reinterpret_cast<const uint4 *>(gv.X + (size_t)vv * W);
-                for (int w4 = 0; w4 < W; w4 += 4) {
-                    u32 i0 = inc[w4], i1 = inc[w4 + 1], i2 = inc[w4 + 2], i3 = inc[w4 + 3];
-                    if (w4 + 4 == W) i3 &= last_mask;
-                    if ((i0 | i1 | i2 | i3) == 0) continue;                  // uniform
-                    const uint4 x = row[w4 >> 2];
-                    ok = ok && (((i0 & ~x.x) | (i1 & ~x.y) | (i2 & ~x.z) | (i3 & ~x.w)) == 0);
-                    if (!__any_sync(kFull, ok)) break;                       // warp-ballot early exit
-                }
-            } else {
-                const u32 *row = d == 0 ? gv.X + (size_t)vv * W : Pread + (size_t)vv * m.MW;
-                for (int w = 0; w < W; ++w) {
-                    u32 iw = inc[w];
-                    if (w == W - 1) iw &= last_mask;
-                    if (iw == 0) continue;                                   // uniform
-                    const u32 x = d == 0 ? row[w] : msg_word(row, w, m.MS, m.MW);
-                    ok = ok && ((iw & ~x) == 0);
-                    if (!__any_sync(kFull, ok)) break;
+            const u32 *row = d == 0 ? gv.X + (size_t)vv * W : Pread + (size_t)vv * m.MW;
+            bool alive = true;
+            for (int w0 = 0; w0 < W && alive; w0 += 32) {
+                u32 iw_l;
+                if (cached) iw_l = w0 == 0 ? inc_a : inc_b;
+                else iw_l = w0 + lane < W ? inc[w0 + lane] & (w0 + lane == W - 1 ? last_mask : kFull) : 0u;
+                u32 nz = __ballot_sync(kFull, iw_l != 0);
+                if (wide) {
+                    nz = (nz | (nz >> 1) | (nz >> 2) | (nz >> 3)) & 0x11111111u;      // groups of four words with an included literal
+                    while (nz) {
+                        const int b = __ffs(nz) - 1;
+                        nz &= nz - 1;
+                        const u32 i0 = __shfl_sync(kFull, iw_l, b), i1 = __shfl_sync(kFull, iw_l, b + 1),
+                                  i2 = __shfl_sync(kFull, iw_l, b + 2), i3 = __shfl_sync(kFull, iw_l, b + 3);
+                        const uint4 x = reinterpret_cast<const uint4 *>(row)[(w0 + b) >> 2];
+                        ok = ok && (((i0 & ~x.x) | (i1 & ~x.y) | (i2 & ~x.z) | (i3 & ~x.w)) == 0);
+                        if (!__any_sync(kFull, ok)) { alive = false; break; }            // warp-ballot early exit
+                    }
+                } else {
+                    while (nz) {
+                        const int b = __ffs(nz) - 1;
+                        nz &= nz - 1;
+                        const u32 iw = __shfl_sync(kFull, iw_l, b);
+                        const u32 x = d == 0 ? row[w0 + b] : msg_word(row, w0 + b, m.MS, m.MW);
+                        ok = ok && ((iw & ~x) == 0);
+                        if (!__any_sync(kFull, ok)) { alive = false; break; }
+                    }
                 }
             }
         }
@@ -229,16 +295,28 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
         if (lane == 0) out[j] = word;
         any |= word;
         if (scatter && ok) {
-            const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
-            for (u32 k = 0; k < deg; ++k) {
-                const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
-                if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
+            if (scatter->local) {
+                // mark the clause's hypervector bits on this (source) node; most are there already
                 for (int b = 0; b < m.MB; ++b) {
-                    u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
-                    if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                    u32 bit = cv.hv[b];
+                    if (bit >= (u32)m.MS) bit %= (u32)m.MS;
+                    u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
+                    const u32 mbit = 1u << (bit & 31);
+                    if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
+                }
+            } else {
+                const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
+                for (u32 k = 0; k < deg; ++k) {
+                    const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
+                    if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
+                    for (int b = 0; b < m.MB; ++b) {
+                        u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
+                        if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                        const u32 mbit = 1u << (bit & 31);
 #pragma unroll
-                    for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
-                        if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), 1u << (bit & 31));
+                        for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
+                            if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), mbit);
+                    }
                 }
             }
         }

@@ -25,6 +25,8 @@ struct FitArgs {
     int clause_words;       // shared-memory words per clause
     int NC;                 // node words of the largest graph
     int pre_words;          // words per clause for pre-generated Type-I masks (0 = every clause generates its own)
+    int stage;              // the state-resident kernel has its two graph staging buffers (0: every graph is read in place)
+    int part_words;         // > 0: shared-memory words per CTA that accumulate one layer's messages before they are merged
     int solo;               // one CTA learns the whole model: CTA barriers replace the grid barrier and the vote exchange
     int p_smem_words;       // solo and depth > 1: message buffers (words per parity) live in that CTA's shared memory
     // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits

@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     extern __shared__ int s_mem[];   // [K] running partial, [K] totals, [K] targets, [K] thresholds
     int *s_sum = s_mem, *s_total = s_mem + m.K, *s_target = s_mem + 2 * m.K;
     float *s_thr = reinterpret_cast<float *>(s_mem + 3 * m.K);
+    u32 *s_part = a.part_words > 0 ? reinterpret_cast<u32 *>(s_mem + ((4 * m.K + 3) & ~3)) : nullptr;   // message accumulation
     __shared__ u32 s_pack[16][kPackWords];
     __shared__ FitShared s_fs;
     fill_fit_shared(&s_fs, m, a);
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     unsigned arrivals = a.barrier_base;
 
     for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
+    for (int t = threadIdx.x; t < a.part_words; t += blockDim.x) s_part[t] = 0;
     __syncthreads();
     if (a.world > 1 && m.D > 1) {
         // clause-sharded start: every rank clears its own message buffers (peers will OR into them), then all ranks meet
@@ -65,6 +67,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 }
                 ScatterTargets targets;
                 targets.world = a.world;
+                targets.local = (!last && s_part != nullptr && gv.n * m.MW <= a.part_words) ? s_part : nullptr;
                 #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
@@ -74,6 +77,12 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                                                       last ? nullptr : &targets, lane);
                     if (last && any)
                         for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], m.weights[(size_t)k * m.C + c]);
+                }
+                if (targets.local) {        // this CTA's share of the layer's messages, merged before the grid barrier
+                    __syncthreads();
+                    flush_messages(targets, gv, m.MS, m.MW);
+                    __syncthreads();
+                    for (int t = threadIdx.x; t < gv.n * m.MW; t += blockDim.x) targets.local[t] = 0;
                 }
             }
             __syncthreads();

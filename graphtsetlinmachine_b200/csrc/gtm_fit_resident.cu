@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     float *s_thr = reinterpret_cast<float *>(s_mem + 5 * KP);
     int *s_size = s_mem + 6 * KP;                                           // [3][4]: n, first node, first edge row, edge rows
     u32 *s_stage = reinterpret_cast<u32 *>(s_size + 12);                    // [2][kStageWords]
-    u32 *s_pack = s_stage + 2 * kStageWords;                                // [12][kPackWords]
+    u32 *s_pack = s_stage + (a.stage ? 2 * kStageWords : 0);                                // [12][kPackWords]
     int *s_rec = reinterpret_cast<int *>(s_pack + 12 * kPackWords);       // [clauses_per_cta][kRecWords] decisions of the step
     int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // work-item table: entries, items, then (clause, first item) pairs
     u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + 2 * a.clauses_per_cta + 2);   // [clauses_per_cta][pre_words]
@@ -61,6 +61,11 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         P_odd = P_even + a.p_smem_words;
         for (int t = threadIdx.x; t < 2 * a.p_smem_words; t += blockDim.x) P_even[t] = 0;
         if (threadIdx.x == 0) { s_fs.P_peer[0][0] = P_even; s_fs.P_peer[0][1] = P_odd; }
+    }
+    u32 *s_part = nullptr;      // message accumulation of one layer (clause-shared buffers are then touched once per word)
+    if (a.part_words > 0) {
+        s_part = s_clauses + (size_t)a.clauses_per_cta * a.clause_words;
+        for (int t = threadIdx.x; t < a.part_words; t += blockDim.x) s_part[t] = 0;
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
@@ -87,7 +92,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     int64_t e_cur = a.first, e_nxt = a.count > 1 ? a.first + 1 : a.first;
     int64_t e_nxt2 = a.count > 2 ? a.first + 2 : (a.count == 2 ? a.first : a.first);
     auto advance = [&](int64_t e) { return e + 1 < a.first + a.count ? e + 1 : a.first; };
-    auto fits = [&](const int *sz) { return sz[0] <= kStageNodes && sz[0] * m.L0 <= kStageRowWords && sz[3] <= kStageEdges; };
+    auto fits = [&](const int *sz) { return a.stage != 0 && sz[0] <= kStageNodes && sz[0] * m.L0 <= kStageRowWords && sz[3] <= kStageEdges; };
     // sizes of the graph of step st -> s_size[st % 3]   (four independent loads)
     auto fetch_sizes = [&](u64 st, int64_t e) {
         if (threadIdx.x < 4 && st < steps) {
@@ -187,6 +192,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             }
             ScatterTargets targets;
             targets.world = a.world;
+            targets.local = (!last && s_part != nullptr && gv.n * m.MW <= a.part_words) ? s_part : nullptr;
             #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
@@ -196,6 +202,12 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                                                   last ? nullptr : &targets, lane);
                 if (last && any)
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
+            }
+            if (targets.local) {            // this CTA's share of the layer's messages, merged before the grid barrier
+                __syncthreads();
+                flush_messages(targets, gv, m.MS, m.MW);
+                __syncthreads();
+                for (int t = threadIdx.x; t < gv.n * m.MW; t += blockDim.x) targets.local[t] = 0;
             }
         }
         __syncthreads();
@@ -336,7 +348,7 @@ static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0; size_t smem = 0; };
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1; size_t smem = 0; };
 
 static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses, bool solo_allowed)
 {
@@ -350,30 +362,41 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     // cooperative mask generation: layers of at most 32 words, at most 32 classes; room for 8 Type-I classes per clause
     int pre_words = 0;
     if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
+    const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
+    const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
     for (int per_sm = 2; per_sm >= 1; --per_sm) {
-        int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
-        const int cpb = (d.C + grid - 1) / grid;
-        grid = (d.C + cpb - 1) / cpb;
-        size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + 2 * (size_t)kStageWords + 12 * (size_t)kPackWords) * sizeof(int) +
-                      ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
-                      (size_t)cpb * words * sizeof(u32);
-        if (smem > 200 * 1024) continue;
-        // a model that one CTA learns alone needs no grid-wide step; its message buffers (two parities) then live in
-        // shared memory, which they must fit (messages written with atomics to global memory would need a device-scope
-        // acquire before they are read, i.e. the grid barrier)
-        const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
-        int solo = 0, p_smem_words = 0;
-        if (solo_allowed && grid == 1 && (d.D == 1 || smem + 2 * p_words * sizeof(u32) <= 96 * 1024)) {
-            solo = 1;
-            p_smem_words = (int)p_words;
-            smem += 2 * p_words * sizeof(u32);
+        // choices at the same occupancy, in order of preference: message accumulation in shared memory with and without
+        // the graph staging buffers, then staging alone
+        const bool part_possible = d.D > 1 && layer_bytes <= 64 * 1024;
+        for (int choice = part_possible ? 0 : 2; choice < 3; ++choice) {
+            const int with_part = choice < 2, stage = choice != 1;
+            int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
+            const int cpb = (d.C + grid - 1) / grid;
+            grid = (d.C + cpb - 1) / cpb;
+            size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + (stage ? 2 * (size_t)kStageWords : 0) + 12 * (size_t)kPackWords) * sizeof(int) +
+                          ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
+                          (size_t)cpb * words * sizeof(u32);
+            // a model that one CTA learns alone needs no grid-wide step; its message buffers (two parities) then live in
+            // shared memory, which they must fit (messages written with atomics to global memory would need a device-scope
+            // acquire before they are read, i.e. the grid barrier)
+            int solo = 0, p_smem_words = 0, part_words = 0;
+            if (solo_allowed && grid == 1 && (d.D == 1 || smem + 2 * p_words * sizeof(u32) <= 96 * 1024)) {
+                solo = 1;
+                p_smem_words = (int)p_words;
+                smem += 2 * p_words * sizeof(u32);
+            } else if (with_part) {
+                part_words = ds->max_nodes * d.MW;
+                smem += layer_bytes;
+            }
+            if (smem > 200 * 1024) continue;
+            if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
+            int occ = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
+            if ((long long)occ * m->sm_count < grid) continue;
+            plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
+            plan.solo = solo; plan.p_smem_words = p_smem_words; plan.part_words = part_words; plan.stage = stage;
+            return plan;
         }
-        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
-        int occ = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
-        if ((long long)occ * m->sm_count < grid) continue;
-        plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem; plan.solo = solo; plan.p_smem_words = p_smem_words;
-        return plan;
     }
     return plan;
 }
@@ -419,7 +442,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
         }
         resident = cm.resident; grid = cm.grid;
-        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words;
+        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage;
         smem = cm.smem;
     } else {
         a.world = 1; a.rank = 0; a.c_begin = 0; a.c_end = d.C;
@@ -439,7 +462,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         resident = plan.grid > 0;
         grid = resident ? plan.grid : m->fit_grid;
         a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
-        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words;
+        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage;
         smem = plan.smem;
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
@@ -455,7 +478,11 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     } else {
         fn = fit_global_kernel(d.SB);
         block = m->fit_block;
-        smem = 4 * (size_t)d.K * sizeof(int);
+        // one layer's messages are accumulated per CTA in shared memory when a layer takes at most 64 KB
+        const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
+        a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 64 * 1024) ? ds->max_nodes * d.MW : 0;
+        smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + (size_t)a.part_words * sizeof(u32);
+        if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &sc, &a, &eval_only};
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
     }
@@ -501,7 +528,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     cm.resident = plan.grid > 0;
     if (cm.resident) {
         cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
-        cm.pre_words = plan.pre_words; cm.smem = plan.smem;
+        cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.smem = plan.smem;
     } else {
         const int warps = m->fit_block / 32;
         cm.grid = std::max(1, std::min(m->fit_grid, (per + warps - 1) / warps));

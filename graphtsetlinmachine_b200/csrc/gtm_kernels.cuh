@@ -66,11 +66,13 @@ struct ScoreArgs {
     int *class_sums;      // [count][K]
     int *clause_outputs;  // optional [count][C] (transform)
     size_t cno_stride, P_stride, ninc_stride;  // per-CTA scratch strides (elements)
+    int part_words;       // > 0: shared-memory words (after the vote partial) that accumulate one layer's messages
 };
 
 __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs g, EvalScratch sc0, ScoreArgs a)
 {
-    extern __shared__ int s_sum[];   // [K]
+    extern __shared__ int s_sum[];   // [K], then the message accumulation words
+    u32 *s_part = a.part_words > 0 ? reinterpret_cast<u32 *>(s_sum + ((m.K + 3) & ~3)) : nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     EvalScratch sc = sc0;
     sc.cno += blockIdx.x * a.cno_stride;
@@ -83,8 +85,10 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
         const GraphView gv = global_graph(g, e, m.L0);
         const int n = gv.n;
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
+        const bool part = s_part != nullptr && n * m.MW <= a.part_words;     // source-node message bits fit the shared buffer
         if (m.D > 1) {
             const size_t rows = (size_t)n * m.MW;
+            if (part) for (size_t t = threadIdx.x; t < rows; t += blockDim.x) s_part[t] = 0;
             for (int d = 0; d < m.D - 1; ++d)
                 for (size_t t = threadIdx.x; t < rows; t += blockDim.x) sc.P[(size_t)d * layer_words + t] = 0;
         }
@@ -93,6 +97,7 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
             const bool last = d == m.D - 1;
             ScatterTargets targets;
             targets.world = 1;
+            targets.local = part && !last ? s_part : nullptr;
             targets.base[0] = sc.P + (size_t)d * layer_words;
             for (int c = warp; c < m.C; c += nwarps) {
                 const ClauseView cv = global_view(m, sc.n_inc, c);
@@ -106,6 +111,13 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
                 }
             }
             __syncthreads();
+            if (targets.local) {
+                // every clause has marked its bits on the source nodes: one walk over the edges makes the layer's messages
+                flush_messages(targets, gv, m.MS, m.MW);
+                __syncthreads();
+                for (int t = threadIdx.x; t < n * m.MW; t += blockDim.x) s_part[t] = 0;
+                __syncthreads();
+            }
         }
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) a.class_sums[(size_t)i * m.K + k] = s_sum[k];
         __syncthreads();
