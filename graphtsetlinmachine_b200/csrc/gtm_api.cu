@@ -15,6 +15,12 @@
 #include "gtm_handles.h"
 #include "gtm_kernels.cuh"
 
+// The general scoring kernel with or without four-at-a-time node words (graph sets with more than 32 nodes per graph).
+static const void *score_kernel_for(int max_nodes)
+{
+    return max_nodes > 32 ? (const void *)score_graphs_kernel<true> : (const void *)score_graphs_kernel<false>;
+}
+
 static int bind(gtm_model *m)
 {
     if (!m) return fail(GTM_ERR_ARG, "null model handle");
@@ -345,9 +351,9 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
         ds->score_smem += (size_t)ds->score_part_words * sizeof(u32);
     }
     if (ds->score_smem > 48 * 1024)
-        GTM_CU(cudaFuncSetAttribute(score_graphs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+        GTM_CU(cudaFuncSetAttribute(score_kernel_for(ds->max_nodes), cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
     int per_sm = 0;
-    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_graphs_kernel, 256, ds->score_smem));
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_kernel_for(ds->max_nodes), 256, ds->score_smem));
     ds->score_grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)m->sm_count * std::max(1, per_sm), v->number_of_graphs));
     ds->cno_stride = (size_t)2 * d.C * ds->NC;
     ds->P_stride = p_words;
@@ -429,7 +435,12 @@ static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int6
     a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
     a.part_words = ds->score_part_words;
     const int grid = (int)std::min<int64_t>(ds->score_grid, count);
-    score_graphs_kernel<<<grid, 256, ds->score_smem, m->stream>>>(m->dm, g, ds->score_sc, a);
+    {
+        DevModel dm = m->dm;
+        EvalScratch sc = ds->score_sc;
+        void *args[] = {&dm, &g, &sc, &a};
+        GTM_CU(cudaLaunchKernel(score_kernel_for(ds->max_nodes), dim3(grid), dim3(256), args, ds->score_smem, m->stream));
+    }
     GTM_CU(cudaGetLastError());
     return GTM_OK;
 }
@@ -560,7 +571,7 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         a.part_words = 0;
         EvalScratch sc = ds->fit_sc;
         sc.P = ds->P_pair[0];
-        score_graphs_kernel<<<1, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
+        score_graphs_kernel<true><<<1, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
         cudaError_t e = cudaStreamSynchronize(m->stream);
         if (e == cudaSuccess && class_sum_out) e = cudaMemcpy(class_sum_out, sums, (size_t)d.K * sizeof(int), cudaMemcpyDeviceToHost);
         cudaFree(sums);
@@ -667,7 +678,7 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr;
     a.cno_stride = a.P_stride = a.ninc_stride = per_cta;                             // one contiguous slice per CTA
     a.part_words = 0;
-    score_graphs_kernel<<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
+    score_graphs_kernel<true><<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
     GTM_CU(cudaGetLastError());
     return GTM_OK;
 }

@@ -216,11 +216,137 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
     }
 }
 
+template <int N>
+__device__ __forceinline__ bool any_of(const bool (&f)[N])
+{
+    bool r = false;
+#pragma unroll
+    for (int i = 0; i < N; ++i) r = r || f[i];
+    return r;
+}
+
+// Include words of a clause layer as eval_clause_layer holds them: word w0 + lane in lanes, layers of at most 64 words in
+// two registers (cached), wider ones reloaded per 32 words.
+struct IncludeWords {
+    const u32 *inc;
+    u32 a, b, last_mask;
+    bool cached;
+};
+
+// kBatch consecutive node words (from j0) of one clause layer, with independent state so that the loads of the batch
+// (node types, rows) are in flight together: a warp's evaluation is a chain of dependent memory latencies otherwise.
+// Returns the OR of the node-output words written.
+template <int kBatch>
+__device__ __forceinline__ u32 eval_node_words(const DevModel &m, const GraphView &gv, const ClauseView &cv, int d, int W,
+                                               const IncludeWords &iw_all, u32 my_type, int j0, int words, const u32 *prev,
+                                               u32 *out, const u32 *Pread, const ScatterTargets *scatter, int lane)
+{
+    const int n = gv.n;
+    const bool wide = d == 0 && (W & 3) == 0;     // literal rows are 16-byte aligned: 128-bit loads
+    const bool cached = iw_all.cached;
+    const u32 inc_a = iw_all.a, inc_b = iw_all.b, last_mask = iw_all.last_mask;
+    const u32 *inc = iw_all.inc;
+    u32 any = 0;
+    {
+        bool ok[kBatch];
+        const u32 *row[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int j = j0 + q, v = j * 32 + lane;
+            ok[q] = j < words && v < n;
+            if (d > 0 && j < words) ok[q] = ok[q] && ((prev[j] >> lane) & 1u);
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int v = (j0 + q) * 32 + lane;
+            const u32 ty = ok[q] ? gv.type[v] : ~0u;
+            ok[q] = ok[q] && ty == my_type;
+            const int vv = ok[q] ? v : 0;
+            row[q] = d == 0 ? gv.X + (size_t)vv * W : Pread + (size_t)vv * m.MW;
+        }
+        bool alive = __any_sync(kFull, any_of<kBatch>(ok));
+        for (int w0 = 0; w0 < W && alive; w0 += 32) {
+            u32 iw_l;
+            if (cached) iw_l = w0 == 0 ? inc_a : inc_b;
+            else iw_l = w0 + lane < W ? inc[w0 + lane] & (w0 + lane == W - 1 ? last_mask : kFull) : 0u;
+            u32 nz = __ballot_sync(kFull, iw_l != 0);
+            if (wide) {
+                nz = (nz | (nz >> 1) | (nz >> 2) | (nz >> 3)) & 0x11111111u;      // groups of four words with an included literal
+                while (nz) {
+                    const int b = __ffs(nz) - 1;
+                    nz &= nz - 1;
+                    const u32 i0 = __shfl_sync(kFull, iw_l, b), i1 = __shfl_sync(kFull, iw_l, b + 1),
+                              i2 = __shfl_sync(kFull, iw_l, b + 2), i3 = __shfl_sync(kFull, iw_l, b + 3);
+                    uint4 x[kBatch];
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q)
+                        x[q] = ok[q] ? reinterpret_cast<const uint4 *>(row[q])[(w0 + b) >> 2] : make_uint4(kFull, kFull, kFull, kFull);
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q)
+                        ok[q] = ok[q] && (((i0 & ~x[q].x) | (i1 & ~x[q].y) | (i2 & ~x[q].z) | (i3 & ~x[q].w)) == 0);
+                    if (!__any_sync(kFull, any_of<kBatch>(ok))) { alive = false; break; }   // warp-ballot early exit
+                }
+            } else {
+                while (nz) {
+                    const int b = __ffs(nz) - 1;
+                    nz &= nz - 1;
+                    const u32 iw = __shfl_sync(kFull, iw_l, b);
+                    u32 x[kBatch];
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q)
+                        x[q] = !ok[q] ? kFull : d == 0 ? row[q][w0 + b] : msg_word(row[q], w0 + b, m.MS, m.MW);
+#pragma unroll
+                    for (int q = 0; q < kBatch; ++q) ok[q] = ok[q] && ((iw & ~x[q]) == 0);
+                    if (!__any_sync(kFull, any_of<kBatch>(ok))) { alive = false; break; }
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int j = j0 + q, v = j * 32 + lane;
+            if (j >= words) break;
+            const u32 word = __ballot_sync(kFull, ok[q]);
+            if (lane == 0) out[j] = word;
+            any |= word;
+            if (scatter && ok[q]) {
+                if (scatter->local) {
+                    // mark the clause's hypervector bits on this (source) node; most are there already
+                    for (int b = 0; b < m.MB; ++b) {
+                        u32 bit = cv.hv[b];
+                        if (bit >= (u32)m.MS) bit %= (u32)m.MS;
+                        u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
+                        const u32 mbit = 1u << (bit & 31);
+                        if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
+                    }
+                } else {
+                    const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
+                    for (u32 k = 0; k < deg; ++k) {
+                        const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
+                        if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
+                        for (int b = 0; b < m.MB; ++b) {
+                            u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
+                            if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                            const u32 mbit = 1u << (bit & 31);
+#pragma unroll
+                            for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
+                                if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), mbit);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    return any;
+}
+
 // One warp evaluates a clause at layer `d` over all nodes of a graph (lanes = the 32 nodes of a node word) and
 // writes the node-output words out[0..ceil(n/32)).  Layer 0 tests the node's literal row, layer d >= 1 the node's
 // message row ANDed with the node's bit of layer d-1 in `prev` (kernels.py:407-530).  Returns the OR of the words
 // written (warp-uniform).  When `scatter` is given, every true node sends the clause's hypervector bits along
 // its out-edges into every target buffer (kernels.py:549-590): bit (hv[c][b] + edge type) mod MS of the destination node.
+// kBatchNodes: node words are also taken four at a time (graph sets with more than 32 nodes per graph); without it the
+// code for single node words is all there is, which keeps small-graph kernels lean.
+template <bool kBatchNodes>
 __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphView &gv, int n_types, const ClauseView &cv,
                                                  int c, int d, const u32 *prev, u32 *out, const u32 *Pread,
                                                  const ScatterTargets *scatter, int lane)
@@ -248,79 +374,16 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
     if (lane == 0) *cv.n_inc = (d == 0 ? 0 : *cv.n_inc) + cnt;
 
     const int words = (n + 31) >> 5;
-    const bool wide = d == 0 && (W & 3) == 0;     // literal rows are 16-byte aligned: 128-bit loads
+    IncludeWords iw_all;
+    iw_all.inc = inc; iw_all.a = inc_a; iw_all.b = inc_b; iw_all.last_mask = last_mask; iw_all.cached = cached;
     u32 any = 0;
-    for (int j = 0; j < words; ++j) {
-        const int v = j * 32 + lane;
-        bool ok = v < n;
-        if (d > 0) {
-            const u32 pw = prev[j];
-            if (pw == 0) { if (lane == 0) out[j] = 0; continue; }       // uniform: nothing can stay true
-            ok = ok && ((pw >> lane) & 1u);
-        }
-        ok = ok && gv.type[ok ? v : 0] == my_type;
-        if (__any_sync(kFull, ok)) {
-            const int vv = v < n ? v : 0;
-            const u32 *row = d == 0 ? gv.X + (size_t)vv * W : Pread + (size_t)vv * m.MW;
-            bool alive = true;
-            for (int w0 = 0; w0 < W && alive; w0 += 32) {
-                u32 iw_l;
-                if (cached) iw_l = w0 == 0 ? inc_a : inc_b;
-                else iw_l = w0 + lane < W ? inc[w0 + lane] & (w0 + lane == W - 1 ? last_mask : kFull) : 0u;
-                u32 nz = __ballot_sync(kFull, iw_l != 0);
-                if (wide) {
-                    nz = (nz | (nz >> 1) | (nz >> 2) | (nz >> 3)) & 0x11111111u;      // groups of four words with an included literal
-                    while (nz) {
-                        const int b = __ffs(nz) - 1;
-                        nz &= nz - 1;
-                        const u32 i0 = __shfl_sync(kFull, iw_l, b), i1 = __shfl_sync(kFull, iw_l, b + 1),
-                                  i2 = __shfl_sync(kFull, iw_l, b + 2), i3 = __shfl_sync(kFull, iw_l, b + 3);
-                        const uint4 x = reinterpret_cast<const uint4 *>(row)[(w0 + b) >> 2];
-                        ok = ok && (((i0 & ~x.x) | (i1 & ~x.y) | (i2 & ~x.z) | (i3 & ~x.w)) == 0);
-                        if (!__any_sync(kFull, ok)) { alive = false; break; }            // warp-ballot early exit
-                    }
-                } else {
-                    while (nz) {
-                        const int b = __ffs(nz) - 1;
-                        nz &= nz - 1;
-                        const u32 iw = __shfl_sync(kFull, iw_l, b);
-                        const u32 x = d == 0 ? row[w0 + b] : msg_word(row, w0 + b, m.MS, m.MW);
-                        ok = ok && ((iw & ~x) == 0);
-                        if (!__any_sync(kFull, ok)) { alive = false; break; }
-                    }
-                }
-            }
-        }
-        const u32 word = __ballot_sync(kFull, ok);
-        if (lane == 0) out[j] = word;
-        any |= word;
-        if (scatter && ok) {
-            if (scatter->local) {
-                // mark the clause's hypervector bits on this (source) node; most are there already
-                for (int b = 0; b < m.MB; ++b) {
-                    u32 bit = cv.hv[b];
-                    if (bit >= (u32)m.MS) bit %= (u32)m.MS;
-                    u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
-                    const u32 mbit = 1u << (bit & 31);
-                    if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
-                }
-            } else {
-                const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
-                for (u32 k = 0; k < deg; ++k) {
-                    const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
-                    if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
-                    for (int b = 0; b < m.MB; ++b) {
-                        u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
-                        if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
-                        const u32 mbit = 1u << (bit & 31);
-#pragma unroll
-                        for (int r = 0; r < kMaxRanks; ++r)     // constant indices keep the pointers in registers
-                            if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), mbit);
-                    }
-                }
-            }
-        }
-    }
+    int j0 = 0;
+    // batches of four node words while more than one is left (large graphs), single words otherwise
+    if (kBatchNodes)
+        for (; words - j0 > 1; j0 += 4)
+            any |= eval_node_words<4>(m, gv, cv, d, W, iw_all, my_type, j0, words, prev, out, Pread, scatter, lane);
+    for (; j0 < words; ++j0)
+        any |= eval_node_words<1>(m, gv, cv, d, W, iw_all, my_type, j0, words, prev, out, Pread, scatter, lane);
     return any;
 }
 

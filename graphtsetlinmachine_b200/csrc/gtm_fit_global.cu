@@ -16,7 +16,7 @@ namespace gtm {
 // #warps for the whole launch, so automata and weights of a clause are only ever touched by one warp).  Per
 // graph: layer evaluations separated by grid barriers (messages mix all clauses), one exchange of per-CTA vote
 // partials, then clause-local feedback.  Serves any model size; also the debug path that keeps every layer.
-template <int MAXSB>
+template <int MAXSB, bool kBatchNodes>
 __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, EvalScratch sc, FitArgs a, int eval_only)
 {
     extern __shared__ int s_mem[];   // [K] running partial, [K] totals, [K] targets, [K] thresholds
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
-                    const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                    const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                       cno_row(sc, m.C, d, c), d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
                                                       last ? nullptr : &targets, lane);
                     if (last && any)
@@ -112,4 +112,8 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
 
 }  // namespace gtm
 
-const void *fit_global_kernel(int state_bits) { return state_bits <= 8 ? (const void *)fit_kernel<8> : (const void *)fit_kernel<32>; }
+const void *fit_global_kernel(int state_bits, bool batch_nodes)
+{
+    if (batch_nodes) return state_bits <= 8 ? (const void *)fit_kernel<8, true> : (const void *)fit_kernel<32, true>;
+    return state_bits <= 8 ? (const void *)fit_kernel<8, false> : (const void *)fit_kernel<32, false>;
+}

@@ -9,7 +9,7 @@
 #include "gtm_handles.h"
 #include "gtm_fit.cuh"
 
-const void *fit_global_kernel(int state_bits);   // gtm_fit_global.cu
+const void *fit_global_kernel(int state_bits, bool batch_nodes);   // gtm_fit_global.cu
 
 namespace gtm {
 
@@ -36,7 +36,7 @@ __device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global
 //                  [12] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
 //                  per owned clause: clause_words words =
 //                  draw counter (2) | include count (1) | pad (1) | weights [K] | hypervector [MB] | node words [2][NC] | planes
-template <int MAXSB>
+template <int MAXSB, bool kBatchNodes>
 __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGraphs g, FitArgs a)
 {
     extern __shared__ __align__(16) int s_mem[];
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
-                const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
+                const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
                                                   d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
                                                   last ? nullptr : &targets, lane);
                 if (last && any)
@@ -335,7 +335,7 @@ int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *g
 {
     int per_sm = 0;
     const size_t smem = 4 * (size_t)d.K * sizeof(int);
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_global_kernel(d.SB), block, smem);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fit_global_kernel(d.SB, true), block, smem);
     if (e != cudaSuccess || per_sm < 1)
         return fail(GTM_ERR_CUDA, "learning kernel does not fit on this device: %s", cudaGetErrorString(e));
     const int warps_per_cta = block / 32;
@@ -347,6 +347,13 @@ static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 
 constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 
+// The state-resident kernel for the automaton width, with four-at-a-time node words for graph sets of more than 32 nodes per graph.
+static const void *resident_kernel_for(int state_bits, int max_nodes)
+{
+    if (max_nodes > 32) return state_bits <= 8 ? (const void *)fit_resident_kernel<8, true> : (const void *)fit_resident_kernel<32, true>;
+    return state_bits <= 8 ? (const void *)fit_resident_kernel<8, false> : (const void *)fit_resident_kernel<32, false>;
+}
+
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
 struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1; size_t smem = 0; };
 
@@ -355,7 +362,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     DevModel d = m->dm;
     d.C = n_clauses;   // clauses this rank learns
     ResidentPlan plan;
-    const void *fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+    const void *fn = resident_kernel_for(d.SB, ds->max_nodes);
     const int warps = kResidentThreads / 32;
     int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
     words = (words + 3) & ~3;
@@ -470,13 +477,13 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
 
     DevModel dm = d;
     if (resident) {
-        fn = d.SB <= 8 ? (const void *)fit_resident_kernel<8> : (const void *)fit_resident_kernel<32>;
+        fn = resident_kernel_for(d.SB, ds->max_nodes);
         block = kResidentThreads;
         if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &a};
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
     } else {
-        fn = fit_global_kernel(d.SB);
+        fn = fit_global_kernel(d.SB, ds->max_nodes > 32);
         block = m->fit_block;
         // one layer's messages are accumulated per CTA in shared memory when a layer takes at most 64 KB
         const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);

@@ -69,6 +69,7 @@ struct ScoreArgs {
     int part_words;       // > 0: shared-memory words (after the vote partial) that accumulate one layer's messages
 };
 
+template <bool kBatchNodes>
 __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs g, EvalScratch sc0, ScoreArgs a)
 {
     extern __shared__ int s_sum[];   // [K], then the message accumulation words
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
             targets.base[0] = sc.P + (size_t)d * layer_words;
             for (int c = warp; c < m.C; c += nwarps) {
                 const ClauseView cv = global_view(m, sc.n_inc, c);
-                const u32 any = eval_clause_layer(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                   cno_row(sc, m.C, d, c), d > 0 ? sc.P + (size_t)(d - 1) * layer_words : nullptr,
                                                   last ? nullptr : &targets, lane);
                 if (last) {
