@@ -161,6 +161,82 @@ def reference_kernels_on_gpu(tm, train, y_train, sums_host, batch, sample=4096):
                    "per kernel and per graph with the per-graph class-sum copies of the reference's host loop; wall clock"}
 
 
+def host_side_baselines(tm, batch, sums_host, threads, sample=4096):
+    """The reference's host-side work on this box's cores: `Graphs` encoding of the workload's images through the
+    per-item API (one core: it is Python-bound) and through the vectorised builders, and a NumPy evaluation of the
+    same clause semantics (fail = any(include & ~X), votes by a matrix product) on `threads` threads, checked against
+    the engine's class sums."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from graphtsetlinmachine_b200 import datasets
+    from graphtsetlinmachine_b200.graphs import Graphs
+
+    protos = datasets.image_prototypes(1)
+    rng = np.random.default_rng(5)
+    n_api = 256
+    labels = rng.integers(0, CLASSES, size=n_api)
+    pixels = rng.random((n_api, protos.shape[1])) < protos[labels]
+    np.random.seed(1)
+    t0 = time.perf_counter()
+    g = Graphs(n_api, symbols=list(range(protos.shape[1])), hypervector_size=HV_SIZE, hypervector_bits=HV_BITS)
+    for i in range(n_api):
+        g.set_number_of_graph_nodes(i, 1)
+    g.prepare_node_configuration()
+    for i in range(n_api):
+        g.add_graph_node(i, "Image Node", 0)
+    g.prepare_edge_configuration()
+    for i in range(n_api):
+        for k in pixels[i].nonzero()[0]:
+            g.add_graph_node_property(i, "Image Node", int(k))
+    g.encode()
+    api_s = time.perf_counter() - t0
+    n_bulk = 1 << 16
+    np.random.seed(1)
+    t0 = time.perf_counter()
+    datasets.vanilla_images(n_bulk, 6, protos, HV_SIZE, HV_BITS)
+    bulk_s = time.perf_counter() - t0
+
+    state = tm.get_state()
+    include = np.ascontiguousarray(state[0].reshape(CLAUSES, -1, 8)[:, :, 7])            # top state plane = include mask
+    weights = state[1].reshape(CLASSES, CLAUSES).astype(np.int32)
+    X = np.ascontiguousarray(batch.X[:sample])
+
+    def evaluate(lo, hi):
+        fails = ((include[None, :, :] & ~X[lo:hi, None, :]) != 0).any(axis=2)           # [graphs][clauses]
+        return (~fails).astype(np.int32) @ weights.T
+
+    chunk = 64
+    spans = [(lo, min(sample, lo + chunk)) for lo in range(0, sample, chunk)]
+    with ThreadPoolExecutor(threads) as pool:
+        list(pool.map(lambda sp: evaluate(*sp), spans[:threads]))
+        t0 = time.perf_counter()
+        parts = list(pool.map(lambda sp: evaluate(*sp), spans))
+        numpy_s = time.perf_counter() - t0
+    assert np.array_equal(np.concatenate(parts), sums_host[:sample]), "NumPy evaluation differs from the engine"
+    return {"graphs_encoding_api": {"value": n_api / api_s, "unit": "graphs/s", "cores": 1, "sample": "%d images through add_graph_node_property" % n_api},
+            "graphs_encoding_vectorised": {"value": n_bulk / bulk_s, "unit": "graphs/s", "cores": 1, "sample": "%d images through the bulk builders" % n_bulk},
+            "numpy_clause_evaluation": {"value": sample / numpy_s, "unit": "graphs/s", "cores": threads, "sample": "%d graphs, chunks of %d over a thread pool" % (sample, chunk)}}
+
+
+def reference_fit_on_cpu(tm_state, train, y_train, graphs=512):
+    """Learning rate of the reference's kernels compiled for the host (learning is sequential: one core)."""
+    try:
+        from oracle.ref_tm import RefTM
+
+        ref = RefTM(clauses=CLAUSES, classes=CLASSES, literals=2 * HV_SIZE, threshold=T, s=S, depth=1, max_nodes=1, seed=7)
+    except (FileNotFoundError, OSError):
+        return None
+    ref.ta_state[:] = tm_state[0].reshape(ref.ta_state.shape)
+    ref.clause_weights[:] = tm_state[1].reshape(ref.clause_weights.shape)
+    ref.set_graphs(train)
+    enc = np.where(y_train[:, None] == np.arange(CLASSES)[None, :], T, -T).astype(np.int32)
+    ref.fit(enc, 0, 16)
+    t0 = time.perf_counter()
+    ref.fit(enc, 16, graphs)
+    return {"value": graphs / (time.perf_counter() - t0), "unit": "graphs/s", "cores": 1, "kind": "reference",
+            "sample": "%d graphs, reference learning kernels compiled for the host" % graphs}
+
+
 def trained_state_on_cpu(train, y_train):
     """A trained state for the reference arm when no GPU run precedes it: a short fit with the C restatement."""
     from oracle.oracle import OracleTM
@@ -336,6 +412,11 @@ def main():
             cpu = {"value": cnt / sec, "unit": "graphs/s", "cores": threads, "kind": kind,
                    "sample": "%d graphs of the same batch, %d host threads, reference scoring kernels compiled for the host" % (cnt, threads)}
 
+    host_side, cpu_fit = None, None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        host_side = host_side_baselines(tm, batch, sums_host, os.cpu_count() or 1)
+        cpu_fit = reference_fit_on_cpu(tm.get_state(), train, y_train)
+
     # ---- the reference's own kernels on this GPU, launched per graph as its host code does (bounded sample) ----
     ref_gpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
@@ -364,6 +445,8 @@ def main():
                                      "achieved_tlop3_s": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12}},
             "cpu_baseline": cpu,
             "reference_kernels_on_gpu": ref_gpu,
+            "host_side": host_side,
+            "cpu_fit_baseline": cpu_fit,
             "fit": {"value": TRAIN_GRAPHS / fit_s, "unit": "graphs/s", "graphs": TRAIN_GRAPHS, "epoch_s": fit_s,
                     "n_gpus": world, "train_accuracy_after_2_epochs": train_acc, "scaling": "strong",
                     "partitioning": "clauses sharded over ranks, per-graph class-sum exchange by NVLink peer stores" if world > 1 else "single GPU",
