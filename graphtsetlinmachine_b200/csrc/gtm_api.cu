@@ -342,18 +342,31 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->fit_sc.P = ds->P_pair[0];
 
     // general scoring scratch: one slice per resident CTA
-    // depth > 1: the source-node message bits of a graph are accumulated in shared memory when they are small enough
-    // not to cost resident CTAs (flush_messages)
+    // General scoring kernel, shared memory per CTA: vote partial; for depth > 1 the source-node message bits of a graph
+    // (flush_messages) when they are small enough not to cost resident CTAs; for graph sets of 33..1024 nodes per graph the
+    // transposed copy of the graph - and then the message bits too (up to 64 KB), in CTAs of 512 threads, one or two per SM.
     ds->score_part_words = 0;
+    ds->score_t_stride = 0;
+    ds->score_block = 256;
     ds->score_smem = (size_t)((d.K + 3) & ~3) * sizeof(int);
-    if (d.D > 1 && (size_t)ds->max_nodes * d.MW * sizeof(u32) <= 8 * 1024) {
+    const size_t msg_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
+    {
+        const int t_stride = ds->NC | 1;
+        const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);
+        if (ds->max_nodes > 32 && ds->NC <= 32 && t_bytes <= 96 * 1024) {
+            ds->score_t_stride = t_stride;
+            ds->score_smem += t_bytes;
+            ds->score_block = 512;
+        }
+    }
+    if (d.D > 1 && (msg_bytes <= 8 * 1024 || (ds->score_t_stride > 0 && msg_bytes <= 64 * 1024))) {
         ds->score_part_words = ds->max_nodes * d.MW;
-        ds->score_smem += (size_t)ds->score_part_words * sizeof(u32);
+        ds->score_smem += msg_bytes;
     }
     if (ds->score_smem > 48 * 1024)
-        GTM_CU(cudaFuncSetAttribute(score_kernel_for(ds->max_nodes), cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+        GTM_CU(cudaFuncSetAttribute(score_kernel_for(ds->max_nodes), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ds->score_smem));
     int per_sm = 0;
-    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_kernel_for(ds->max_nodes), 256, ds->score_smem));
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_kernel_for(ds->max_nodes), ds->score_block, ds->score_smem));
     ds->score_grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)m->sm_count * std::max(1, per_sm), v->number_of_graphs));
     ds->cno_stride = (size_t)2 * d.C * ds->NC;
     ds->P_stride = p_words;
@@ -433,13 +446,13 @@ static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int6
     ScoreArgs a;
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = clause_out_dev;
     a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
-    a.part_words = ds->score_part_words;
+    a.part_words = ds->score_part_words; a.t_stride = ds->score_t_stride;
     const int grid = (int)std::min<int64_t>(ds->score_grid, count);
     {
         DevModel dm = m->dm;
         EvalScratch sc = ds->score_sc;
         void *args[] = {&dm, &g, &sc, &a};
-        GTM_CU(cudaLaunchKernel(score_kernel_for(ds->max_nodes), dim3(grid), dim3(256), args, ds->score_smem, m->stream));
+        GTM_CU(cudaLaunchKernel(score_kernel_for(ds->max_nodes), dim3(grid), dim3(ds->score_block), args, ds->score_smem, m->stream));
     }
     GTM_CU(cudaGetLastError());
     return GTM_OK;
@@ -568,7 +581,7 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         ScoreArgs a;
         a.first = graph; a.count = 1; a.class_sums = sums; a.clause_outputs = nullptr;
         a.cno_stride = a.P_stride = a.ninc_stride = 0;
-        a.part_words = 0;
+        a.part_words = 0; a.t_stride = 0;
         EvalScratch sc = ds->fit_sc;
         sc.P = ds->P_pair[0];
         score_graphs_kernel<true><<<1, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
@@ -677,7 +690,7 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     ScoreArgs a;
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr;
     a.cno_stride = a.P_stride = a.ninc_stride = per_cta;                             // one contiguous slice per CTA
-    a.part_words = 0;
+    a.part_words = 0; a.t_stride = 0;
     score_graphs_kernel<true><<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
     GTM_CU(cudaGetLastError());
     return GTM_OK;

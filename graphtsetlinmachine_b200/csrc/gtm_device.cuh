@@ -197,21 +197,125 @@ __device__ __forceinline__ u32 rotated_word(const u32 *row, int w, u32 t, int MS
 // All threads of the CTA, between two CTA barriers; the local buffer is cleared by the caller afterwards.
 __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW)
 {
-    const int items = gv.n * MW;
-    for (int i = threadIdx.x; i < items; i += blockDim.x) {
-        const int u = i / MW, w = i - u * MW;
-        const u32 *row = t.local + (size_t)u * MW;
-        const u32 e0 = gv.eidx[u] - gv.e_off, deg = gv.degree[u];
-        for (u32 k = 0; k < deg; ++k) {
-            const u32 dst = gv.edge[2 * (size_t)(e0 + k)];
-            u32 ty = gv.edge[2 * (size_t)(e0 + k) + 1];
-            if (dst >= (u32)gv.n) continue;                                // malformed edge: ignore, never fault
-            if (ty >= (u32)MS) ty %= (u32)MS;
-            const u32 v = rotated_word(row, w, ty, MS, MW);
-            if (v == 0) continue;
+    // The merge is bound by the atomics that all CTAs send to the same rows: rows of an even number of words go out as
+    // 64-bit atomics (half as many).  An item is (source node, word or word pair).
+    const bool pairs = (MW & 1) == 0;
+    const int per_row = pairs ? MW >> 1 : MW;
+    const int items = gv.n * per_row;
+    constexpr int kInFlight = 4;      // items per thread whose CSR loads are issued together
+    for (int i0 = threadIdx.x; i0 < items; i0 += kInFlight * blockDim.x) {
+        int u[kInFlight], w[kInFlight];
+        u32 e0[kInFlight], deg[kInFlight], maxdeg = 0;
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < t.world) atomicOr(t.base[r] + (size_t)dst * MW + w, v);
+        for (int q = 0; q < kInFlight; ++q) {
+            const int i = i0 + q * blockDim.x;
+            u[q] = i < items ? i / per_row : 0;
+            w[q] = (i - u[q] * per_row) << (pairs ? 1 : 0);
+            e0[q] = gv.eidx[u[q]] - gv.e_off;
+            deg[q] = i < items ? gv.degree[u[q]] : 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < kInFlight; ++q) {
+            // a source row without bits sends nothing
+            if (deg[q] != 0) {
+                const u32 *row = t.local + (size_t)u[q] * MW;
+                u32 any = 0;
+                for (int x = 0; x < MW; ++x) any |= row[x];
+                if (any == 0) deg[q] = 0;
+            }
+            maxdeg = max(maxdeg, deg[q]);
+        }
+        for (u32 k = 0; k < maxdeg; ++k) {
+            u32 dst[kInFlight], ty[kInFlight];
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) {
+                dst[q] = k < deg[q] ? gv.edge[2 * (size_t)(e0[q] + k)] : ~0u;
+                ty[q] = k < deg[q] ? gv.edge[2 * (size_t)(e0[q] + k) + 1] : 0u;
+            }
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) {
+                if (dst[q] >= (u32)gv.n) continue;                         // no edge in this slot, or a malformed edge: never fault
+                const u32 tq = ty[q] >= (u32)MS ? ty[q] % (u32)MS : ty[q];
+                const u32 *row = t.local + (size_t)u[q] * MW;
+                const u32 lo = rotated_word(row, w[q], tq, MS, MW);
+                if (pairs) {
+                    const u32 hi = rotated_word(row, w[q] + 1, tq, MS, MW);
+                    if ((lo | hi) == 0) continue;
+                    const unsigned long long v = ((unsigned long long)hi << 32) | lo;
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                        if (r < t.world)
+                            atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + (size_t)dst[q] * MW + w[q]), v);
+                } else {
+                    if (lo == 0) continue;
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                        if (r < t.world) atomicOr(t.base[r] + (size_t)dst[q] * MW + w[q], lo);
+                }
+            }
+        }
+    }
+}
+
+// In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.
+__device__ __forceinline__ void transpose32(u32 (&a)[32])
+{
+    u32 mask = 0x0000ffffu;
+#pragma unroll
+    for (int j = 16; j != 0; j >>= 1, mask ^= mask << j) {
+#pragma unroll
+        for (int k = 0; k < 32; k = (k + j + 1) & ~j) {
+            const u32 t = ((a[k] >> j) ^ a[k + j]) & mask;
+            a[k] ^= t << j;
+            a[k + j] ^= t;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ transposed evaluation (large graphs)
+// For graphs of 33..1024 nodes a CTA keeps the graph's literal rows TRANSPOSED in shared memory: row(l) holds, for
+// literal l, one bit per node (word j = nodes 32j..32j+31).  A warp then evaluates a clause on ALL nodes at once, lane j
+// owning node word j: r = type/valid mask; for every included literal l: r &= row(l) - one conflict-free shared load per
+// included literal, instead of one pass over the include words per node word.  Layers >= 1 do the same on the
+// transposed positive message bits (a negated message literal ANDs the complement).
+// Storage: literal l = 32w + b lives at T[((b * W) + w) * S + j] with S odd (>= node words), so that the threads that
+// build it (adjacent w) and the lanes that read it (adjacent j) are both conflict-free.
+constexpr int kTransposedTypes = 8;   // node types a transposed graph keeps masks for
+struct TransposedGraph {
+    u32 *T;        // [32 * Wmax][S] literal rows of the current layer (layer 0: literals, layer d: positive message bits)
+    u32 *TM;       // [n_types][S] nodes of each type (valid nodes only)
+    int S;         // row stride in words (odd)
+    int words;     // node words of the current graph (<= 32)
+};
+
+// All threads of the CTA: rows[v][0..W) of nodes v < n (row stride `stride` words) -> T.
+__device__ __forceinline__ void build_transposed(const u32 *rows, int n, int W, int stride, const TransposedGraph &tg)
+{
+    const int blocks = tg.words * W;
+    for (int blk = threadIdx.x; blk < blocks; blk += blockDim.x) {
+        const int j = blk / W, w = blk - j * W;
+        u32 r[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int v = 32 * j + i;
+            r[i] = v < n ? rows[(size_t)v * stride + w] : 0u;
+        }
+        transpose32(r);
+#pragma unroll
+        for (int b = 0; b < 32; ++b) tg.T[(size_t)(b * W + w) * tg.S + j] = r[b];
+    }
+}
+
+// All threads of the CTA: node-type masks of the graph (types 0..n_types-1).
+__device__ __forceinline__ void build_type_masks(const u32 *type, int n, int n_types, const TransposedGraph &tg)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int j = warp; j < tg.words; j += nwarps) {
+        const int v = 32 * j + lane;
+        const u32 ty = v < n ? type[v] : ~0u;
+        for (int t = 0; t < n_types; ++t) {
+            const u32 col = __ballot_sync(kFull, ty == (u32)t);
+            if (lane == 0) tg.TM[(size_t)t * tg.S + j] = col;
         }
     }
 }
@@ -384,6 +488,87 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
             any |= eval_node_words<4>(m, gv, cv, d, W, iw_all, my_type, j0, words, prev, out, Pread, scatter, lane);
     for (; j0 < words; ++j0)
         any |= eval_node_words<1>(m, gv, cv, d, W, iw_all, my_type, j0, words, prev, out, Pread, scatter, lane);
+    return any;
+}
+
+// eval_clause_layer on a transposed graph: lane j owns node word j (graphs of at most 1024 nodes).  Same results:
+// node-output words in out[], include count, OR of the words returned, messages through `scatter`.
+__device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, const GraphView &gv, int n_types,
+                                                            const ClauseView &cv, int c, int d, const u32 *prev, u32 *out,
+                                                            const TransposedGraph &tg, const ScatterTargets *scatter, int lane)
+{
+    const int n = gv.n;
+    const int W = d == 0 ? m.L0 : m.M;
+    const int WT = d == 0 ? m.L0 : m.MW;                 // words per transposed source row
+    const u32 *inc = cv.ta(d) + (size_t)(m.SB - 1) * W;
+    const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
+
+    u32 r = lane < tg.words ? tg.TM[(size_t)(c % n_types) * tg.S + lane] : 0u;
+    if (d > 0 && lane < tg.words) r &= prev[lane];
+    int cnt = 0;
+    bool alive = __any_sync(kFull, r != 0);
+    for (int w0 = 0; w0 < W; w0 += 32) {
+        const u32 iw_l = w0 + lane < W ? inc[w0 + lane] & (w0 + lane == W - 1 ? last_mask : kFull) : 0u;
+        cnt += __popc(iw_l);
+        if (!alive) continue;
+        u32 nz = __ballot_sync(kFull, iw_l != 0);
+        while (nz && alive) {
+            const int bw = __ffs(nz) - 1;
+            nz &= nz - 1;
+            u32 iw = __shfl_sync(kFull, iw_l, bw);
+            const int w = w0 + bw;
+            while (iw) {
+                const int b = __ffs(iw) - 1;
+                iw &= iw - 1;
+                if (d == 0) {
+                    r &= tg.T[(size_t)(b * WT + w) * tg.S + lane];
+                } else {
+                    const int l = 32 * w + b;                               // message literal: positive bits, then their complements
+                    const int p = l < m.MS ? l : l - m.MS;
+                    const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + lane];
+                    r &= l < m.MS ? x : ~x;
+                }
+            }
+            alive = __any_sync(kFull, r != 0);
+        }
+    }
+    cnt = __reduce_add_sync(kFull, cnt);
+    if (lane == 0) *cv.n_inc = (d == 0 ? 0 : *cv.n_inc) + cnt;
+    if (lane >= tg.words) r = 0;                                             // lanes past the graph read nothing valid
+    else if (d > 0) r &= tg.TM[(size_t)(c % n_types) * tg.S + lane];         // complements set bits of missing nodes
+    if (lane < tg.words) out[lane] = r;
+    const u32 any = __ballot_sync(kFull, r != 0);
+    if (scatter && r) {
+        u32 bits = r;
+        while (bits) {
+            const int i = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int v = 32 * lane + i;
+            if (scatter->local) {
+                for (int b = 0; b < m.MB; ++b) {
+                    u32 bit = cv.hv[b];
+                    if (bit >= (u32)m.MS) bit %= (u32)m.MS;
+                    u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
+                    const u32 mbit = 1u << (bit & 31);
+                    if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
+                }
+            } else {
+                const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
+                for (u32 k = 0; k < deg; ++k) {
+                    const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
+                    if (dst >= (u32)n) continue;
+                    for (int b = 0; b < m.MB; ++b) {
+                        u32 bit = cv.hv[b] + t;
+                        if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                        const u32 mbit = 1u << (bit & 31);
+#pragma unroll
+                        for (int rk = 0; rk < kMaxRanks; ++rk)
+                            if (rk < scatter->world) atomicOr(scatter->base[rk] + (size_t)dst * m.MW + (bit >> 5), mbit);
+                    }
+                }
+            }
+        }
+    }
     return any;
 }
 

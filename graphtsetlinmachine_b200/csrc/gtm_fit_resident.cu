@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         s_part = s_clauses + (size_t)a.clauses_per_cta * a.clause_words;
         for (int t = threadIdx.x; t < a.part_words; t += blockDim.x) s_part[t] = 0;
     }
+    // transposed copy of the current graph (graphs of 33..1024 nodes): literal rows, then node-type masks
+    const int t_rows = 32 * max(m.L0, m.MW);
+    u32 *s_T = s_clauses + (size_t)a.clauses_per_cta * a.clause_words + a.part_words + 2 * a.p_smem_words;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
@@ -174,6 +177,9 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         }
         u32 *P = par ? P_odd : P_even;
         const int *y = s_y + par * KP;
+        TransposedGraph tg;
+        tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (gv.n + 31) >> 5;
+        const bool transposed = kBatchNodes && a.t_stride > 0 && gv.n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
         fetch_sizes(step + 2, e_nxt2);
 
@@ -190,6 +196,16 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
             }
+            if (transposed) {
+                // this layer's literal rows, one bit per node: the graph's literals, or the messages of the layer below
+                if (d == 0) {
+                    build_transposed(gv.X, gv.n, m.L0, m.L0, tg);
+                    build_type_masks(gv.type, gv.n, g.n_types, tg);
+                } else {
+                    build_transposed(P + (size_t)(d - 1) * layer_words, gv.n, m.MW, m.MW, tg);
+                }
+                __syncthreads();
+            }
             ScatterTargets targets;
             targets.world = a.world;
             targets.local = (!last && s_part != nullptr && gv.n * m.MW <= a.part_words) ? s_part : nullptr;
@@ -197,7 +213,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
-                const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
+                const u32 any = transposed
+                    ? eval_clause_layer_transposed(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
+                                                   tg, last ? nullptr : &targets, lane)
+                    : eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
                                                   d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
                                                   last ? nullptr : &targets, lane);
                 if (last && any)
@@ -355,7 +374,7 @@ static const void *resident_kernel_for(int state_bits, int max_nodes)
 }
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1; size_t smem = 0; };
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1, t_stride = 0; size_t smem = 0; };
 
 static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses, bool solo_allowed)
 {
@@ -371,10 +390,15 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
     const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
     const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
+    // transposed-graph buffer (graph sets of 33..1024 nodes per graph, few node types): rows of max(L0, MW) words plus type masks
+    const int t_stride = ds->NC | 1;
+    const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);
+    const bool t_possible = ds->max_nodes > 32 && ds->NC <= 32 && t_bytes <= 96 * 1024;
+    const bool part_possible = d.D > 1 && layer_bytes <= 64 * 1024;
+    // preference: the transposed evaluation first (it is worth an occupancy step), then two CTAs per SM, then the message
+    // accumulation buffer with and without the graph staging buffers, then staging alone
+    for (int with_t = t_possible ? 1 : 0; with_t >= 0; --with_t)
     for (int per_sm = 2; per_sm >= 1; --per_sm) {
-        // choices at the same occupancy, in order of preference: message accumulation in shared memory with and without
-        // the graph staging buffers, then staging alone
-        const bool part_possible = d.D > 1 && layer_bytes <= 64 * 1024;
         for (int choice = part_possible ? 0 : 2; choice < 3; ++choice) {
             const int with_part = choice < 2, stage = choice != 1;
             int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
@@ -395,6 +419,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
                 part_words = ds->max_nodes * d.MW;
                 smem += layer_bytes;
             }
+            if (with_t) smem += t_bytes;
             if (smem > 200 * 1024) continue;
             if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
             int occ = 0;
@@ -402,6 +427,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
             if ((long long)occ * m->sm_count < grid) continue;
             plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
             plan.solo = solo; plan.p_smem_words = p_smem_words; plan.part_words = part_words; plan.stage = stage;
+            plan.t_stride = with_t ? t_stride : 0;
             return plan;
         }
     }
@@ -449,7 +475,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
         }
         resident = cm.resident; grid = cm.grid;
-        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage;
+        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride;
         smem = cm.smem;
     } else {
         a.world = 1; a.rank = 0; a.c_begin = 0; a.c_end = d.C;
@@ -469,7 +495,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         resident = plan.grid > 0;
         grid = resident ? plan.grid : m->fit_grid;
         a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
-        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage;
+        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage; a.t_stride = plan.t_stride;
         smem = plan.smem;
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
@@ -535,7 +561,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     cm.resident = plan.grid > 0;
     if (cm.resident) {
         cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
-        cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.smem = plan.smem;
+        cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.t_stride = plan.t_stride; cm.smem = plan.smem;
     } else {
         const int warps = m->fit_block / 32;
         cm.grid = std::max(1, std::min(m->fit_grid, (per + warps - 1) / warps));

@@ -38,7 +38,7 @@ struct FitComm {
     size_t bytes = 0, exchange_off = 0, P_off[2] = {0, 0};
     int world = 1, rank = 0, grid = 0;
     bool resident = false;
-    int clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1;
+    int clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1, t_stride = 0;
     size_t smem = 0;
     bool connected = false, broken = false;
     u32 tag_base = 0;
@@ -58,6 +58,8 @@ struct gtm_dataset {
     EvalScratch score_sc;
     size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
     int score_grid = 0;
+    int score_block = 256;         // threads per CTA of the general scoring kernel
+    int score_t_stride = 0;        // row stride of the general scoring kernel's transposed-graph buffer (0 = none)
     int score_part_words = 0;      // shared-memory message accumulation of the general scoring kernel (0 = none)
     size_t score_smem = 0;
     int *Y = nullptr;

@@ -67,13 +67,16 @@ struct ScoreArgs {
     int *clause_outputs;  // optional [count][C] (transform)
     size_t cno_stride, P_stride, ninc_stride;  // per-CTA scratch strides (elements)
     int part_words;       // > 0: shared-memory words (after the vote partial) that accumulate one layer's messages
+    int t_stride;         // > 0: a transposed-graph buffer follows, with this (odd) row stride (TransposedGraph)
 };
 
 template <bool kBatchNodes>
-__global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs g, EvalScratch sc0, ScoreArgs a)
+__global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) score_graphs_kernel(DevModel m, DevGraphs g, EvalScratch sc0, ScoreArgs a)
 {
     extern __shared__ int s_sum[];   // [K], then the message accumulation words
     u32 *s_part = a.part_words > 0 ? reinterpret_cast<u32 *>(s_sum + ((m.K + 3) & ~3)) : nullptr;
+    u32 *s_T = reinterpret_cast<u32 *>(s_sum + ((m.K + 3) & ~3)) + max(a.part_words, 0);
+    const int t_rows = 32 * max(m.L0, m.MW);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     EvalScratch sc = sc0;
     sc.cno += blockIdx.x * a.cno_stride;
@@ -87,6 +90,9 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
         const int n = gv.n;
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
         const bool part = s_part != nullptr && n * m.MW <= a.part_words;     // source-node message bits fit the shared buffer
+        TransposedGraph tg;
+        tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (n + 31) >> 5;
+        const bool transposed = kBatchNodes && a.t_stride > 0 && n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         if (m.D > 1) {
             const size_t rows = (size_t)n * m.MW;
             if (part) for (size_t t = threadIdx.x; t < rows; t += blockDim.x) s_part[t] = 0;
@@ -100,9 +106,21 @@ __global__ void __launch_bounds__(256) score_graphs_kernel(DevModel m, DevGraphs
             targets.world = 1;
             targets.local = part && !last ? s_part : nullptr;
             targets.base[0] = sc.P + (size_t)d * layer_words;
+            if (transposed) {
+                if (d == 0) {
+                    build_transposed(gv.X, n, m.L0, m.L0, tg);
+                    build_type_masks(gv.type, n, g.n_types, tg);
+                } else {
+                    build_transposed(sc.P + (size_t)(d - 1) * layer_words, n, m.MW, m.MW, tg);
+                }
+                __syncthreads();
+            }
             for (int c = warp; c < m.C; c += nwarps) {
                 const ClauseView cv = global_view(m, sc.n_inc, c);
-                const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                const u32 any = transposed
+                    ? eval_clause_layer_transposed(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                                                   cno_row(sc, m.C, d, c), tg, last ? nullptr : &targets, lane)
+                    : eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                   cno_row(sc, m.C, d, c), d > 0 ? sc.P + (size_t)(d - 1) * layer_words : nullptr,
                                                   last ? nullptr : &targets, lane);
                 if (last) {

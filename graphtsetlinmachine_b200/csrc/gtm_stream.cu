@@ -107,21 +107,6 @@ __device__ __forceinline__ uint4 lds128(unsigned addr)
     return v;
 }
 
-// In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.
-__device__ __forceinline__ void transpose32(u32 (&a)[32])
-{
-    u32 mask = 0x0000ffffu;
-#pragma unroll
-    for (int j = 16; j != 0; j >>= 1, mask ^= mask << j) {
-#pragma unroll
-        for (int k = 0; k < 32; k = (k + j + 1) & ~j) {
-            const u32 t = ((a[k] >> j) ^ a[k + j]) & mask;
-            a[k] ^= t << j;
-            a[k + j] ^= t;
-        }
-    }
-}
-
 constexpr int kRTStride = 33;   // RT[cw][b * 33 + j] holds node 32j+b: conflict-free both for the writer (lanes = j) and the reader (lanes = b)
 
 template <int KP>
