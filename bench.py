@@ -422,6 +422,9 @@ def main():
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         ref_gpu = reference_kernels_on_gpu(tm, train, y_train, sums_host, batch)
 
+    int_peak = C.c_double(0.0)
+    _lib.check(lib.gtm_debug_logic_op_rate(tm._model, C.byref(int_peak)))     # measured LOP3 rate of this GPU (integer roofline)
+
     if rank == 0:
         peak, peak_kind = peaks()
         achieved = BYTES_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e9
@@ -442,7 +445,10 @@ def main():
                          "kernel": "stream_score_kernel, one launch per step",
                          "note": "integer / shared-memory bound (ncu: shared-memory wavefronts 68 % of peak, DRAM 0.3 %), see int_ops",
                          "int_ops": {"dense_lop3_per_graph": LOP3_PER_GRAPH,
-                                     "achieved_tlop3_s": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12}},
+                                     "achieved_tlop3_s": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12,
+                                     "peak_tlop3_s": int_peak.value,
+                                     "frac": LOP3_PER_GRAPH * n / (ms_per_step * 1e-3) / 1e12 / max(int_peak.value, 1e-9),
+                                     "peak_source": "register-resident independent LOP3 chains measured in this run (gtm_debug_logic_op_rate)"}},
             "cpu_baseline": cpu,
             "reference_kernels_on_gpu": ref_gpu,
             "host_side": host_side,

@@ -70,6 +70,7 @@ PROTOTYPES = {
                            C.c_void_p, C.c_void_p],
     "gtm_debug_last_feedback": [C.c_void_p, C.c_void_p, C.c_void_p],
     "gtm_debug_fit_phase_cycles": [C.c_void_p, C.c_void_p],
+    "gtm_debug_logic_op_rate": [C.c_void_p, C.POINTER(C.c_double)],
 }
 
 _lib = None

@@ -349,7 +349,7 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->score_t_stride = 0;
     ds->score_block = 256;
     ds->score_smem = (size_t)((d.K + 3) & ~3) * sizeof(int);
-    const size_t msg_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
+    const size_t msg_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);     // padded rows, see ScatterTargets
     {
         const int t_stride = ds->NC | 1;
         const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);
@@ -359,8 +359,8 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
             ds->score_block = 512;
         }
     }
-    if (d.D > 1 && (msg_bytes <= 8 * 1024 || (ds->score_t_stride > 0 && msg_bytes <= 64 * 1024))) {
-        ds->score_part_words = ds->max_nodes * d.MW;
+    if (d.D > 1 && (msg_bytes <= 8 * 1024 || (ds->score_t_stride > 0 && msg_bytes <= 72 * 1024))) {
+        ds->score_part_words = (int)(msg_bytes / sizeof(u32));
         ds->score_smem += msg_bytes;
     }
     if (ds->score_smem > 48 * 1024)
@@ -609,6 +609,53 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         return GTM_OK;
     }
     return fail(GTM_ERR_ARG, "path must be 0 (scoring kernel) or 1 (learning kernel)");
+}
+
+// Eight independent chains of three-input logic operations per thread, all in registers.
+__global__ void __launch_bounds__(256) logic_op_rate_kernel(int iterations, u32 seed, u32 *sink)
+{
+    u32 x[8], a = seed ^ (threadIdx.x * 2654435761u), b = seed + blockIdx.x * 40503u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = a * (2 * i + 3) + b;
+    for (int it = 0; it < iterations; ++it) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)                                       // one LOP3 each (bitwise select), chains independent of one another
+                asm volatile("lop3.b32 %0, %0, %1, %2, 0xCA;" : "+r"(x[i]) : "r"(a), "r"(b));
+        }
+    }
+    u32 v = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v ^= x[i];
+    if (v == 0x12345u) sink[0] = v;                                           // keeps the chains alive
+}
+
+extern "C" int gtm_debug_logic_op_rate(gtm_model *m, double *tera_ops_per_second_out)
+{
+    if (!m || !tera_ops_per_second_out) return fail(GTM_ERR_ARG, "null argument");
+    GTM_TRY(bind(m));
+    u32 *sink = nullptr;
+    GTM_TRY(dev_alloc(&sink, 1));
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    const int iterations = 4096, grid = m->sm_count * 16;
+    float ms = 0.0f;
+    for (int rep = 0; rep < 3; ++rep) {          // the last repetition is the one reported
+        cudaEventRecord(e0, m->stream);
+        logic_op_rate_kernel<<<grid, 256, 0, m->stream>>>(iterations, 1u + rep, sink);
+        cudaEventRecord(e1, m->stream);
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&ms, e0, e1);
+    }
+    cudaError_t e = cudaGetLastError();
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    GTM_CU(e);
+    *tera_ops_per_second_out = (double)grid * 256.0 * iterations * 64.0 / (ms * 1e-3) / 1e12;
+    return GTM_OK;
 }
 
 extern "C" int gtm_debug_fit_phase_cycles(gtm_model *m, uint64_t *cycles_out)

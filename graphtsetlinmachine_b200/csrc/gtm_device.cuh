@@ -165,9 +165,19 @@ struct ClauseView {
 constexpr int kMaxRanks = 8;
 struct ScatterTargets {
     int world;
-    u32 *local;            // CTA-local accumulation in shared memory [n][MW] of SOURCE-node bits (see flush_messages), or null
+    u32 *local;            // CTA-local accumulation in shared memory of SOURCE-node bits (see flush_messages), or null:
+                           // node v's MW words start at local_row(v) * (MW | 1) - odd row stride, and for the transposed
+                           // evaluation (lane = node word) the rows of the nodes of one word are `local_words` apart, so
+                           // that neither evaluation's lanes meet in one bank
+    int local_words;       // node words of the graph when the rows are in transposed order, 0 for node order
     u32 *base[kMaxRanks];
 };
+
+__device__ __forceinline__ u32 *local_row(const ScatterTargets &t, int v, int MW)
+{
+    const int r = t.local_words > 0 ? (v & 31) * t.local_words + (v >> 5) : v;
+    return t.local + (size_t)r * (MW | 1);
+}
 
 // Bits [32w, 32w+32) of the message vector `row` (MS bits in MW words) rotated up by t: bit j = row bit (j - t) mod MS.
 __device__ __forceinline__ u32 rotated_word(const u32 *row, int w, u32 t, int MS, int MW)
@@ -218,7 +228,7 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
         for (int q = 0; q < kInFlight; ++q) {
             // a source row without bits sends nothing
             if (deg[q] != 0) {
-                const u32 *row = t.local + (size_t)u[q] * MW;
+                const u32 *row = local_row(t, u[q], MW);
                 u32 any = 0;
                 for (int x = 0; x < MW; ++x) any |= row[x];
                 if (any == 0) deg[q] = 0;
@@ -236,7 +246,7 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
             for (int q = 0; q < kInFlight; ++q) {
                 if (dst[q] >= (u32)gv.n) continue;                         // no edge in this slot, or a malformed edge: never fault
                 const u32 tq = ty[q] >= (u32)MS ? ty[q] % (u32)MS : ty[q];
-                const u32 *row = t.local + (size_t)u[q] * MW;
+                const u32 *row = local_row(t, u[q], MW);
                 const u32 lo = rotated_word(row, w[q], tq, MS, MW);
                 if (pairs) {
                     const u32 hi = rotated_word(row, w[q] + 1, tq, MS, MW);
@@ -418,7 +428,7 @@ __device__ __forceinline__ u32 eval_node_words(const DevModel &m, const GraphVie
                     for (int b = 0; b < m.MB; ++b) {
                         u32 bit = cv.hv[b];
                         if (bit >= (u32)m.MS) bit %= (u32)m.MS;
-                        u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
+                        u32 *addr = local_row(*scatter, v, m.MW) + (bit >> 5);
                         const u32 mbit = 1u << (bit & 31);
                         if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
                     }
@@ -548,7 +558,7 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
                 for (int b = 0; b < m.MB; ++b) {
                     u32 bit = cv.hv[b];
                     if (bit >= (u32)m.MS) bit %= (u32)m.MS;
-                    u32 *addr = scatter->local + (size_t)v * m.MW + (bit >> 5);
+                    u32 *addr = local_row(*scatter, v, m.MW) + (bit >> 5);
                     const u32 mbit = 1u << (bit & 31);
                     if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
                 }

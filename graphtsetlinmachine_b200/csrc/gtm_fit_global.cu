@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 }
                 ScatterTargets targets;
                 targets.world = a.world;
-                targets.local = (!last && s_part != nullptr && gv.n * m.MW <= a.part_words) ? s_part : nullptr;
+                targets.local_words = 0;
+                targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) <= a.part_words) ? s_part : nullptr;
                 #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                     __syncthreads();
                     flush_messages(targets, gv, m.MS, m.MW);
                     __syncthreads();
-                    for (int t = threadIdx.x; t < gv.n * m.MW; t += blockDim.x) targets.local[t] = 0;
+                    for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) targets.local[t] = 0;
                 }
             }
             __syncthreads();

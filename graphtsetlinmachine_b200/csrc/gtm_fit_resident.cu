@@ -208,7 +208,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             }
             ScatterTargets targets;
             targets.world = a.world;
-            targets.local = (!last && s_part != nullptr && gv.n * m.MW <= a.part_words) ? s_part : nullptr;
+            targets.local_words = transposed ? tg.words : 0;
+            targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) <= a.part_words) ? s_part : nullptr;
             #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 __syncthreads();
                 flush_messages(targets, gv, m.MS, m.MW);
                 __syncthreads();
-                for (int t = threadIdx.x; t < gv.n * m.MW; t += blockDim.x) targets.local[t] = 0;
+                for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) targets.local[t] = 0;
             }
         }
         __syncthreads();
@@ -389,12 +390,12 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     int pre_words = 0;
     if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
     const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
-    const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
+    const size_t layer_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);   // message bits of one layer, padded rows
     // transposed-graph buffer (graph sets of 33..1024 nodes per graph, few node types): rows of max(L0, MW) words plus type masks
     const int t_stride = ds->NC | 1;
     const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);
     const bool t_possible = ds->max_nodes > 32 && ds->NC <= 32 && t_bytes <= 96 * 1024;
-    const bool part_possible = d.D > 1 && layer_bytes <= 64 * 1024;
+    const bool part_possible = d.D > 1 && layer_bytes <= 72 * 1024;
     // preference: the transposed evaluation first (it is worth an occupancy step), then two CTAs per SM, then the message
     // accumulation buffer with and without the graph staging buffers, then staging alone
     for (int with_t = t_possible ? 1 : 0; with_t >= 0; --with_t)
@@ -416,7 +417,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
                 p_smem_words = (int)p_words;
                 smem += 2 * p_words * sizeof(u32);
             } else if (with_part) {
-                part_words = ds->max_nodes * d.MW;
+                part_words = (int)(layer_bytes / sizeof(u32));
                 smem += layer_bytes;
             }
             if (with_t) smem += t_bytes;
@@ -512,8 +513,8 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         fn = fit_global_kernel(d.SB, ds->max_nodes > 32);
         block = m->fit_block;
         // one layer's messages are accumulated per CTA in shared memory when a layer takes at most 64 KB
-        const size_t layer_bytes = (size_t)ds->max_nodes * d.MW * sizeof(u32);
-        a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 64 * 1024) ? ds->max_nodes * d.MW : 0;
+        const size_t layer_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);
+        a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 72 * 1024) ? (int)(layer_bytes / sizeof(u32)) : 0;
         smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + (size_t)a.part_words * sizeof(u32);
         if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &sc, &a, &eval_only};

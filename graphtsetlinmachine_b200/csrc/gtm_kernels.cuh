@@ -89,13 +89,13 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
         const GraphView gv = global_graph(g, e, m.L0);
         const int n = gv.n;
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
-        const bool part = s_part != nullptr && n * m.MW <= a.part_words;     // source-node message bits fit the shared buffer
+        const bool part = s_part != nullptr && ((n + 31) & ~31) * (m.MW | 1) <= a.part_words;     // source-node message bits fit the shared buffer
         TransposedGraph tg;
         tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (n + 31) >> 5;
         const bool transposed = kBatchNodes && a.t_stride > 0 && n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         if (m.D > 1) {
             const size_t rows = (size_t)n * m.MW;
-            if (part) for (size_t t = threadIdx.x; t < rows; t += blockDim.x) s_part[t] = 0;
+            if (part) for (int t = threadIdx.x; t < ((n + 31) & ~31) * (m.MW | 1); t += blockDim.x) s_part[t] = 0;
             for (int d = 0; d < m.D - 1; ++d)
                 for (size_t t = threadIdx.x; t < rows; t += blockDim.x) sc.P[(size_t)d * layer_words + t] = 0;
         }
@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
             ScatterTargets targets;
             targets.world = 1;
             targets.local = part && !last ? s_part : nullptr;
+            targets.local_words = transposed ? tg.words : 0;
             targets.base[0] = sc.P + (size_t)d * layer_words;
             if (transposed) {
                 if (d == 0) {
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
                 // every clause has marked its bits on the source nodes: one walk over the edges makes the layer's messages
                 flush_messages(targets, gv, m.MS, m.MW);
                 __syncthreads();
-                for (int t = threadIdx.x; t < n * m.MW; t += blockDim.x) s_part[t] = 0;
+                for (int t = threadIdx.x; t < ((n + 31) & ~31) * (m.MW | 1); t += blockDim.x) s_part[t] = 0;
                 __syncthreads();
             }
         }

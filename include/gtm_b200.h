@@ -199,6 +199,11 @@ int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t 
  * its four phases, uint64[4] = {clause evaluation, waiting at grid barriers, summing vote partials, feedback}. */
 int gtm_debug_fit_phase_cycles(gtm_model *model, uint64_t *cycles_out);
 
+/* Measurement aid (no counterpart in the reference): the device's rate of register-resident, dependence-free 32-bit
+ * three-input logic operations (LOP3), in 1e12 operations per second - the denominator of the integer roofline that
+ * the word tests of clause evaluation are reported against.  Runs a short kernel on the model's device and stream. */
+int gtm_debug_logic_op_rate(gtm_model *model, double *tera_ops_per_second_out);
+
 #ifdef __cplusplus
 }
 #endif
