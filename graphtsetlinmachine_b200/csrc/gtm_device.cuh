@@ -513,6 +513,8 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
     const u32 *inc = cv.ta(d) + (size_t)(m.SB - 1) * W;
     const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
 
+    // lanes past the graph's last node word keep r == 0; they read column 0 so that no load leaves the buffer
+    const int col = lane < tg.words ? lane : 0;
     u32 r = lane < tg.words ? tg.TM[(size_t)(c % n_types) * tg.S + lane] : 0u;
     if (d > 0 && lane < tg.words) r &= prev[lane];
     int cnt = 0;
@@ -531,11 +533,11 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
                 const int b = __ffs(iw) - 1;
                 iw &= iw - 1;
                 if (d == 0) {
-                    r &= tg.T[(size_t)(b * WT + w) * tg.S + lane];
+                    r &= tg.T[(size_t)(b * WT + w) * tg.S + col];
                 } else {
                     const int l = 32 * w + b;                               // message literal: positive bits, then their complements
                     const int p = l < m.MS ? l : l - m.MS;
-                    const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + lane];
+                    const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + col];
                     r &= l < m.MS ? x : ~x;
                 }
             }

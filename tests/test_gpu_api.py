@@ -109,3 +109,17 @@ def test_other_model_classes_and_untrained_score(engine_lib):
     fresh = MultiClassGraphTsetlinMachine(4, 10, 2.0)
     with pytest.raises(SystemExit):
         fresh.score(test)
+
+
+def test_logic_op_rate_is_plausible(engine_lib):
+    """The measured LOP3 rate (integer-roofline denominator) lies between a tenth and ten times 148 SMs x 64 lanes x 2 GHz."""
+    import ctypes as C
+
+    from graphtsetlinmachine_b200 import _lib
+    from util import EngineTM
+
+    tm = EngineTM(clauses=4, classes=2, literals=32, threshold=4, s=2.0)
+    rate = C.c_double(0.0)
+    _lib.check(engine_lib.gtm_debug_logic_op_rate(tm.model, C.byref(rate)))
+    assert 1.9 < rate.value < 190.0
+    tm.close()

@@ -48,3 +48,35 @@ def test_engine_equals_checker_on_random_shapes(engine_lib, seed, clauses, class
         assert np.array_equal(a.score(), b.transform()[1])
     finally:
         b.close()
+
+
+@pytest.mark.parametrize("hv,ms,max_nodes,depth", [(24, 96, 40, 3), (5, 37, 70, 2), (40, 64, 33, 3), (16, 512, 200, 2)])
+def test_large_graphs_with_few_node_words(engine_lib, hv, ms, max_nodes, depth):
+    """Graphs of more than 32 nodes go through the transposed evaluation, whose rows are only as long as the graph
+    set's node words: shapes with two to seven node words, odd and even message word counts, against the checker."""
+    rng = np.random.default_rng(hv + ms)
+    np.random.seed(hv + ms)
+    n, clauses, classes, T = 24, 50, 2, 25
+    graphs = random_graphs(n, rng, hv_size=hv, hv_bits=2, max_nodes=max_nodes, node_types=2, edge_types=3)
+    graphs_big = random_graphs(n, rng, hv_size=hv, hv_bits=2, fixed_nodes=max_nodes, node_types=2, edge_types=3, init_with=graphs)
+    encY = encode_labels(rng.integers(0, classes, size=n), classes, T)
+    hvs = np.stack([rng.choice(ms, size=2, replace=False) for _ in range(clauses)]).astype(np.uint32)
+    kw = dict(clauses=clauses, classes=classes, literals=2 * hv, threshold=T, s=2.0, depth=depth, message_size=ms,
+              message_bits=2, max_nodes=max_nodes, hypervectors=hvs, seed=9)
+    for fit_kernel in (0, 1):
+        a, b = OracleTM(**kw), EngineTM(**kw, options={"fit_kernel": fit_kernel})
+        try:
+            for g in (graphs, graphs_big):
+                for tm in (a, b):
+                    tm.set_graphs(g)
+                    if g is graphs:
+                        tm.prepare()
+                    tm.fit(encY)
+                assert np.array_equal(a.ta_state, b.ta_state)
+                for x, y in zip(a.message_ta_state, b.message_ta_state):
+                    assert np.array_equal(x, y)
+                assert np.array_equal(a.clause_weights, b.clause_weights)
+                assert np.array_equal(a.score(), b.score())
+                assert np.array_equal(a.score(), b.transform()[1])
+        finally:
+            b.close()
