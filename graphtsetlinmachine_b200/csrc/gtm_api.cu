@@ -349,7 +349,7 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->score_t_stride = 0;
     ds->score_block = 256;
     ds->score_smem = (size_t)((d.K + 3) & ~3) * sizeof(int);
-    const size_t msg_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);     // padded rows, see ScatterTargets
+    const size_t msg_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);   // padded rows + per-type rows, see ScatterTargets
     {
         const int t_stride = ds->NC | 1;
         const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);

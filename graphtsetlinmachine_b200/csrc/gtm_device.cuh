@@ -163,6 +163,7 @@ struct ClauseView {
 // Message buffers that receive a scatter: the local one, or the same buffer on every GPU of a clause-sharded fit
 // (peer pointers; plain atomics over NVLink).
 constexpr int kMaxRanks = 8;
+constexpr int kTransposedTypes = 8;   // node types a transposed graph keeps masks for
 struct ScatterTargets {
     int world;
     u32 *local;            // CTA-local accumulation in shared memory of SOURCE-node bits (see flush_messages), or null:
@@ -170,6 +171,8 @@ struct ScatterTargets {
                            // evaluation (lane = node word) the rows of the nodes of one word are `local_words` apart, so
                            // that neither evaluation's lanes meet in one bank
     int local_words;       // node words of the graph when the rows are in transposed order, 0 for node order
+    u32 *all;              // [kTransposedTypes][MW | 1] bits of clauses that are true on EVERY node of their type (one mark
+                           // instead of one per node; flush_messages folds them into the rows), or null
     u32 *base[kMaxRanks];
 };
 
@@ -209,6 +212,16 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
 {
     // The merge is bound by the atomics that all CTAs send to the same rows: rows of an even number of words go out as
     // 64-bit atomics (half as many).  An item is (source node, word or word pair).
+    if (t.all != nullptr) {
+        for (int i = threadIdx.x; i < gv.n * MW; i += blockDim.x) {
+            const int u = i / MW, w = i - u * MW;
+            const u32 ty = gv.type[u];
+            const u32 v = ty < (u32)kTransposedTypes ? t.all[ty * (MW | 1) + w] : 0u;
+            if (v) local_row(t, u, MW)[w] |= v;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < kTransposedTypes * (MW | 1); i += blockDim.x) t.all[i] = 0;
+    }
     const bool pairs = (MW & 1) == 0;
     const int per_row = pairs ? MW >> 1 : MW;
     const int items = gv.n * per_row;
@@ -290,7 +303,6 @@ __device__ __forceinline__ void transpose32(u32 (&a)[32])
 // transposed positive message bits (a negated message literal ANDs the complement).
 // Storage: literal l = 32w + b lives at T[((b * W) + w) * S + j] with S odd (>= node words), so that the threads that
 // build it (adjacent w) and the lanes that read it (adjacent j) are both conflict-free.
-constexpr int kTransposedTypes = 8;   // node types a transposed graph keeps masks for
 struct TransposedGraph {
     u32 *T;        // [32 * Wmax][S] literal rows of the current layer (layer 0: literals, layer d: positive message bits)
     u32 *TM;       // [n_types][S] nodes of each type (valid nodes only)
@@ -529,17 +541,21 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
             nz &= nz - 1;
             u32 iw = __shfl_sync(kFull, iw_l, bw);
             const int w = w0 + bw;
+            // up to four included literals per step, their loads issued together
+            auto literal_row = [&](int b) -> u32 {
+                if (d == 0) return tg.T[(size_t)(b * WT + w) * tg.S + col];
+                const int l = 32 * w + b;                                   // message literal: positive bits, then their complements
+                const int p = l < m.MS ? l : l - m.MS;
+                const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + col];
+                return l < m.MS ? x : ~x;
+            };
             while (iw) {
-                const int b = __ffs(iw) - 1;
-                iw &= iw - 1;
-                if (d == 0) {
-                    r &= tg.T[(size_t)(b * WT + w) * tg.S + col];
-                } else {
-                    const int l = 32 * w + b;                               // message literal: positive bits, then their complements
-                    const int p = l < m.MS ? l : l - m.MS;
-                    const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + col];
-                    r &= l < m.MS ? x : ~x;
-                }
+                u32 x0, x1 = kFull, x2 = kFull, x3 = kFull;
+                x0 = literal_row(__ffs(iw) - 1); iw &= iw - 1;
+                if (iw) { x1 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                if (iw) { x2 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                if (iw) { x3 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                r &= (x0 & x1) & (x2 & x3);
             }
             alive = __any_sync(kFull, r != 0);
         }
@@ -550,6 +566,16 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
     else if (d > 0) r &= tg.TM[(size_t)(c % n_types) * tg.S + lane];         // complements set bits of missing nodes
     if (lane < tg.words) out[lane] = r;
     const u32 any = __ballot_sync(kFull, r != 0);
+    if (scatter && scatter->all != nullptr && any != 0 &&
+        __all_sync(kFull, lane >= tg.words || r == tg.TM[(size_t)(c % n_types) * tg.S + col])) {
+        // true on every node of its type: one mark per hypervector bit for the whole type
+        if (lane < m.MB) {
+            u32 bit = cv.hv[lane];
+            if (bit >= (u32)m.MS) bit %= (u32)m.MS;
+            atomicOr(scatter->all + (size_t)(c % n_types) * (m.MW | 1) + (bit >> 5), 1u << (bit & 31));
+        }
+        return any;
+    }
     if (scatter && r) {
         u32 bits = r;
         while (bits) {

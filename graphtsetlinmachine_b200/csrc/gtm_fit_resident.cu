@@ -209,7 +209,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             ScatterTargets targets;
             targets.world = a.world;
             targets.local_words = transposed ? tg.words : 0;
-            targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) <= a.part_words) ? s_part : nullptr;
+            // the last kTransposedTypes rows of the buffer hold the marks of clauses that are true on every node of their type
+            const int all_words = kTransposedTypes * (m.MW | 1);
+            targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) + all_words <= a.part_words) ? s_part : nullptr;
+            targets.all = (targets.local != nullptr && transposed) ? s_part + a.part_words - all_words : nullptr;
             #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
@@ -390,7 +393,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     int pre_words = 0;
     if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
     const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
-    const size_t layer_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);   // message bits of one layer, padded rows
+    const size_t layer_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);   // message bits of one layer: padded rows + per-type rows
     // transposed-graph buffer (graph sets of 33..1024 nodes per graph, few node types): rows of max(L0, MW) words plus type masks
     const int t_stride = ds->NC | 1;
     const size_t t_bytes = ((size_t)32 * std::max(d.L0, d.MW) + kTransposedTypes) * t_stride * sizeof(u32);
@@ -513,7 +516,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         fn = fit_global_kernel(d.SB, ds->max_nodes > 32);
         block = m->fit_block;
         // one layer's messages are accumulated per CTA in shared memory when a layer takes at most 64 KB
-        const size_t layer_bytes = (size_t)((ds->max_nodes + 31) & ~31) * (d.MW | 1) * sizeof(u32);
+        const size_t layer_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);
         a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 72 * 1024) ? (int)(layer_bytes / sizeof(u32)) : 0;
         smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + (size_t)a.part_words * sizeof(u32);
         if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

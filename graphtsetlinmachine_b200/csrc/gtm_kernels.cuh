@@ -89,13 +89,14 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
         const GraphView gv = global_graph(g, e, m.L0);
         const int n = gv.n;
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
-        const bool part = s_part != nullptr && ((n + 31) & ~31) * (m.MW | 1) <= a.part_words;     // source-node message bits fit the shared buffer
+        const int all_words = kTransposedTypes * (m.MW | 1);    // the buffer's last rows: marks of clauses true on every node of their type
+        const bool part = s_part != nullptr && ((n + 31) & ~31) * (m.MW | 1) + all_words <= a.part_words;     // source-node message bits fit the shared buffer
         TransposedGraph tg;
         tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (n + 31) >> 5;
         const bool transposed = kBatchNodes && a.t_stride > 0 && n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         if (m.D > 1) {
             const size_t rows = (size_t)n * m.MW;
-            if (part) for (int t = threadIdx.x; t < ((n + 31) & ~31) * (m.MW | 1); t += blockDim.x) s_part[t] = 0;
+            if (part) for (int t = threadIdx.x; t < a.part_words; t += blockDim.x) s_part[t] = 0;
             for (int d = 0; d < m.D - 1; ++d)
                 for (size_t t = threadIdx.x; t < rows; t += blockDim.x) sc.P[(size_t)d * layer_words + t] = 0;
         }
@@ -106,6 +107,7 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
             targets.world = 1;
             targets.local = part && !last ? s_part : nullptr;
             targets.local_words = transposed ? tg.words : 0;
+            targets.all = (targets.local != nullptr && transposed) ? s_part + a.part_words - all_words : nullptr;
             targets.base[0] = sc.P + (size_t)d * layer_words;
             if (transposed) {
                 if (d == 0) {
