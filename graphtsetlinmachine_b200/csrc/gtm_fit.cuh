@@ -26,6 +26,7 @@ struct FitArgs {
     int NC;                 // node words of the largest graph
     int pre_words;          // words per clause for pre-generated Type-I masks (0 = every clause generates its own)
     int t_stride;           // > 0: the CTA has a transposed-graph buffer with this (odd) row stride, see TransposedGraph
+    int timers;             // CTA 0 accumulates phase cycle counts (gtm_debug_fit_phase_cycles); off by default: the reads sit on the critical path
     int stage;              // the state-resident kernel has its two graph staging buffers (0: every graph is read in place)
     int part_words;         // > 0: shared-memory words per CTA that accumulate one layer's messages before they are merged
     int solo;               // one CTA learns the whole model: CTA barriers replace the grid barrier and the vote exchange

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
         arrivals += gridDim.x * a.world;
         if (!grid_barrier(a, arrivals)) return;
     }
-    const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
+    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x == 0;
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t0 = clock64(), t1;
 
     u64 step = 0;

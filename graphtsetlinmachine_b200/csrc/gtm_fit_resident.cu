@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         arrivals += gridDim.x * a.world;
         if (!grid_barrier(a, arrivals)) return;
     }
-    const bool timer = blockIdx.x == 0 && threadIdx.x == 0;
+    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x == 0;
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t_x0 = 0, t_x1 = 0, t_x2 = 0, t_x3 = 0, t0 = clock64(), t1;
 
     int slot3 = 0;   // step % 3
@@ -458,6 +458,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
     a.class_sum_tap = m->class_sum_tap;
     a.phase_cycles = m->phase_cycles;
+    a.timers = m->opt_fit_timers;
     a.NC = ds->NC;
     const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
     GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));

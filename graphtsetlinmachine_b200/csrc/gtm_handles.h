@@ -21,6 +21,7 @@ struct gtm_model {
     int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
     unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
     int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
+    int opt_fit_timers = 0;                   // 1: the learning kernels time their phases (gtm_debug_fit_phase_cycles)
     int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel
     unsigned *barrier = nullptr;
     unsigned long long *phase_cycles = nullptr;

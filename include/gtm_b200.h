@@ -89,6 +89,7 @@ int gtm_set_stream(gtm_model *model, void *cuda_stream);
 /* Kernel selection (the reference has one code path; its only launch knobs are grid/block, tm.py:53-54).
  *   "fit_kernel":   0 = automatic, 1 = learning kernel with state in global memory, 2 = state-resident kernel
  *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel
+ *   "fit_timers":   1 = the learning kernels time their phases for gtm_debug_fit_phase_cycles (default 0)
  * Forcing a kernel that cannot serve the model makes the next fit / score call fail with GTM_ERR_ARG. */
 int gtm_set_option(gtm_model *model, const char *name, int value);
 
@@ -196,7 +197,9 @@ int gtm_debug_evaluate(gtm_model *model, gtm_dataset *dataset, int number_of_nod
 int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t *class_clause_update_out);
 
 /* Profiling tap (no counterpart in the reference): SM clock cycles that CTA 0 of the last gtm_fit launch spent in
- * its four phases, uint64[4] = {clause evaluation, waiting at grid barriers, summing vote partials, feedback}. */
+ * its phases, uint64[8] = {clause evaluation, waiting at grid barriers, summing vote partials, end of step, and for the
+ * state-resident kernel: decisions, work-item table, mask generation, automaton updates}.  Filled only by launches made
+ * after gtm_set_option(model, "fit_timers", 1): the clock reads sit on the per-graph critical path. */
 int gtm_debug_fit_phase_cycles(gtm_model *model, uint64_t *cycles_out);
 
 /* Measurement aid (no counterpart in the reference): the device's rate of register-resident, dependence-free 32-bit
