@@ -71,6 +71,7 @@ PROTOTYPES = {
     "gtm_debug_last_feedback": [C.c_void_p, C.c_void_p, C.c_void_p],
     "gtm_debug_fit_phase_cycles": [C.c_void_p, C.c_void_p],
     "gtm_debug_logic_op_rate": [C.c_void_p, C.POINTER(C.c_double)],
+    "gtm_dataset_create_scored": [C.c_void_p, C.POINTER(GraphsView), C.c_int, C.c_void_p, C.POINTER(C.c_void_p)],
 }
 
 _lib = None

@@ -285,12 +285,12 @@ extern "C" int gtm_set_recorded_draws(gtm_model *m, const uint32_t *draws, uint6
 
 // --------------------------------------------------------------------------------------------- datasets
 template <class T>
-static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s)
+static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s, bool copy = true)
 {
     T *p;
     GTM_TRY(pool_alloc(&p, count, s));
     ds->owned.push_back(p);
-    if (count && host) GTM_CU(cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, s));
+    if (copy && count && host) GTM_CU(cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, s));
     *dev = p;
     return GTM_OK;
 }
@@ -303,17 +303,19 @@ static int scratch(gtm_dataset *ds, T **dev, size_t count)
     return GTM_OK;
 }
 
-static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds)
+// copy_arrays == false: the per-node and per-graph arrays are only allocated; the caller copies them in pieces
+// (gtm_dataset_create_scored).
+static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds, bool copy_arrays = true)
 {
     const DevModel &d = m->dm;
     cudaStream_t s = m->stream;
-    GTM_TRY(upload(ds, &ds->dg.X, v->X, (size_t)v->total_nodes * d.L0, s));
-    GTM_TRY(upload(ds, &ds->dg.node_type, v->node_type, (size_t)v->total_nodes, s));
-    GTM_TRY(upload(ds, &ds->dg.degree, v->number_of_graph_node_edges, (size_t)v->total_nodes, s));
-    GTM_TRY(upload(ds, &ds->dg.edge_index, v->edge_index, (size_t)v->total_nodes, s));
+    GTM_TRY(upload(ds, &ds->dg.X, v->X, (size_t)v->total_nodes * d.L0, s, copy_arrays));
+    GTM_TRY(upload(ds, &ds->dg.node_type, v->node_type, (size_t)v->total_nodes, s, copy_arrays));
+    GTM_TRY(upload(ds, &ds->dg.degree, v->number_of_graph_node_edges, (size_t)v->total_nodes, s, copy_arrays));
+    GTM_TRY(upload(ds, &ds->dg.edge_index, v->edge_index, (size_t)v->total_nodes, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s));
-    GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s));
-    GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s));
+    GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s, copy_arrays));
+    GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s, copy_arrays));
     if (v->total_edges == 0) {
         u32 *zeros;
         GTM_TRY(scratch(ds, &zeros, (size_t)v->number_of_graphs));
@@ -380,7 +382,7 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     return GTM_OK;
 }
 
-extern "C" int gtm_dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **out)
+static int dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **out, bool copy_arrays)
 {
     GTM_TRY(bind(m));
     if (!v || !out) return fail(GTM_ERR_ARG, "null argument");
@@ -398,10 +400,15 @@ extern "C" int gtm_dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_da
     ds->n_graphs = v->number_of_graphs; ds->total_nodes = v->total_nodes; ds->total_edges = v->total_edges;
     ds->max_nodes = v->max_number_of_graph_nodes;
     ds->NC = words_for(ds->max_nodes);
-    int st = dataset_build(m, v, ds);
+    int st = dataset_build(m, v, ds, copy_arrays);
     if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
     *out = ds;
     return GTM_OK;
+}
+
+extern "C" int gtm_dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **out)
+{
+    return dataset_create(m, v, out, true);
 }
 
 extern "C" int gtm_dataset_destroy(gtm_dataset *ds)
@@ -498,6 +505,94 @@ extern "C" int gtm_score(gtm_model *m, gtm_dataset *ds, int n_types, int64_t fir
     if (st == GTM_OK && e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     if (st != GTM_OK) return st;
     GTM_CU(e);
+    return GTM_OK;
+}
+
+// Upload and scoring of a whole host graph set in one call.  Sets of single-node graphs that the node-stream kernel
+// covers are pipelined: the arrays go up in chunks of two full waves of tiles on a copy stream, each chunk is scored as
+// soon as it has landed, and its class sums go back on a second copy stream while the next chunk is scored.  Other
+// sets take gtm_dataset_create followed by gtm_score.  The dataset stays valid for later calls either way.
+extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v, int n_types, int32_t *out,
+                                         gtm_dataset **dataset_out)
+{
+    GTM_TRY(bind(m));
+    if (!v || !out || !dataset_out) return fail(GTM_ERR_ARG, "null argument");
+    *dataset_out = nullptr;
+    if (!m->has_state) return fail(GTM_ERR_STATE, "model has no state: call gtm_init_state or gtm_set_ta_state first");
+    if (n_types < 1) return fail(GTM_ERR_ARG, "number_of_node_types must be positive");
+    const bool pipelined = v->max_number_of_graph_nodes == 1 && v->total_edges == 0 && v->total_nodes == v->number_of_graphs &&
+                           m->opt_score_kernel != 1 && m->sm.lit_off != nullptr && n_types <= 8;   // what the node-stream kernel may cover; stream_supported decides
+    gtm_dataset *ds = nullptr;
+    GTM_TRY(dataset_create(m, v, &ds, !pipelined));
+    const int64_t n = ds->n_graphs;
+    int st = GTM_OK;
+    if (!pipelined || !stream_supported(ds->sd, n_types) || ds->sd.graphs_per_tile <= 0) {
+        if (pipelined) {   // the arrays were not copied, but the node-stream kernel turned out not to cover the set
+            gtm_dataset_destroy(ds);
+            ds = nullptr;
+            GTM_TRY(dataset_create(m, v, &ds, true));
+        }
+        st = gtm_score(m, ds, n_types, 0, n, out);
+        if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
+        *dataset_out = ds;
+        return GTM_OK;
+    }
+
+    const DevModel &d = m->dm;
+    cudaStream_t in = nullptr, back = nullptr;
+    std::vector<cudaEvent_t> events;
+    int *dev = nullptr;
+    auto body = [&]() -> int {
+        GTM_CU(cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking));
+        GTM_CU(cudaStreamCreateWithFlags(&back, cudaStreamNonBlocking));
+        GTM_TRY(refresh_lists(m));
+        GTM_TRY(pool_alloc(&dev, (size_t)n * d.K, m->stream));
+        auto event = [&](cudaStream_t s, cudaEvent_t *e) -> int {
+            GTM_CU(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+            events.push_back(*e);
+            GTM_CU(cudaEventRecord(*e, s));
+            return GTM_OK;
+        };
+        cudaEvent_t ready;
+        GTM_TRY(event(m->stream, &ready));                 // allocations and literal lists are in stream order
+        GTM_CU(cudaStreamWaitEvent(in, ready, 0));
+        const int64_t chunk = std::max<int64_t>(1, (int64_t)ds->sd.grid * 2) * ds->sd.graphs_per_tile;
+        for (int64_t g0 = 0; g0 < n; g0 += chunk) {
+            const size_t cnt = (size_t)std::min<int64_t>(chunk, n - g0);
+            // one node per graph: node ranges are graph ranges
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.X) + (size_t)g0 * d.L0, v->X + (size_t)g0 * d.L0, cnt * d.L0 * sizeof(u32), cudaMemcpyHostToDevice, in));
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.node_type) + g0, v->node_type + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.degree) + g0, v->number_of_graph_node_edges + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.edge_index) + g0, v->edge_index + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+            // one element more: a tile ends where the next graph's nodes begin
+            const size_t cnt_index = cnt + (g0 + (int64_t)cnt < n ? 1 : 0);
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.node_index) + g0, v->node_index + g0, cnt_index * sizeof(u32), cudaMemcpyHostToDevice, in));
+            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.n_nodes) + g0, v->number_of_graph_nodes + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+            cudaEvent_t landed, scored;
+            GTM_TRY(event(in, &landed));
+            GTM_CU(cudaStreamWaitEvent(m->stream, landed, 0));
+            GTM_TRY(stream_score(m->sm, ds->sd, d, ds->dg, n_types, g0, (int64_t)cnt, dev + (size_t)g0 * d.K, m->stream));
+            GTM_TRY(event(m->stream, &scored));
+            GTM_CU(cudaStreamWaitEvent(back, scored, 0));
+            GTM_CU(cudaMemcpyAsync(out + (size_t)g0 * d.K, dev + (size_t)g0 * d.K, cnt * d.K * sizeof(int), cudaMemcpyDeviceToHost, back));
+        }
+        GTM_CU(cudaStreamSynchronize(in));
+        GTM_CU(cudaStreamSynchronize(back));
+        GTM_CU(cudaStreamSynchronize(m->stream));
+        return GTM_OK;
+    };
+    st = body();
+    if (st != GTM_OK) {                                    // nothing may still be reading the host arrays when the call returns
+        if (in) cudaStreamSynchronize(in);
+        if (back) cudaStreamSynchronize(back);
+        cudaStreamSynchronize(m->stream);
+    }
+    if (dev) cudaFreeAsync(dev, m->stream);
+    for (cudaEvent_t e : events) cudaEventDestroy(e);
+    if (in) cudaStreamDestroy(in);
+    if (back) cudaStreamDestroy(back);
+    if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
+    *dataset_out = ds;
     return GTM_OK;
 }
 

@@ -38,7 +38,8 @@ def _u32(a):
 class _Dataset:
     """A graph set resident on the device (the uploads of tm.py:528-555 / :759-784)."""
 
-    def __init__(self, lib, model, graphs):
+    def __init__(self, lib, model, graphs, class_sums_out=None):
+        """With `class_sums_out` (int32[N][outputs]) the set is scored while it is uploaded (one pipelined call)."""
         self._lib = lib
         self.handle = C.c_void_p()
         # keep the converted arrays alive for the duration of the call only; the engine copies them
@@ -53,7 +54,11 @@ class _Dataset:
         view.total_nodes = int(X.shape[0])
         view.total_edges = int(graphs.edge.shape[0]) if graphs.edge.size else 0
         view.max_number_of_graph_nodes = int(graphs.max_number_of_graph_nodes)
-        _lib.check(lib.gtm_dataset_create(model, C.byref(view), C.byref(self.handle)))
+        if class_sums_out is None:
+            _lib.check(lib.gtm_dataset_create(model, C.byref(view), C.byref(self.handle)))
+        else:
+            _lib.check(lib.gtm_dataset_create_scored(model, C.byref(view), int(graphs.number_of_node_types()),
+                                                     _ptr(class_sums_out), C.byref(self.handle)))
 
     def close(self):
         if self.handle:
@@ -327,10 +332,21 @@ class CommonTsetlinMachine:
     def _score(self, graphs, out=None):
         """tm.py:786-812: raw class sums int32[N][outputs]; one batched launch instead of a per-graph loop.
         `out` (optional, C-contiguous int32[N][outputs], e.g. page-locked) receives the result in place."""
-        self._score_init(graphs)
+        if not self.initialized:
+            print("Error: Model not trained.")
+            sys.exit(-1)
         class_sum = np.zeros((graphs.number_of_graphs, self.number_of_outputs), dtype=np.int32) if out is None else out
         assert class_sum.dtype == np.int32 and class_sum.flags.c_contiguous
         assert class_sum.shape == (graphs.number_of_graphs, self.number_of_outputs)
+        if not np.array_equal(self.graphs_signature_test, graphs.signature):
+            # a new graph set: upload and scoring in one pipelined call; the set stays resident for later calls
+            if self._test_set is not None:
+                self._test_set.close()
+                self._test_set = None
+            self.graphs_signature_test = np.array([])
+            self._test_set = _Dataset(self._lib, self._model, graphs, class_sums_out=class_sum)
+            self.graphs_signature_test = graphs.signature
+            return class_sum
         _lib.check(self._lib.gtm_score(self._model, self._test_set.handle, int(graphs.number_of_node_types()), 0,
                                        int(graphs.number_of_graphs), _ptr(class_sum)))
         return class_sum

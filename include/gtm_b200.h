@@ -129,6 +129,14 @@ int gtm_dataset_destroy(gtm_dataset *dataset);
  * class_sums_device and returns without synchronising (work is queued on the model's stream). */
 int gtm_score(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
               int32_t *class_sums_out);
+
+/* Upload + scoring of a whole graph set in one call (the reference does both inside `_score`: tm.py:759-784 uploads,
+ * tm.py:786-812 scores): class_sums_out int32[number_of_graphs][CLASSES]; *dataset_out is the resident graph set, as
+ * from gtm_dataset_create, for later calls.  Sets of single-node graphs are pipelined - chunks are scored while the next
+ * chunk is still being copied and the previous chunk's sums are on their way back; page-locked host arrays make the
+ * copies asynchronous.  Host pointers are borrowed for the call only. */
+int gtm_dataset_create_scored(gtm_model *model, const gtm_graphs_view *graphs, int number_of_node_types,
+                              int32_t *class_sums_out, gtm_dataset **dataset_out);
 int gtm_score_device(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first,
                      int64_t count, int32_t *class_sums_device);
 

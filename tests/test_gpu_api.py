@@ -123,3 +123,26 @@ def test_logic_op_rate_is_plausible(engine_lib):
     _lib.check(engine_lib.gtm_debug_logic_op_rate(tm.model, C.byref(rate)))
     assert 1.9 < rate.value < 190.0
     tm.close()
+
+
+def test_pipelined_scoring_equals_resident_scoring(engine_lib):
+    """A new set of single-node graphs is scored while it is uploaded, in several chunks; the result equals scoring
+    the resident set, and the rows of a replicated set repeat."""
+    protos = datasets.image_prototypes(1)
+    np.random.seed(3)
+    train, y = datasets.vanilla_images(1500, 2, protos)
+    unique, _ = datasets.vanilla_images(1 << 16, 4, protos, init_with=train)
+    batch = datasets.replicate(unique, 12)                     # 786,432 graphs: more than one chunk of two tile waves
+    tm = MultiClassGraphTsetlinMachine(300, 400, 10.0, depth=1, seed=2)
+    tm.fit(train, y, epochs=1, incremental=True)
+    first = tm.score(batch).copy()                             # upload + scoring in one call
+    again = tm.score(batch)                                    # the set is resident now
+    assert np.array_equal(first, again)
+    small = tm.score(unique)
+    assert np.array_equal(first.reshape(12, 1 << 16, -1), np.broadcast_to(small, (12,) + small.shape))
+    other, _ = datasets.sequences(6, 5)                        # a set the pipeline does not cover takes the plain path
+    tm2 = MultiClassGraphTsetlinMachine(20, 20, 3.0, depth=2, message_size=64, message_bits=2, seed=2)
+    y2 = np.array([0, 1, 0, 1, 0, 1], dtype=np.uint32)
+    tm2.fit(other, y2, epochs=1, incremental=True)
+    a = tm2.score(other).copy()
+    assert np.array_equal(a, tm2.score(other))
