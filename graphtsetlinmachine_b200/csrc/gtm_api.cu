@@ -16,8 +16,9 @@
 #include "gtm_kernels.cuh"
 
 // The general scoring kernel with or without four-at-a-time node words (graph sets with more than 32 nodes per graph).
-static const void *score_kernel_for(int max_nodes)
+static const void *score_kernel_for(int max_nodes, int units = 1)
 {
+    if (units > 1) return (const void *)score_small_graphs_kernel;
     return max_nodes > 32 ? (const void *)score_graphs_kernel<true> : (const void *)score_graphs_kernel<false>;
 }
 
@@ -366,10 +367,19 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
         ds->score_part_words = (int)(msg_bytes / sizeof(u32));
         ds->score_smem += msg_bytes;
     }
+    // small models on small graphs: a warp per graph, eight graphs per CTA (score_small_graphs_kernel)
+    ds->score_units = 1;
+    if (ds->max_nodes <= 32 && d.C <= 128) {
+        const size_t per_warp = ((size_t)((d.K + 3) & ~3) + ds->score_part_words) * sizeof(int);
+        if (8 * per_warp <= 40 * 1024) {
+            ds->score_units = 8;
+            ds->score_smem = 8 * per_warp;
+        }
+    }
     if (ds->score_smem > 48 * 1024)
         GTM_CU(cudaFuncSetAttribute(score_kernel_for(ds->max_nodes), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ds->score_smem));
     int per_sm = 0;
-    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_kernel_for(ds->max_nodes), ds->score_block, ds->score_smem));
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, score_kernel_for(ds->max_nodes, ds->score_units), ds->score_block, ds->score_smem));
     ds->score_grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)m->sm_count * std::max(1, per_sm), v->number_of_graphs));
     ds->cno_stride = (size_t)2 * d.C * ds->NC;
     ds->P_stride = p_words;
@@ -439,9 +449,10 @@ static int check_range(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first
 static int ensure_score_scratch(gtm_dataset *ds)
 {
     if (ds->score_sc.cno) return GTM_OK;
-    GTM_TRY(scratch(ds, &ds->score_sc.cno, ds->cno_stride * ds->score_grid));
-    GTM_TRY(scratch(ds, &ds->score_sc.P, ds->P_stride * ds->score_grid));
-    GTM_TRY(scratch(ds, &ds->score_sc.n_inc, ds->ninc_stride * ds->score_grid));
+    const size_t slices = (size_t)ds->score_grid * ds->score_units;     // one slice per graph in flight
+    GTM_TRY(scratch(ds, &ds->score_sc.cno, ds->cno_stride * slices));
+    GTM_TRY(scratch(ds, &ds->score_sc.P, ds->P_stride * slices));
+    GTM_TRY(scratch(ds, &ds->score_sc.n_inc, ds->ninc_stride * slices));
     return GTM_OK;
 }
 
@@ -455,12 +466,12 @@ static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int6
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = clause_out_dev;
     a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
     a.part_words = ds->score_part_words; a.t_stride = ds->score_t_stride;
-    const int grid = (int)std::min<int64_t>(ds->score_grid, count);
+    const int grid = (int)std::min<int64_t>(ds->score_grid, (count + ds->score_units - 1) / ds->score_units);
     {
         DevModel dm = m->dm;
         EvalScratch sc = ds->score_sc;
         void *args[] = {&dm, &g, &sc, &a};
-        GTM_CU(cudaLaunchKernel(score_kernel_for(ds->max_nodes), dim3(grid), dim3(ds->score_block), args, ds->score_smem, m->stream));
+        GTM_CU(cudaLaunchKernel(score_kernel_for(ds->max_nodes, ds->score_units), dim3(grid), dim3(ds->score_block), args, ds->score_smem, m->stream));
     }
     GTM_CU(cudaGetLastError());
     return GTM_OK;

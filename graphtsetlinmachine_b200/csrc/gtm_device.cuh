@@ -208,30 +208,31 @@ __device__ __forceinline__ u32 rotated_word(const u32 *row, int w, u32 t, int MS
 // node in a CTA-local buffer (MB atomics per true clause-node pair, no edge walk), and once per CTA and layer this
 // routine walks the graph's edges and ORs the rotated source rows into the destination rows of every target buffer.
 // All threads of the CTA, between two CTA barriers; the local buffer is cleared by the caller afterwards.
-__device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW)
+// `tid` / `nthreads`: the cooperating threads (a CTA by default, or one warp: lane, 32 - then t.all must be null).
+__device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW, int tid, int nthreads)
 {
     // The merge is bound by the atomics that all CTAs send to the same rows: rows of an even number of words go out as
     // 64-bit atomics (half as many).  An item is (source node, word or word pair).
     if (t.all != nullptr) {
-        for (int i = threadIdx.x; i < gv.n * MW; i += blockDim.x) {
+        for (int i = tid; i < gv.n * MW; i += nthreads) {
             const int u = i / MW, w = i - u * MW;
             const u32 ty = gv.type[u];
             const u32 v = ty < (u32)kTransposedTypes ? t.all[ty * (MW | 1) + w] : 0u;
             if (v) local_row(t, u, MW)[w] |= v;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < kTransposedTypes * (MW | 1); i += blockDim.x) t.all[i] = 0;
+        for (int i = tid; i < kTransposedTypes * (MW | 1); i += nthreads) t.all[i] = 0;
     }
     const bool pairs = (MW & 1) == 0;
     const int per_row = pairs ? MW >> 1 : MW;
     const int items = gv.n * per_row;
     constexpr int kInFlight = 4;      // items per thread whose CSR loads are issued together
-    for (int i0 = threadIdx.x; i0 < items; i0 += kInFlight * blockDim.x) {
+    for (int i0 = tid; i0 < items; i0 += kInFlight * nthreads) {
         int u[kInFlight], w[kInFlight];
         u32 e0[kInFlight], deg[kInFlight], maxdeg = 0;
 #pragma unroll
         for (int q = 0; q < kInFlight; ++q) {
-            const int i = i0 + q * blockDim.x;
+            const int i = i0 + q * nthreads;
             u[q] = i < items ? i / per_row : 0;
             w[q] = (i - u[q] * per_row) << (pairs ? 1 : 0);
             e0[q] = gv.eidx[u[q]] - gv.e_off;
@@ -278,6 +279,11 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
             }
         }
     }
+}
+
+__device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW)
+{
+    flush_messages(t, gv, MS, MW, (int)threadIdx.x, (int)blockDim.x);
 }
 
 // In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.

@@ -59,6 +59,7 @@ struct gtm_dataset {
     EvalScratch score_sc;
     size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
     int score_grid = 0;
+    int score_units = 1;           // graphs in flight per CTA of the general scoring path: 1 (a CTA per graph) or 8 (a warp per graph)
     int score_block = 256;         // threads per CTA of the general scoring kernel
     int score_t_stride = 0;        // row stride of the general scoring kernel's transposed-graph buffer (0 = none)
     int score_part_words = 0;      // shared-memory message accumulation of the general scoring kernel (0 = none)

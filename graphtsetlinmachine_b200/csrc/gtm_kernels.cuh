@@ -146,4 +146,66 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
     }
 }
 
+// The same for small models on small graphs (at most 32 nodes): ONE WARP per graph, eight graphs per CTA in flight -
+// a whole CTA per graph would leave most of its warps without a clause.  Scratch slices and the shared-memory words
+// (vote partial, then message accumulation) are per warp; warp barriers replace the CTA barriers.
+__global__ void __launch_bounds__(256, 5) score_small_graphs_kernel(DevModel m, DevGraphs g, EvalScratch sc0, ScoreArgs a)
+{
+    extern __shared__ int s_dyn[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int K4 = (m.K + 3) & ~3;
+    int *s_sum = s_dyn + (size_t)warp * (K4 + a.part_words);
+    u32 *s_part = a.part_words > 0 ? reinterpret_cast<u32 *>(s_sum + K4) : nullptr;
+    const int64_t unit = (int64_t)blockIdx.x * nwarps + warp, units = (int64_t)gridDim.x * nwarps;
+    EvalScratch sc = sc0;
+    sc.cno += unit * a.cno_stride;
+    sc.P += unit * a.P_stride;
+    sc.n_inc += unit * a.ninc_stride;
+    const size_t layer_words = (size_t)sc.max_nodes * m.MW;
+    const int row_words = 32 * (m.MW | 1);                     // message-bit rows of a graph of at most 32 nodes
+
+    for (int64_t i = unit; i < a.count; i += units) {
+        const int64_t e = a.first + i;
+        const GraphView gv = global_graph(g, e, m.L0);
+        const int n = gv.n;
+        for (int k = lane; k < m.K; k += 32) s_sum[k] = 0;
+        const bool part = s_part != nullptr && n <= 32 && row_words <= a.part_words;
+        if (m.D > 1) {
+            if (part) for (int t = lane; t < row_words; t += 32) s_part[t] = 0;
+            for (int d = 0; d < m.D - 1; ++d)
+                for (int t = lane; t < n * m.MW; t += 32) sc.P[(size_t)d * layer_words + t] = 0;
+        }
+        __syncwarp();
+        for (int d = 0; d < m.D; ++d) {
+            const bool last = d == m.D - 1;
+            ScatterTargets targets;
+            targets.world = 1;
+            targets.local = part && !last ? s_part : nullptr;
+            targets.local_words = 0;
+            targets.all = nullptr;
+            targets.base[0] = sc.P + (size_t)d * layer_words;
+            for (int c = 0; c < m.C; ++c) {
+                const ClauseView cv = global_view(m, sc.n_inc, c);
+                const u32 any = eval_clause_layer<false>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
+                                                         cno_row(sc, m.C, d, c), d > 0 ? sc.P + (size_t)(d - 1) * layer_words : nullptr,
+                                                         last ? nullptr : &targets, lane);
+                if (last) {
+                    if (any)
+                        for (int k = lane; k < m.K; k += 32) s_sum[k] += m.weights[(size_t)k * m.C + c];
+                    if (a.clause_outputs && lane == 0) a.clause_outputs[(size_t)i * m.C + c] = any != 0;
+                }
+            }
+            __syncwarp();
+            if (targets.local) {
+                flush_messages(targets, gv, m.MS, m.MW, lane, 32);
+                __syncwarp();
+                for (int t = lane; t < row_words; t += 32) s_part[t] = 0;
+                __syncwarp();
+            }
+        }
+        for (int k = lane; k < m.K; k += 32) a.class_sums[(size_t)i * m.K + k] = s_sum[k];
+        __syncwarp();
+    }
+}
+
 }  // namespace gtm
