@@ -12,7 +12,7 @@ reference text is the replacement of its ``#include <curand_kernel.h>`` line by 
 Because the reference specialises its kernels by preprocessor constants, one shared object is built per
 hyper-parameter set; ``config_key`` names it.  The intermediate translation unit is deleted after compiling.
 
-The reference checkout is looked up in ``$GTM_REFERENCE``, ``baseline/_ref`` and ``/root/reference``; when none
+The reference checkout is looked up in ``$GTM_REFERENCE``, ``baseline/_ref`` and ``DEFAULT_REFERENCE``; when none
 is present (e.g. on a GPU box) only shared objects built earlier can be used.
 """
 
@@ -32,9 +32,12 @@ PARAM_ORDER = (
 )
 
 
+DEFAULT_REFERENCE = "/root/reference"   # where the build machine keeps the read-only checkout
+
+
 def find_reference():
     """Path of the reference's kernels.py, or None."""
-    roots = [os.environ.get("GTM_REFERENCE"), os.path.join(HERE, "..", "baseline", "_ref"), "/root/reference"]
+    roots = [os.environ.get("GTM_REFERENCE"), os.path.join(HERE, "..", "baseline", "_ref"), DEFAULT_REFERENCE]
     for root in roots:
         if not root:
             continue

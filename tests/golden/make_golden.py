@@ -1,5 +1,5 @@
-"""Generates the golden vectors of this folder.  Needs the reference checkout (``/root/reference`` or
-``$GTM_REFERENCE``); run as ``python tests/golden/make_golden.py`` from the repository root.
+"""Generates the golden vectors of this folder.  Needs the reference checkout (``$GTM_REFERENCE``, or the
+default location known to oracle/build_ref.py); run as ``python tests/golden/make_golden.py`` from the repository root.
 
 Two kinds of vectors, both produced by the reference's own code:
  * ``graphs_*.npz``   arrays built by the reference's ``Graphs`` class (GraphTsetlinMachine/graphs.py, imported
@@ -26,7 +26,9 @@ from oracle.ref_tm import RefTM  # noqa: E402
 def reference_graphs_class():
     import importlib.util
 
-    ref_root = os.environ.get("GTM_REFERENCE", "/root/reference")
+    from oracle import build_ref
+
+    ref_root = os.environ.get("GTM_REFERENCE", build_ref.DEFAULT_REFERENCE)
     spec = importlib.util.spec_from_file_location("_ref_graphs", os.path.join(ref_root, "GraphTsetlinMachine", "graphs.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
