@@ -57,10 +57,12 @@ PROTOTYPES = {
     "gtm_get_draw_positions": [C.c_void_p, C.c_void_p],
     "gtm_set_recorded_draws": [C.c_void_p, C.c_void_p, C.c_uint64],
     "gtm_dataset_create": [C.c_void_p, C.POINTER(GraphsView), C.POINTER(C.c_void_p)],
+    "gtm_validate_graphs": [C.POINTER(GraphsView)],
     "gtm_dataset_destroy": [C.c_void_p],
     "gtm_score": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_score_device": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p],
     "gtm_score_static_scratch": [C.c_void_p, C.POINTER(GraphsView), C.c_int, C.c_int64, C.c_int64, C.c_void_p],
+    "gtm_check_skipped_graphs": [C.c_void_p, C.POINTER(C.c_int)],
     "gtm_shard_range": [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)],
     "gtm_shard_prepare": [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p],
     "gtm_shard_connect": [C.c_void_p, C.c_void_p, C.c_void_p],

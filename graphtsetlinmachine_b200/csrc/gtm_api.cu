@@ -111,12 +111,14 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     if (st == GTM_OK) st = dev_alloc(&m->class_sum_tap, (size_t)d.K);
     if (st == GTM_OK) st = dev_alloc(&m->barrier, 1);
     if (st == GTM_OK) st = dev_alloc(&m->error, 1);
+    if (st == GTM_OK) st = dev_alloc(&m->score_error, 1);
     if (st == GTM_OK) st = dev_alloc(&m->phase_cycles, 8);
     if (st != GTM_OK) { gtm_destroy(m); return st; }
     d.hv = hv;
     cudaMemset(hv, 0, (size_t)d.C * d.MB * sizeof(u32));
     cudaMemset(d.draw_pos, 0, (size_t)d.C * sizeof(u64));
     cudaMemset(d.weights, 0, (size_t)d.K * d.C * sizeof(int));
+    cudaMemset(m->score_error, 0, sizeof(int));
 
     // learning grid: all CTAs must be co-resident (cooperative launch); no more warps than clauses
     st = fit_grid_for_global_state(d, m->sm_count, m->fit_block, &m->fit_grid);
@@ -134,7 +136,7 @@ extern "C" int gtm_destroy(gtm_model *m)
     cudaSetDevice(m->cfg.device);
     cudaFree(m->dm.ta0); cudaFree(m->dm.tam);
     cudaFree(m->dm.weights); cudaFree((void *)m->dm.hv); cudaFree(m->dm.draw_pos); cudaFree(m->recorded);
-    cudaFree(m->exchange); cudaFree(m->error); cudaFree(m->clause_node); cudaFree(m->update);
+    cudaFree(m->exchange); cudaFree(m->error); cudaFree(m->score_error); cudaFree(m->clause_node); cudaFree(m->update);
     cudaFree(m->class_sum_tap); cudaFree(m->barrier); cudaFree(m->phase_cycles);
     stream_model_destroy(&m->sm);
     delete m;
@@ -304,6 +306,57 @@ static int scratch(gtm_dataset *ds, T **dev, size_t count)
     return GTM_OK;
 }
 
+// Host arrays must have the layout that graphs.py produces: node_index and edge_index are exclusive prefix sums of the
+// node counts and out-degrees (graphs.py:101-102,127-128), every graph has 1..max_number_of_graph_nodes nodes.  The
+// kernels size their scratch rows from max_number_of_graph_nodes and index the arrays with these values, so anything
+// else is refused here.  Checks graphs [g_lo, g_hi) and their nodes.
+static int validate_graphs(const gtm_graphs_view *v, int64_t g_lo, int64_t g_hi)
+{
+    const int64_t N = v->number_of_graphs;
+    const u32 max_nodes = (u32)v->max_number_of_graph_nodes;
+    if (g_lo == 0 && v->node_index[0] != 0) return fail(GTM_ERR_ARG, "node_index[0] must be 0");
+    u32 bad_count = 0, bad_index = 0;
+    for (int64_t gi = g_lo; gi < g_hi; ++gi) {
+        const u32 n = v->number_of_graph_nodes[gi];
+        const uint64_t end = (uint64_t)v->node_index[gi] + n;
+        const uint64_t want = gi + 1 < N ? (uint64_t)v->node_index[gi + 1] : (uint64_t)v->total_nodes;
+        bad_count |= (u32)(n - 1u >= max_nodes);
+        bad_index |= (u32)(end != want);
+    }
+    if (bad_count) return fail(GTM_ERR_ARG, "a graph has no nodes or more than max_number_of_graph_nodes = %d", v->max_number_of_graph_nodes);
+    if (bad_index) return fail(GTM_ERR_ARG, "node_index is not the running sum of number_of_graph_nodes (or exceeds total_nodes)");
+    const int64_t v_lo = v->node_index[g_lo], v_hi = g_hi < N ? (int64_t)v->node_index[g_hi] : v->total_nodes;
+    if (v_lo == 0 && v->edge_index[0] != 0) return fail(GTM_ERR_ARG, "edge_index[0] must be 0");
+    u32 bad_edges = 0;
+    for (int64_t vi = v_lo; vi < v_hi; ++vi) {
+        const uint64_t end = (uint64_t)v->edge_index[vi] + v->number_of_graph_node_edges[vi];
+        const uint64_t want = vi + 1 < v->total_nodes ? (uint64_t)v->edge_index[vi + 1] : (uint64_t)v->total_edges;
+        bad_edges |= (u32)(end != want);
+    }
+    if (bad_edges) return fail(GTM_ERR_ARG, "edge_index is not the running sum of number_of_graph_node_edges (or exceeds total_edges)");
+    return GTM_OK;
+}
+
+static int check_view(const gtm_graphs_view *v)
+{
+    if (!v) return fail(GTM_ERR_ARG, "null argument");
+    if (v->number_of_graphs < 1 || v->total_nodes < 1) return fail(GTM_ERR_ARG, "empty graph set");
+    if (!v->X || !v->node_type || !v->number_of_graph_node_edges || !v->edge_index || !v->node_index || !v->number_of_graph_nodes)
+        return fail(GTM_ERR_ARG, "graph arrays must not be null");
+    if (v->total_edges < 0 || (v->total_edges > 0 && !v->edge)) return fail(GTM_ERR_ARG, "edge array is null but total_edges > 0");
+    if (v->max_number_of_graph_nodes < 1) return fail(GTM_ERR_ARG, "max_number_of_graph_nodes must be positive");
+    if (v->total_nodes >= (int64_t)1 << 31 || v->total_edges >= (int64_t)1 << 31)
+        return fail(GTM_ERR_ARG, "graph sets beyond 2^31 nodes or edges are not supported");
+    if (v->number_of_graphs > v->total_nodes) return fail(GTM_ERR_ARG, "more graphs than nodes");
+    return GTM_OK;
+}
+
+extern "C" int gtm_validate_graphs(const gtm_graphs_view *v)
+{
+    GTM_TRY(check_view(v));
+    return validate_graphs(v, 0, v->number_of_graphs);
+}
+
 // copy_arrays == false: the per-node and per-graph arrays are only allocated; the caller copies them in pieces
 // (gtm_dataset_create_scored).
 static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds, bool copy_arrays = true)
@@ -335,6 +388,8 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
         GTM_CU(cudaStreamSynchronize(s));   // the vectors go out of scope
     }
     ds->dg.n_types = 1;
+    ds->dg.total_nodes = (u32)v->total_nodes; ds->dg.total_edges = (u32)v->total_edges;
+    ds->dg.max_nodes = ds->max_nodes; ds->dg.error = m->score_error;
 
     // learning scratch
     const size_t p_words = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW;
@@ -397,20 +452,16 @@ static int dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **
     GTM_TRY(bind(m));
     if (!v || !out) return fail(GTM_ERR_ARG, "null argument");
     *out = nullptr;
-    if (v->number_of_graphs < 1 || v->total_nodes < 1) return fail(GTM_ERR_ARG, "empty graph set");
-    if (!v->X || !v->node_type || !v->number_of_graph_node_edges || !v->edge_index || !v->node_index || !v->number_of_graph_nodes)
-        return fail(GTM_ERR_ARG, "graph arrays must not be null");
-    if (v->total_edges > 0 && !v->edge) return fail(GTM_ERR_ARG, "edge array is null but total_edges > 0");
-    if (v->max_number_of_graph_nodes < 1) return fail(GTM_ERR_ARG, "max_number_of_graph_nodes must be positive");
-    if (v->total_nodes >= (int64_t)1 << 31 || v->total_edges >= (int64_t)1 << 31)
-        return fail(GTM_ERR_ARG, "graph sets beyond 2^31 nodes or edges are not supported");
+    GTM_TRY(check_view(v));
     gtm_dataset *ds = new (std::nothrow) gtm_dataset();
     if (!ds) return fail(GTM_ERR_OOM, "host allocation failed");
     ds->model = m;
     ds->n_graphs = v->number_of_graphs; ds->total_nodes = v->total_nodes; ds->total_edges = v->total_edges;
     ds->max_nodes = v->max_number_of_graph_nodes;
     ds->NC = words_for(ds->max_nodes);
-    int st = dataset_build(m, v, ds, copy_arrays);
+    // the pipelined caller validates chunk by chunk, just before each chunk is copied
+    int st = copy_arrays ? validate_graphs(v, 0, v->number_of_graphs) : GTM_OK;
+    if (st == GTM_OK) st = dataset_build(m, v, ds, copy_arrays);
     if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
     *out = ds;
     return GTM_OK;
@@ -570,6 +621,7 @@ extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v,
         const int64_t chunk = std::max<int64_t>(1, (int64_t)ds->sd.grid * 2) * ds->sd.graphs_per_tile;
         for (int64_t g0 = 0; g0 < n; g0 += chunk) {
             const size_t cnt = (size_t)std::min<int64_t>(chunk, n - g0);
+            GTM_TRY(validate_graphs(v, g0, g0 + (int64_t)cnt));     // overlaps the copies of the chunks before
             // one node per graph: node ranges are graph ranges
             GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.X) + (size_t)g0 * d.L0, v->X + (size_t)g0 * d.L0, cnt * d.L0 * sizeof(u32), cudaMemcpyHostToDevice, in));
             GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.node_type) + g0, v->node_type + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
@@ -805,6 +857,17 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
         !v->number_of_graph_nodes || (v->total_edges > 0 && !v->edge))
         return fail(GTM_ERR_ARG, "device arrays must not be null");
     if (v->max_number_of_graph_nodes < 1) return fail(GTM_ERR_ARG, "max_number_of_graph_nodes must be positive");
+    if (v->total_nodes < 1 || v->total_nodes >= (int64_t)1 << 31 || v->total_edges < 0 || v->total_edges >= (int64_t)1 << 31)
+        return fail(GTM_ERR_ARG, "total_nodes must be in 1..2^31-1 and total_edges in 0..2^31-1");
+    // layer-0 rows of a multiple of four words are read with 128-bit loads; every array is read as 32-bit words
+    if ((m->dm.L0 & 3) == 0 && ((uintptr_t)v->X & 15) != 0)
+        return fail(GTM_ERR_ARG, "X must be 16-byte aligned when a literal row is a multiple of 16 bytes (it is %d bytes here)", m->dm.L0 * 4);
+    {
+        const void *arrays[] = {v->X, v->node_type, v->number_of_graph_node_edges, v->edge_index, v->edge, v->node_index,
+                                v->number_of_graph_nodes, sums_dev};
+        for (const void *p : arrays)
+            if (((uintptr_t)p & 3) != 0) return fail(GTM_ERR_ARG, "device arrays must be 4-byte aligned");
+    }
     const int dev = m->cfg.device;
     if (dev >= 64) return fail(GTM_ERR_ARG, "device ordinal %d beyond the 64 this entry point keeps an address for", dev);
 
@@ -836,6 +899,10 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     g.X = v->X; g.node_type = v->node_type; g.degree = v->number_of_graph_node_edges; g.edge_index = v->edge_index;
     g.edge = v->edge; g.node_index = v->node_index; g.n_nodes = v->number_of_graph_nodes;
     g.n_types = n_types;
+    // the arrays are in device memory and cannot be checked here: the kernel skips graphs that would leave them or the
+    // scratch slice and raises the word that gtm_check_skipped_graphs reads
+    g.total_nodes = (u32)v->total_nodes; g.total_edges = (u32)v->total_edges;
+    g.max_nodes = v->max_number_of_graph_nodes; g.error = m->score_error;
     EvalScratch sc;
     sc.cno = scratch_base;
     sc.P = scratch_base + cno_words;
@@ -847,5 +914,17 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     a.part_words = 0; a.t_stride = 0;
     score_graphs_kernel<true><<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);
     GTM_CU(cudaGetLastError());
+    return GTM_OK;
+}
+
+extern "C" int gtm_check_skipped_graphs(gtm_model *m, int *skipped_out)
+{
+    GTM_TRY(bind(m));
+    if (!skipped_out) return fail(GTM_ERR_ARG, "skipped_out is null");
+    GTM_CU(cudaStreamSynchronize(m->stream));
+    int flag = 0;
+    GTM_CU(cudaMemcpy(&flag, m->score_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) GTM_CU(cudaMemset(m->score_error, 0, sizeof(int)));
+    *skipped_out = flag != 0;
     return GTM_OK;
 }

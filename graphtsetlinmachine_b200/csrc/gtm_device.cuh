@@ -51,6 +51,12 @@ struct DevGraphs {
     const u32 *X, *node_type, *degree, *edge_index, *edge, *node_index, *n_nodes;
     const u32 *graph_edge0, *graph_edges;   // per graph: first edge row and number of edge rows (derived at upload)
     int n_types;
+    // Bounds for the kernels' guards.  Host arrays are validated when a graph set is created; arrays that arrive as
+    // device pointers cannot be, so a graph whose node range or node count is out of bounds is skipped (its class sums
+    // are zero) and *error is raised, and edge rows past total_edges are ignored.
+    u32 total_nodes, total_edges;
+    int max_nodes;
+    int *error;                             // may be null
 };
 
 // One graph as the evaluation sees it: either pointers into the uploaded arrays or into a shared-memory copy.
@@ -61,20 +67,28 @@ struct GraphView {
     const u32 *eidx;     // [n] CSR row starts (absolute edge rows)
     const u32 *edge;     // edge rows (dst, type); row r of the graph set is at edge + 2*(r - e_off)
     u32 e_off;
+    u32 e_cnt;           // rows addressable through `edge`: a row r is read only when r - e_off < e_cnt
     int n;
 };
 
 __device__ __forceinline__ GraphView global_graph(const DevGraphs &g, int64_t e, int L0)
 {
     GraphView v;
-    const u32 base = g.node_index[e];
-    v.n = (int)g.n_nodes[e];
+    u32 base = g.node_index[e];
+    u32 n = g.n_nodes[e];
+    if (n > (u32)g.max_nodes || base > g.total_nodes || n > g.total_nodes - base) {   // malformed: skip, never index past the arrays or the scratch
+        if (g.error) *g.error = 1;
+        n = 0;
+        base = 0;
+    }
+    v.n = (int)n;
     v.X = g.X + (size_t)base * L0;
     v.type = g.node_type + base;
     v.degree = g.degree + base;
     v.eidx = g.edge_index + base;
     v.edge = g.edge;
     v.e_off = 0;
+    v.e_cnt = g.total_edges;
     return v;
 }
 
@@ -253,8 +267,9 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
             u32 dst[kInFlight], ty[kInFlight];
 #pragma unroll
             for (int q = 0; q < kInFlight; ++q) {
-                dst[q] = k < deg[q] ? gv.edge[2 * (size_t)(e0[q] + k)] : ~0u;
-                ty[q] = k < deg[q] ? gv.edge[2 * (size_t)(e0[q] + k) + 1] : 0u;
+                const bool row_ok = k < deg[q] && e0[q] + k < gv.e_cnt;
+                dst[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k)] : ~0u;
+                ty[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k) + 1] : 0u;
             }
 #pragma unroll
             for (int q = 0; q < kInFlight; ++q) {
@@ -452,7 +467,7 @@ __device__ __forceinline__ u32 eval_node_words(const DevModel &m, const GraphVie
                     }
                 } else {
                     const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
-                    for (u32 k = 0; k < deg; ++k) {
+                    for (u32 k = 0; k < deg && e0 + k < gv.e_cnt; ++k) {
                         const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
                         if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
                         for (int b = 0; b < m.MB; ++b) {
@@ -598,7 +613,7 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
                 }
             } else {
                 const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
-                for (u32 k = 0; k < deg; ++k) {
+                for (u32 k = 0; k < deg && e0 + k < gv.e_cnt; ++k) {
                     const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
                     if (dst >= (u32)n) continue;
                     for (int b = 0; b < m.MB; ++b) {

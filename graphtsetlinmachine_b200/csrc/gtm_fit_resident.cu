@@ -169,11 +169,11 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         if (fits(sz)) {
             const u32 *st_x = s_stage + par * kStageWords;
             gv.X = st_x; gv.type = st_x + kStageRowWords; gv.degree = gv.type + kStageNodes; gv.eidx = gv.degree + kStageNodes;
-            gv.edge = gv.eidx + kStageNodes; gv.e_off = (u32)sz[2];
+            gv.edge = gv.eidx + kStageNodes; gv.e_off = (u32)sz[2]; gv.e_cnt = (u32)sz[3];
         } else {
             const int base = sz[1];
             gv.X = g.X + (size_t)base * m.L0; gv.type = g.node_type + base; gv.degree = g.degree + base;
-            gv.eidx = g.edge_index + base; gv.edge = g.edge; gv.e_off = 0;
+            gv.eidx = g.edge_index + base; gv.edge = g.edge; gv.e_off = 0; gv.e_cnt = g.total_edges;
         }
         u32 *P = par ? P_odd : P_even;
         const int *y = s_y + par * KP;

@@ -18,6 +18,7 @@ struct gtm_model {
     u32 *recorded = nullptr;
     // learning-kernel buffers
     int fit_grid = 0, fit_block = 512;
+    int *score_error = nullptr;               // raised by scoring kernels that skipped a malformed graph (device-pointer inputs)
     int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
     unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
     int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory

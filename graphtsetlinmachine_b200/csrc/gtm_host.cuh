@@ -50,26 +50,42 @@ inline int dev_alloc(T **p, size_t count)
 }
 
 
-// Stream-ordered allocation from the device's default memory pool, whose release threshold is raised once per
-// device so that freed blocks stay cached: graph sets and result buffers that come and go with every scoring call
-// then cost no cudaMalloc / cudaFree (both of which synchronise the device).
+// Stream-ordered allocation from a memory pool that belongs to this library (one per device, created on first use):
+// freed blocks stay cached in it, so graph sets and result buffers that come and go with every scoring call cost no
+// cudaMalloc / cudaFree (both of which synchronise the device).  The device's default pool, which other allocators of
+// the process share, is left as it is.
+inline cudaMemPool_t *gtm_pools()
+{
+    static cudaMemPool_t pools[64];
+    return pools;
+}
+
 inline int pool_prepare(int device)
 {
-    static bool done[64];
-    if (device < 0 || device >= 64 || done[device]) return GTM_OK;
+    if (device < 0 || device >= 64) return fail(GTM_ERR_ARG, "device ordinal %d beyond the 64 this library keeps a memory pool for", device);
+    if (gtm_pools()[device]) return GTM_OK;
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device;
     cudaMemPool_t pool;
-    GTM_CU(cudaDeviceGetDefaultMemPool(&pool, device));
+    GTM_CU(cudaMemPoolCreate(&pool, &props));
     unsigned long long keep = ~0ull;
     GTM_CU(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-    done[device] = true;
+    gtm_pools()[device] = pool;
     return GTM_OK;
 }
 
+// Allocates on the CURRENT device (every entry point binds the model's device first).
 template <class T>
 inline int pool_alloc(T **p, size_t count, cudaStream_t s)
 {
     *p = nullptr;
     if (count == 0) count = 1;
-    GTM_CU(cudaMallocAsync((void **)p, count * sizeof(T), s));
+    int device = 0;
+    GTM_CU(cudaGetDevice(&device));
+    GTM_TRY(pool_prepare(device));
+    GTM_CU(cudaMallocFromPoolAsync((void **)p, count * sizeof(T), gtm_pools()[device], s));
     return GTM_OK;
 }

@@ -119,8 +119,13 @@ int gtm_get_draw_positions(gtm_model *model, uint64_t *positions_out);
 int gtm_set_recorded_draws(gtm_model *model, const uint32_t *draws, uint64_t draws_per_clause);
 
 /* Graph sets on the device.  Replaces the uploads and scratch allocations of tm.py:528-555 (_init_fit) and
- * tm.py:759-784 (_score_init).  Signature caching stays with the caller. */
+ * tm.py:759-784 (_score_init).  Signature caching stays with the caller.  The arrays must have the layout graphs.py
+ * produces -- node_index / edge_index are the running sums of number_of_graph_nodes / number_of_graph_node_edges
+ * (graphs.py:101-102,127-128) and every graph has 1..max_number_of_graph_nodes nodes -- otherwise GTM_ERR_ARG. */
 int gtm_dataset_create(gtm_model *model, const gtm_graphs_view *graphs, gtm_dataset **dataset_out);
+/* The same checks on HOST arrays without a model or a device (GTM_OK or GTM_ERR_ARG with the reason in
+ * gtm_last_error).  No counterpart in the reference, whose kernels index whatever they are given. */
+int gtm_validate_graphs(const gtm_graphs_view *graphs);
 int gtm_dataset_destroy(gtm_dataset *dataset);
 
 /* Replaces the per-graph loop of tm.py:786-812 (_score): raw, unclamped class sums int32[count][CLASSES] for
@@ -154,6 +159,13 @@ int gtm_score_device(gtm_model *model, gtm_dataset *dataset, int number_of_node_
  *    the process exits.
  * It runs the general scoring kernel (any depth), queues the work on the model's stream and returns without
  * synchronising, like gtm_score_device, and gives the same class sums.
+ * Requirements on the caller's buffers: every array 4-byte aligned; X 16-byte aligned when a literal row
+ * (4*ceil(literals/32) bytes) is a multiple of 16 bytes, because such rows are read with 128-bit loads -- a buffer
+ * carved out of a pool at an odd offset is refused with GTM_ERR_ARG before anything is launched.  The arrays are in
+ * device memory, so their CONTENTS cannot be checked by the host: the kernel itself skips a graph whose node count
+ * exceeds max_number_of_graph_nodes or whose node range leaves total_nodes (its class sums are zero), ignores edge
+ * rows beyond total_edges and edges to nodes outside the graph, and records the fact; gtm_check_skipped_graphs
+ * reports it.
  * Limits: the scratch of ONE thread block, 4*(2*CLAUSES*ceil(max_nodes/32) + max(1,depth-1)*max_nodes*
  * ceil(MESSAGE_SIZE/32) + CLAUSES) bytes, must fit in GTM_STATIC_SCRATCH_BYTES, otherwise GTM_ERR_ARG (nothing is
  * launched); fewer thread blocks run concurrently the larger that figure is.  Device ordinals 0..63.
@@ -164,6 +176,11 @@ int gtm_score_device(gtm_model *model, gtm_dataset *dataset, int number_of_node_
 #define GTM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
 int gtm_score_static_scratch(gtm_model *model, const gtm_graphs_view *device_graphs, int number_of_node_types,
                              int64_t first, int64_t count, int32_t *class_sums_device);
+
+/* Waits for the model's stream and tells whether a scoring kernel launched since the last call skipped a malformed
+ * graph (see gtm_score_static_scratch; *skipped_out = 0 or 1, then cleared).  NO COUNTERPART IN THE REFERENCE, which
+ * checks nothing and indexes out of bounds on such input (tm.py:765 vs kernels.py:35). */
+int gtm_check_skipped_graphs(gtm_model *model, int *skipped_out);
 
 /* Replaces the learning loop of tm.py:668-747 (_fit): `epochs` passes over graphs [first, first+count) in
  * order; encoded_Y is int32[number_of_graphs][CLASSES] with +-T targets (tm.py:949-951), indexed by the
