@@ -10,7 +10,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgtm_b200.so")
-SOURCES = [os.path.join(HERE, "csrc", f) for f in ("gtm_api.cu", "gtm_fit_global.cu", "gtm_fit_resident.cu", "gtm_stream.cu")]
+SOURCES = [os.path.join(HERE, "csrc", f) for f in ("gtm_api.cu", "gtm_fit_global.cu", "gtm_fit_resident.cu", "gtm_stream.cu", "gtm_tile.cu")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 

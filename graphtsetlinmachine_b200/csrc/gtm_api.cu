@@ -112,6 +112,7 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     if (st == GTM_OK) st = dev_alloc(&m->barrier, 1);
     if (st == GTM_OK) st = dev_alloc(&m->error, 1);
     if (st == GTM_OK) st = dev_alloc(&m->score_error, 1);
+    if (st == GTM_OK && cudaMallocHost((void **)&m->flag_host, sizeof(int)) != cudaSuccess) st = fail(GTM_ERR_OOM, "page-locked host allocation failed");
     if (st == GTM_OK) st = dev_alloc(&m->phase_cycles, 8);
     if (st != GTM_OK) { gtm_destroy(m); return st; }
     d.hv = hv;
@@ -125,6 +126,7 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     if (st != GTM_OK) { gtm_destroy(m); return st; }
     st = dev_alloc(&m->exchange, 2 * (size_t)(2 * m->sm_count) * d.K);
     if (st == GTM_OK) st = stream_model_create(&m->sm, d);
+    if (st == GTM_OK) st = tile_model_create(&m->tm, d);
     if (st != GTM_OK) { gtm_destroy(m); return fail(st, "device allocation failed"); }
     *out = m;
     return GTM_OK;
@@ -139,6 +141,8 @@ extern "C" int gtm_destroy(gtm_model *m)
     cudaFree(m->exchange); cudaFree(m->error); cudaFree(m->score_error); cudaFree(m->clause_node); cudaFree(m->update);
     cudaFree(m->class_sum_tap); cudaFree(m->barrier); cudaFree(m->phase_cycles);
     stream_model_destroy(&m->sm);
+    tile_model_destroy(&m->tm);
+    if (m->flag_host) cudaFreeHost(m->flag_host);
     delete m;
     return GTM_OK;
 }
@@ -155,7 +159,7 @@ extern "C" int gtm_set_option(gtm_model *m, const char *name, int value)
     GTM_TRY(bind(m));
     if (!name) return fail(GTM_ERR_ARG, "option name is null");
     if (!strcmp(name, "fit_kernel") && value >= 0 && value <= 2) { m->opt_fit_kernel = value; return GTM_OK; }
-    if (!strcmp(name, "score_kernel") && value >= 0 && value <= 2) { m->opt_score_kernel = value; return GTM_OK; }
+    if (!strcmp(name, "score_kernel") && value >= 0 && value <= 3) { m->opt_score_kernel = value; return GTM_OK; }
     if (!strcmp(name, "fit_timers") && value >= 0 && value <= 1) { m->opt_fit_timers = value; return GTM_OK; }
     return fail(GTM_ERR_ARG, "unknown option '%s' or value %d out of range", name, value);
 }
@@ -173,7 +177,7 @@ extern "C" int gtm_init_state(gtm_model *m, int reset_message_layers)
     GTM_CU(cudaGetLastError());
     GTM_CU(cudaStreamSynchronize(m->stream));
     m->has_state = true;
-    m->lists_dirty = true;
+    m->lists_dirty = true; ++m->state_version;
     return GTM_OK;
 }
 
@@ -201,7 +205,7 @@ extern "C" int gtm_set_ta_state(gtm_model *m, int layer, const uint32_t *ta)
     cudaFree(tmp);
     GTM_CU(e);
     m->has_state = true;
-    m->lists_dirty = true;
+    m->lists_dirty = true; ++m->state_version;
     return GTM_OK;
 }
 
@@ -229,7 +233,7 @@ extern "C" int gtm_set_weights(gtm_model *m, const int32_t *w)
     if (!w) return fail(GTM_ERR_ARG, "clause_weights is null");
     GTM_CU(cudaMemcpyAsync(m->dm.weights, w, (size_t)m->dm.K * m->dm.C * sizeof(int), cudaMemcpyHostToDevice, m->stream));
     GTM_CU(cudaStreamSynchronize(m->stream));
-    m->lists_dirty = true;
+    m->lists_dirty = true; ++m->state_version;
     return GTM_OK;
 }
 
@@ -248,7 +252,7 @@ extern "C" int gtm_set_hypervectors(gtm_model *m, const uint32_t *hv)
     if (!hv) return fail(GTM_ERR_ARG, "hypervectors is null");
     GTM_CU(cudaMemcpyAsync((void *)m->dm.hv, hv, (size_t)m->dm.C * m->dm.MB * sizeof(u32), cudaMemcpyHostToDevice, m->stream));
     GTM_CU(cudaStreamSynchronize(m->stream));
-    m->lists_dirty = true;
+    m->lists_dirty = true; ++m->state_version;
     return GTM_OK;
 }
 
@@ -287,11 +291,12 @@ extern "C" int gtm_set_recorded_draws(gtm_model *m, const uint32_t *draws, uint6
 }
 
 // --------------------------------------------------------------------------------------------- datasets
+// `slack`: elements allocated beyond `count` (never copied, never interpreted)
 template <class T>
-static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s, bool copy = true)
+static int upload(gtm_dataset *ds, const T **dev, const T *host, size_t count, cudaStream_t s, bool copy = true, size_t slack = 0)
 {
     T *p;
-    GTM_TRY(pool_alloc(&p, count, s));
+    GTM_TRY(pool_alloc(&p, count + slack, s));
     ds->owned.push_back(p);
     if (copy && count && host) GTM_CU(cudaMemcpyAsync(p, host, count * sizeof(T), cudaMemcpyHostToDevice, s));
     *dev = p;
@@ -363,7 +368,8 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
 {
     const DevModel &d = m->dm;
     cudaStream_t s = m->stream;
-    GTM_TRY(upload(ds, &ds->dg.X, v->X, (size_t)v->total_nodes * d.L0, s, copy_arrays));
+    // the tile kernel fetches literal rows with bulk copies widened to 16-byte boundaries: a little slack at the end
+    GTM_TRY(upload(ds, &ds->dg.X, v->X, (size_t)v->total_nodes * d.L0, s, copy_arrays, 4));
     GTM_TRY(upload(ds, &ds->dg.node_type, v->node_type, (size_t)v->total_nodes, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.degree, v->number_of_graph_node_edges, (size_t)v->total_nodes, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.edge_index, v->edge_index, (size_t)v->total_nodes, s, copy_arrays));
@@ -443,6 +449,8 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     ds->score_sc.cno = nullptr;   // allocated on first use of the general kernel (ensure_score_scratch)
 
     GTM_TRY(stream_data_create(&ds->sd, m->sm, d, ds->dg, v, m->sm_count, s));
+    // tiles of whole graphs for the tile kernel: deeper models, or sets the node-stream kernel does not cover
+    if (d.D > 1 || !ds->sd.supported || m->opt_score_kernel == 3) GTM_TRY(tile_data_create(&ds->td, m->tm, d, v, m->sm_count, s));
     GTM_CU(cudaStreamSynchronize(s));
     return GTM_OK;
 }
@@ -480,6 +488,7 @@ extern "C" int gtm_dataset_destroy(gtm_dataset *ds)
     for (void *p : ds->owned) cudaFreeAsync(p, ds->model->stream);
     cudaFree(ds->Y);
     stream_data_destroy(&ds->sd);
+    tile_data_destroy(&ds->td);
     fit_comm_release(ds);
     delete ds;
     return GTM_OK;
@@ -495,6 +504,15 @@ static int check_range(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first
         return fail(GTM_ERR_ARG, "graph range [%lld, %lld) outside the set of %lld graphs", (long long)first,
                     (long long)(first + count), (long long)ds->n_graphs);
     return GTM_OK;
+}
+
+// What the word that scoring kernels raise means to the caller (cleared once it was seen).
+static int score_flag_status(gtm_model *m, int flag)
+{
+    if (flag == 0) return GTM_OK;
+    cudaMemsetAsync(m->score_error, 0, sizeof(int), m->stream);
+    if (flag == 2) return fail(GTM_ERR_TIMEOUT, "a scoring kernel gave up waiting for a bulk copy into shared memory; the class sums are not valid");
+    return fail(GTM_ERR_ARG, "a scoring kernel skipped a malformed graph (node count or node range out of bounds)");
 }
 
 static int ensure_score_scratch(gtm_dataset *ds)
@@ -536,6 +554,14 @@ static int refresh_lists(gtm_model *m)
     return GTM_OK;
 }
 
+static int refresh_tile_lists(gtm_model *m)
+{
+    if (m->tile_lists_version == m->state_version) return GTM_OK;
+    GTM_TRY(tile_model_refresh(&m->tm, m->dm, m->stream));
+    m->tile_lists_version = m->state_version;
+    return GTM_OK;
+}
+
 extern "C" int gtm_score_device(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
                                 int32_t *sums_dev)
 {
@@ -545,9 +571,15 @@ extern "C" int gtm_score_device(gtm_model *m, gtm_dataset *ds, int n_types, int6
     if (!sums_dev) return fail(GTM_ERR_ARG, "class_sums_device is null");
     if (m->opt_score_kernel == 2 && !stream_supported(ds->sd, n_types))
         return fail(GTM_ERR_ARG, "the node-stream scoring kernel does not cover this model / graph set");
-    if (m->opt_score_kernel != 1 && stream_supported(ds->sd, n_types)) {
+    if (m->opt_score_kernel == 3 && !tile_supported(ds->td, n_types))
+        return fail(GTM_ERR_ARG, "the tile scoring kernel does not cover this model / graph set");
+    if ((m->opt_score_kernel == 0 || m->opt_score_kernel == 2) && stream_supported(ds->sd, n_types)) {
         GTM_TRY(refresh_lists(m));
         return stream_score(m->sm, ds->sd, m->dm, ds->dg, n_types, first, count, sums_dev, m->stream);
+    }
+    if ((m->opt_score_kernel == 0 || m->opt_score_kernel == 3) && tile_supported(ds->td, n_types)) {
+        GTM_TRY(refresh_tile_lists(m));
+        return tile_score(m->tm, ds->td, m->dm, ds->dg, n_types, first, count, sums_dev, m->score_error, m->stream);
     }
     return launch_score_general(m, ds, n_types, first, count, sums_dev, nullptr);
 }
@@ -564,10 +596,11 @@ extern "C" int gtm_score(gtm_model *m, gtm_dataset *ds, int n_types, int64_t fir
     cudaError_t e = cudaSuccess;
     if (st == GTM_OK) e = cudaMemcpyAsync(out, dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
     cudaFreeAsync(dev, m->stream);
+    if (st == GTM_OK && e == cudaSuccess) e = cudaMemcpyAsync(m->flag_host, m->score_error, sizeof(int), cudaMemcpyDeviceToHost, m->stream);
     if (st == GTM_OK && e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     if (st != GTM_OK) return st;
     GTM_CU(e);
-    return GTM_OK;
+    return score_flag_status(m, *m->flag_host);
 }
 
 // Upload and scoring of a whole host graph set in one call.  Sets of single-node graphs that the node-stream kernel
@@ -695,7 +728,7 @@ extern "C" int gtm_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int32_t
     }
     GTM_CU(cudaMemcpyAsync(ds->Y + (size_t)first * m->dm.K, Y + (size_t)first * m->dm.K,
                            (size_t)count * m->dm.K * sizeof(int), cudaMemcpyHostToDevice, m->stream));
-    m->lists_dirty = true;
+    m->lists_dirty = true; ++m->state_version;
     return launch_fit(m, ds, n_types, ds->Y, first, count, epochs, 0);
 }
 
@@ -925,6 +958,7 @@ extern "C" int gtm_check_skipped_graphs(gtm_model *m, int *skipped_out)
     int flag = 0;
     GTM_CU(cudaMemcpy(&flag, m->score_error, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) GTM_CU(cudaMemset(m->score_error, 0, sizeof(int)));
-    *skipped_out = flag != 0;
+    *skipped_out = flag == 1;
+    if (flag == 2) return score_flag_status(m, flag);
     return GTM_OK;
 }

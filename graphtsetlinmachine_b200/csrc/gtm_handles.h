@@ -5,6 +5,7 @@
 #include "gtm_device.cuh"
 #include "gtm_host.cuh"
 #include "gtm_stream.h"
+#include "gtm_tile.h"
 
 using namespace gtm;
 
@@ -18,17 +19,21 @@ struct gtm_model {
     u32 *recorded = nullptr;
     // learning-kernel buffers
     int fit_grid = 0, fit_block = 512;
+    int *flag_host = nullptr;                 // page-locked landing place of score_error
     int *score_error = nullptr;               // raised by scoring kernels that skipped a malformed graph (device-pointer inputs)
     int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
     unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
     int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
     int opt_fit_timers = 0;                   // 1: the learning kernels time their phases (gtm_debug_fit_phase_cycles)
-    int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel
+    int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel, 3 tile kernel
     unsigned *barrier = nullptr;
     unsigned long long *phase_cycles = nullptr;
     // node-stream scoring: derived include lists (rebuilt when the automata changed)
     StreamModel sm;
     bool lists_dirty = true;
+    // tile scoring: included-literal lists of every layer, rebuilt when the state version moved on
+    TileModel tm;
+    unsigned long long state_version = 1, tile_lists_version = 0;
 };
 
 // Buffers through which the learning kernels of several GPUs talk to each other when clauses are sharded over ranks
@@ -69,6 +74,8 @@ struct gtm_dataset {
     size_t Y_capacity = 0;
     // node-stream scoring
     StreamData sd;
+    // tile scoring
+    TileData td;
     // clause-sharded learning
     FitComm comm;
 };

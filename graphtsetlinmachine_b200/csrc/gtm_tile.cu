@@ -1,0 +1,750 @@
+// Tile scoring: batched inference for any depth on graph sets whose graphs have at most 128 nodes.
+//
+// The reference evaluates one graph at a time with five kernels per message layer (tm.py:563-662 driving
+// kernels.py:407-615).  Here a persistent CTA takes a TILE of consecutive whole graphs (32*TNC node slots, graphs
+// never straddle a 128-slot "quad") and keeps everything of the tile in shared memory for all layers:
+//
+//   1. the tile's literal rows - one contiguous piece of X - arrive through a bulk asynchronous copy
+//      (cp.async.bulk, completion on an mbarrier) and are transposed into XT[literal][node word]
+//      (bit i of word j = that literal on node slot 32j+i);
+//   2. layer 0: a thread evaluates one clause on one quad, r = type/valid mask AND the rows of the clause's INCLUDED
+//      literals (one 128-bit shared load per literal and 128 nodes; included-literal lists are rebuilt from the
+//      include planes whenever the automata changed), leaving as soon as r is empty; an empty clause is true
+//      (kernels.py:443-460);
+//   3. clauses that are still true somewhere go to a per-quad survivor list (clause, node bits) and mark their
+//      hypervector bits on the SOURCE nodes (node-major rows P[slot]); later layers only visit survivors, which is
+//      what "layer d is ANDed with layer d-1" (kernels.py:525-527) comes to;
+//   4. one pass over the tile's edges ORs the source rows, rotated by the edge type ((hv + type) mod MS,
+//      kernels.py:581), into the destination rows, and the result is transposed into PT[message bit][node word], the
+//      literal rows of the next layer (a negated message literal ANDs the complement of its row);
+//   5. after the last layer, per graph and warp, the weights of the clauses that fired are summed over the warp with
+//      redux.sync and added to the graph's class sums in shared memory (kernels.py:279-317, unclamped).
+//
+// The two big buffers swap roles from layer to layer (literal rows <-> message rows), so the footprint is one
+// transposed tile plus one node-major message tile.  Global scratch: the survivor lists (L2 traffic proportional
+// to the clauses that are still true).
+#include "../../include/gtm_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "gtm_tile.h"
+
+namespace gtm {
+
+constexpr int kTileThreads = 512;
+constexpr int kTileMaxK = 16;
+constexpr int kTileMaxTypes = 8;
+constexpr int kTileMaxGraphs = 512;   // graphs per tile: their vote accumulators and node masks live in shared memory
+constexpr int kQuadNodes = 128;
+constexpr unsigned long long kTileWaitNs = 500ull * 1000ull * 1000ull;   // bound of one wait for a bulk copy: 0.5 s
+
+// ------------------------------------------------------------------------------------------- list building
+__device__ __forceinline__ const u32 *include_plane(const DevModel &m, int layer, int c)
+{
+    return layer == 0 ? m.ta0 + ((size_t)c * m.SB + (m.SB - 1)) * m.L0
+                      : m.tam + (((size_t)(layer - 1) * m.C + c) * m.SB + (m.SB - 1)) * m.M;
+}
+
+// cnt[2c] / cnt[2c+1]: literals of clause c that are tested as they are / complemented, padded to multiples of 4.
+// Layer 0 has both polarities of a feature as literals of its own (graphs.py:150-159), so nothing is complemented;
+// a message layer's literal l >= MS is the complement of message bit l - MS (kernels.py:544-545).
+__global__ void tile_count_kernel(DevModel m, int layer, int *cnt)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= m.C) return;
+    const int W = layer == 0 ? m.L0 : m.M;
+    const u32 last = layer == 0 ? m.lit_mask : m.msg_mask;
+    const u32 *inc = include_plane(m, layer, c);
+    int plain = 0, negated = 0;
+    for (int w = 0; w < W; ++w) {
+        const u32 bits = inc[w] & (w == W - 1 ? last : kFull);
+        const int lo = 32 * w;
+        if (layer == 0 || lo + 32 <= m.MS) plain += __popc(bits);
+        else if (lo >= m.MS) negated += __popc(bits);
+        else {
+            const int split = m.MS - lo;
+            plain += __popc(bits & ((1u << split) - 1u));
+            negated += __popc(bits >> split);
+        }
+    }
+    cnt[2 * c] = (plain + 3) & ~3;
+    cnt[2 * c + 1] = (negated + 3) & ~3;
+}
+
+// Exclusive scan of cnt[0..n) into off[0..n], one block.
+__global__ void tile_scan_kernel(const int *cnt, int *off, int n, int *total_out)
+{
+    __shared__ int s_part[1024];
+    const int per = (n + blockDim.x - 1) / blockDim.x;
+    const int lo = min(n, (int)threadIdx.x * per), hi = min(n, lo + per);
+    int sum = 0;
+    for (int i = lo; i < hi; ++i) sum += cnt[i];
+    s_part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int t = 0; t < (int)blockDim.x; ++t) { const int v = s_part[t]; s_part[t] = run; run += v; }
+        off[n] = run;
+        *total_out = run;
+    }
+    __syncthreads();
+    int run = s_part[threadIdx.x];
+    for (int i = lo; i < hi; ++i) { off[i] = run; run += cnt[i]; }
+}
+
+// Row of literal bit p in the transposed buffer whose source rows have W words: bit b of word w lives in row b*W + w
+// (so that the threads that transpose adjacent words write adjacent rows); rows 32*W and 32*W+1 are all ones / zeros.
+__device__ __forceinline__ unsigned short tile_row(int p, int W) { return (unsigned short)((p & 31) * W + (p >> 5)); }
+
+__global__ void tile_fill_kernel(DevModel m, int layer, const int *off, unsigned short *list, int *Wt, int KROW, u32 *hvm)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= m.C) return;
+    const int W = layer == 0 ? m.L0 : m.M;
+    const int WS = layer == 0 ? m.L0 : m.MW;           // words of a source row (literal row / positive message bits)
+    const u32 last = layer == 0 ? m.lit_mask : m.msg_mask;
+    const u32 *inc = include_plane(m, layer, c);
+    int at_plain = off[2 * c], at_neg = off[2 * c + 1];
+    for (int w = 0; w < W; ++w) {
+        u32 bits = inc[w] & (w == W - 1 ? last : kFull);
+        while (bits) {
+            const int l = 32 * w + __ffs(bits) - 1;
+            bits &= bits - 1;
+            if (layer == 0 || l < m.MS) list[at_plain++] = tile_row(l, WS);
+            else list[at_neg++] = tile_row(l - m.MS, WS);
+        }
+    }
+    while (at_plain < off[2 * c + 1]) list[at_plain++] = (unsigned short)(32 * WS);        // all ones: no effect on an AND
+    while (at_neg < off[2 * c + 2]) list[at_neg++] = (unsigned short)(32 * WS + 1);        // all zeros: no effect when complemented
+    if (layer == 0) {
+        for (int k = 0; k < KROW; ++k) Wt[(size_t)c * KROW + k] = k < m.K ? m.weights[(size_t)k * m.C + c] : 0;
+        for (int b = 0; b < m.MB; ++b) hvm[(size_t)c * m.MB + b] = m.hv[(size_t)c * m.MB + b] % (u32)m.MS;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------- scoring
+struct TileArgs {
+    const int *tile_graph;              // first graph of every tile, or NULL: every tile holds graphs_per_tile graphs
+    const unsigned short *gpos;         // first node slot of every graph in its tile, or NULL (uniform sets)
+    int uniform_n, graphs_per_tile;
+    int tile_lo, tile_hi;               // tiles [tile_lo, tile_hi)
+    int64_t first, count;               // graphs written: [first, first+count)
+    int64_t n_graphs;
+    int *class_sums;                    // [count][K]
+    unsigned *tile_counter;             // dynamic tile scheduler (zeroed before launch)
+    int TNC, PS, words_a, words_b, stage_rows, gmax;
+    int rot_step;                       // message transposition: block column j is read rotated by (rot_step * j) & 31
+    const TileLayer *layers;            // [D]
+    const int *Wt;
+    int KROW;
+    const u32 *hvm;
+    int *surv_c;                        // [grid][2][Q][C]
+    uint4 *surv_r;
+    int *error;                         // raised (2) when the wait for a bulk copy gave up
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint4 tile_lds128(unsigned addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// ---- bulk asynchronous copy global -> shared with completion on an mbarrier (plain form: this CTA's own shared
+// memory, this GPU's own global memory, no multicast) ----
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void bulk_copy_to_shared(unsigned dst, const void *src, unsigned bytes, unsigned bar)
+{
+    // earlier generic-proxy accesses to the destination (ordered before this thread by a CTA barrier) precede the copy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Bounded wait for phase `parity` of the barrier: polls without blocking and gives up after kTileWaitNs of wall
+// time (a bulk copy of a few kilobytes takes microseconds); false when it gave up.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity)
+{
+    unsigned long long t0 = 0;
+    for (unsigned spins = 0;; ++spins) {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spins & 63u) == 63u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kTileWaitNs) return false;
+        }
+    }
+}
+
+// Node bits of a clause on one quad after ANDing the rows of its included literals (plain, then complemented).
+// tq: shared address of the quad's first word in row 0; a row is `1 << rowshift` bytes.
+__device__ __forceinline__ uint4 tile_eval(uint4 r, const TileLayer &L, int c, unsigned tq, int rowshift)
+{
+    const int o0 = L.off[2 * c] >> 2, o1 = L.off[2 * c + 1] >> 2, o2 = L.off[2 * c + 2] >> 2;
+    const uint2 *lp = reinterpret_cast<const uint2 *>(L.list);       // four 16-bit row numbers per load
+    for (int q = o0; q < o1; ++q) {
+        if ((r.x | r.y | r.z | r.w) == 0) return r;
+        const uint2 four = __ldg(lp + q);
+        const uint4 x0 = tile_lds128(tq + ((four.x & 0xffffu) << rowshift));
+        const uint4 x1 = tile_lds128(tq + ((four.x >> 16) << rowshift));
+        const uint4 x2 = tile_lds128(tq + ((four.y & 0xffffu) << rowshift));
+        const uint4 x3 = tile_lds128(tq + ((four.y >> 16) << rowshift));
+        r.x &= x0.x & x1.x; r.y &= x0.y & x1.y; r.z &= x0.z & x1.z; r.w &= x0.w & x1.w;
+        r.x &= x2.x & x3.x; r.y &= x2.y & x3.y; r.z &= x2.z & x3.z; r.w &= x2.w & x3.w;
+    }
+    for (int q = o1; q < o2; ++q) {
+        if ((r.x | r.y | r.z | r.w) == 0) return r;
+        const uint2 four = __ldg(lp + q);
+        const uint4 x0 = tile_lds128(tq + ((four.x & 0xffffu) << rowshift));
+        const uint4 x1 = tile_lds128(tq + ((four.x >> 16) << rowshift));
+        const uint4 x2 = tile_lds128(tq + ((four.y & 0xffffu) << rowshift));
+        const uint4 x3 = tile_lds128(tq + ((four.y >> 16) << rowshift));
+        r.x &= ~(x0.x | x1.x); r.y &= ~(x0.y | x1.y); r.z &= ~(x0.z | x1.z); r.w &= ~(x0.w | x1.w);
+        r.x &= ~(x2.x | x3.x); r.y &= ~(x2.y | x3.y); r.z &= ~(x2.z | x3.z); r.w &= ~(x2.w | x3.w);
+    }
+    return r;
+}
+
+// Bits [lo, lo+n) of a 128-bit quad.
+__device__ __forceinline__ uint4 quad_mask(int lo, int n)
+{
+    u32 wd[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int a = min(32, max(0, lo - 32 * i)), b = min(32, max(0, lo + n - 32 * i));
+        const u32 below_b = b >= 32 ? kFull : (1u << b) - 1u, below_a = a >= 32 ? kFull : (1u << a) - 1u;
+        wd[i] = below_b & ~below_a;
+    }
+    return make_uint4(wd[0], wd[1], wd[2], wd[3]);
+}
+
+template <int KP>
+__global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m, DevGraphs g, TileArgs a)
+{
+    extern __shared__ __align__(16) u32 s_dyn[];
+    const int TNC = a.TNC, TN = TNC * 32, Q = TNC >> 2, PS = a.PS;
+    const int rowshift = 31 - __clz(TNC * 4);
+    u32 *bufA = s_dyn;                                              // literal rows / message rows, swapping roles
+    u32 *bufB = bufA + a.words_a;                                   // staging of X / message rows, swapping roles
+    u32 *TMV = bufB + a.words_b;                                    // [kTileMaxTypes][TNC] valid nodes of each type
+    u32 *tnode = TMV + kTileMaxTypes * TNC;                         // [TN] node of each slot, or ~0
+    u32 *pinfo = tnode + TN;                                        // [TN] first slot of the slot's graph | nodes << 16
+    uint4 *gmask = reinterpret_cast<uint4 *>(pinfo + TN);           // [gmax] node slots of a graph inside its quad
+    int *sums = reinterpret_cast<int *>(gmask + a.gmax);            // [gmax][KP]
+    int *gq_first = sums + a.gmax * KP;                             // [Q+1] first graph of every quad
+    int *cnt = gq_first + 12;                                       // [2][8] survivor counts per list and quad
+    int *misc = cnt + 16;                                           // tile number, node range of a staging round
+    unsigned long long *mbar_mem = reinterpret_cast<unsigned long long *>(misc + 4);
+    unsigned char *gquad = reinterpret_cast<unsigned char *>(mbar_mem + 1);   // [gmax]
+    unsigned char *pflag = gquad + ((a.gmax + 3) & ~3);             // [TN] slot's message row has bits
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kTileThreads / 32;
+    const unsigned bar = smem_u32(mbar_mem);
+    int *surv_c = a.surv_c + (size_t)blockIdx.x * 2 * Q * m.C;
+    uint4 *surv_r = a.surv_r + (size_t)blockIdx.x * 2 * Q * m.C;
+    const size_t x_words = (size_t)g.total_nodes * m.L0;
+
+    if (tid == 0) mbar_init(bar, 1);
+    __syncthreads();
+    unsigned parity = 0;
+
+    while (true) {
+        if (tid == 0) misc[0] = a.tile_lo + (int)atomicAdd(a.tile_counter, 1u);
+        __syncthreads();
+        const int tile = misc[0];
+        if (tile >= a.tile_hi) break;
+        const int g0 = a.tile_graph ? a.tile_graph[tile] : (int)min((int64_t)tile * a.graphs_per_tile, a.n_graphs);
+        const int g1 = a.tile_graph ? a.tile_graph[tile + 1] : (int)min((int64_t)(tile + 1) * a.graphs_per_tile, a.n_graphs);
+        const int ng = g1 - g0;
+
+        // ---- slot tables: which node sits where, which slots belong to which graph ----
+        for (int i = tid; i < TN; i += kTileThreads) { tnode[i] = ~0u; pinfo[i] = 0u; }
+        for (int i = tid; i < ng * KP; i += kTileThreads) sums[i] = 0;
+        if (tid < 16) cnt[tid] = 0;
+        __syncthreads();
+        {
+            const int gpq = a.uniform_n > 0 ? kQuadNodes / a.uniform_n : 1;
+            for (int gl = tid; gl < ng; gl += kTileThreads) {
+                const int n = (int)g.n_nodes[g0 + gl];
+                const u32 nb = g.node_index[g0 + gl];
+                const int pos = a.uniform_n > 0 ? (gl / gpq) * kQuadNodes + (gl % gpq) * n : (int)a.gpos[g0 + gl];
+                for (int i = 0; i < n; ++i) { tnode[pos + i] = nb + i; pinfo[pos + i] = (u32)pos | ((u32)n << 16); }
+                gmask[gl] = quad_mask(pos & (kQuadNodes - 1), n);
+                gquad[gl] = (unsigned char)(pos >> 7);
+            }
+        }
+        __syncthreads();
+        for (int gl = tid; gl <= ng; gl += kTileThreads) {      // gq_first[q] = first graph whose quad is >= q
+            const int qhi = gl < ng ? (int)gquad[gl] : Q, qlo = gl > 0 ? (int)gquad[gl - 1] + 1 : 0;
+            for (int qq = qlo; qq <= qhi; ++qq) gq_first[qq] = gl;
+        }
+
+        // ---- literal rows of the tile: bulk copy into the staging buffer, transposed into bufA ----
+        const int groups_per_round = a.stage_rows >> 5;
+        for (int jr = 0; jr < TNC; jr += groups_per_round) {
+            const int jend = min(TNC, jr + groups_per_round);
+            if (tid == 0) { misc[1] = 0x7fffffff; misc[2] = -1; }
+            __syncthreads();
+            for (int p = 32 * jr + tid; p < 32 * jend; p += kTileThreads) {
+                const u32 nd = tnode[p];
+                if (nd != ~0u) { atomicMin(&misc[1], (int)nd); atomicMax(&misc[2], (int)nd); }
+            }
+            __syncthreads();
+            const int na = misc[1], nb = misc[2] + 1;
+            int lead = 0;
+            if (nb > na) {
+                // the rows of nodes [na, nb) are one contiguous piece of X; widened to 16-byte boundaries (the
+                // array is allocated with that much slack)
+                const size_t w0 = (size_t)na * m.L0, w1 = (size_t)nb * m.L0;
+                const size_t a0 = w0 & ~(size_t)3, a1 = min((w1 + 3) & ~(size_t)3, (x_words + 3) & ~(size_t)3);
+                lead = (int)(w0 - a0);
+                if (tid == 0) bulk_copy_to_shared(smem_u32(bufB), g.X + a0, (unsigned)((a1 - a0) * sizeof(u32)), bar);
+                if (!mbar_wait(bar, parity)) {
+                    if (a.error) atomicExch(a.error, 2);
+                    mbar_wait(bar, parity);           // the copy may still be in flight: give it one more bounded wait
+                }
+                parity ^= 1u;
+            }
+            const int nblk = (jend - jr) * m.L0;
+            for (int blk = tid; blk < nblk; blk += kTileThreads) {
+                const int jj = blk / m.L0, w = blk - jj * m.L0, j = jr + jj, rot = j & 31;
+                u32 rows[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const u32 nd = tnode[32 * j + ((i + rot) & 31)];
+                    rows[i] = nd != ~0u ? bufB[lead + (size_t)(nd - (u32)na) * m.L0 + w] : 0u;
+                }
+                transpose32(rows);
+#pragma unroll
+                for (int b = 0; b < 32; ++b) bufA[(size_t)(b * m.L0 + w) * TNC + j] = __funnelshift_l(rows[b], rows[b], rot);
+            }
+            __syncthreads();                          // the staging buffer is rewritten by the next round
+        }
+        for (int j = tid; j < TNC; j += kTileThreads) {
+            bufA[(size_t)(32 * m.L0) * TNC + j] = kFull;
+            bufA[(size_t)(32 * m.L0 + 1) * TNC + j] = 0u;
+        }
+        for (int j = warp; j < TNC; j += nwarps) {
+            const u32 nd = tnode[32 * j + lane];
+            const u32 ty = nd != ~0u ? g.node_type[nd] : ~0u;
+            for (int t = 0; t < g.n_types; ++t) {
+                const u32 col = __ballot_sync(kFull, ty == (u32)t);
+                if (lane == 0) TMV[t * TNC + j] = col;
+            }
+        }
+        if (m.D > 1)
+            for (int i = tid; i < TN * PS; i += kTileThreads) bufB[i] = 0u;
+        __syncthreads();
+
+        // ---- layers ----
+        u32 *T = bufA, *Pm = bufB;
+        for (int d = 0; d < m.D; ++d) {
+            const bool last = d == m.D - 1;
+            const TileLayer L = a.layers[d];
+            const int wr = d & 1, rd = wr ^ 1;        // survivor list written by this layer / read by it
+            const unsigned t32 = smem_u32(T);
+
+            // one warp pass: lanes hold (clause, node bits on quad q) before the layer; evaluates and hands the result on
+            auto pass = [&](int c, uint4 r, int q) {
+                if (c >= 0) r = tile_eval(r, L, c, t32 + q * 16, rowshift);
+                const bool alive = (r.x | r.y | r.z | r.w) != 0;
+                const u32 amask = __ballot_sync(kFull, alive);
+                if (amask == 0) return;
+                if (!last) {
+                    int base = 0;
+                    if (lane == 0) base = atomicAdd(&cnt[wr * 8 + q], __popc(amask));
+                    base = __shfl_sync(kFull, base, 0);
+                    if (alive) {
+                        const size_t at = (size_t)(wr * Q + q) * m.C + base + __popc(amask & ((1u << lane) - 1u));
+                        surv_c[at] = c;
+                        surv_r[at] = r;
+                        // the clause's hypervector bits on every node it is true on (the SOURCE side of kernels.py:571-588)
+                        const u32 wd[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) {
+                            u32 bits = wd[wi];
+                            while (bits) {
+                                const int slot = q * kQuadNodes + wi * 32 + __ffs(bits) - 1;
+                                bits &= bits - 1;
+                                u32 *row = Pm + (size_t)slot * PS;
+                                for (int b = 0; b < m.MB; ++b) {
+                                    const u32 bit = a.hvm[(size_t)c * m.MB + b];
+                                    const u32 mbit = 1u << (bit & 31);
+                                    if (!(*(volatile u32 *)(row + (bit >> 5)) & mbit)) atomicOr(row + (bit >> 5), mbit);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    // votes: per graph of the quad, the weights of the lanes that fired, summed over the warp
+                    int w[KP];
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) w[k] = 0;
+                    if (alive) {
+                        const int4 *wr4 = reinterpret_cast<const int4 *>(a.Wt + (size_t)c * a.KROW);
+#pragma unroll
+                        for (int k4 = 0; k4 < (KP + 3) / 4; ++k4) {
+                            const int4 t = __ldg(wr4 + k4);
+                            w[4 * k4] = t.x;
+                            if (4 * k4 + 1 < KP) w[4 * k4 + 1] = t.y;
+                            if (4 * k4 + 2 < KP) w[4 * k4 + 2] = t.z;
+                            if (4 * k4 + 3 < KP) w[4 * k4 + 3] = t.w;
+                        }
+                    }
+                    const u32 ax = __reduce_or_sync(kFull, r.x), ay = __reduce_or_sync(kFull, r.y),
+                              az = __reduce_or_sync(kFull, r.z), aw = __reduce_or_sync(kFull, r.w);
+                    for (int gl = gq_first[q]; gl < gq_first[q + 1]; ++gl) {
+                        const uint4 gm = gmask[gl];
+                        if (((ax & gm.x) | (ay & gm.y) | (az & gm.z) | (aw & gm.w)) == 0) continue;    // nobody fired on this graph
+                        const bool f = ((r.x & gm.x) | (r.y & gm.y) | (r.z & gm.z) | (r.w & gm.w)) != 0;
+                        int mine = 0;
+#pragma unroll
+                        for (int k = 0; k < KP; ++k) {
+                            const int s = __reduce_add_sync(kFull, f ? w[k] : 0);
+                            if (lane == k) mine = s;
+                        }
+                        if (lane < m.K) atomicAdd(&sums[gl * KP + lane], mine);
+                    }
+                }
+            };
+
+            if (d == 0) {
+                const int cblocks = (m.C + 31) >> 5;
+                for (int task = warp; task < cblocks * Q; task += nwarps) {
+                    const int q = task % Q;
+                    int c = (task / Q) * 32 + lane;
+                    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                    if (c < m.C) r = *reinterpret_cast<const uint4 *>(TMV + (c % g.n_types) * TNC + 4 * q);
+                    else c = -1;
+                    pass(c, r, q);
+                }
+            } else {
+                for (int q = 0; q < Q; ++q) {
+                    const int n_ent = cnt[rd * 8 + q];
+                    for (int base = warp * 32; base < n_ent; base += nwarps * 32) {
+                        int c = -1;
+                        uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                        if (base + lane < n_ent) {
+                            const size_t at = (size_t)(rd * Q + q) * m.C + base + lane;
+                            c = surv_c[at];
+                            r = surv_r[at];
+                        }
+                        pass(c, r, q);
+                    }
+                }
+            }
+            __syncthreads();
+            if (last) break;
+
+            // ---- messages of this layer -> literal rows of the next ----
+            int survivors = 0;
+            for (int q = 0; q < Q; ++q) survivors += cnt[wr * 8 + q];
+            if (survivors == 0) break;                // no clause is true anywhere: nothing can fire in later layers
+            u32 *Pdst = T;                            // the literal rows are no longer needed
+            for (int i = tid; i < TN * PS; i += kTileThreads) Pdst[i] = 0u;
+            for (int u = tid; u < TN; u += kTileThreads) {
+                u32 any = 0;
+                if (tnode[u] != ~0u)
+                    for (int w = 0; w < m.MW; ++w) any |= Pm[(size_t)u * PS + w];
+                pflag[u] = any != 0;
+            }
+            if (tid < 8) cnt[rd * 8 + tid] = 0;      // the list the next layer writes
+            __syncthreads();
+            for (int i = tid; i < TN * m.MW; i += kTileThreads) {
+                const int u = i / m.MW, w = i - u * m.MW;
+                if (!pflag[u]) continue;              // a source row without bits sends nothing
+                const u32 nd = tnode[u], info = pinfo[u];
+                const u32 base = info & 0xffffu, n = info >> 16;
+                const u32 deg = g.degree[nd], e0 = g.edge_index[nd];
+                const u32 *row = Pm + (size_t)u * PS;
+                for (u32 k = 0; k < deg && e0 + k < g.total_edges; ++k) {
+                    const u32 dst = g.edge[2 * (size_t)(e0 + k)], ty = g.edge[2 * (size_t)(e0 + k) + 1];
+                    if (dst >= n) continue;           // malformed edge: ignore, never fault
+                    const u32 val = rotated_word(row, w, ty >= (u32)m.MS ? ty % (u32)m.MS : ty, m.MS, m.MW);
+                    if (val) atomicOr(&Pdst[(size_t)(base + dst) * PS + w], val);
+                }
+            }
+            __syncthreads();
+            u32 *PT = Pm;                             // the source rows are no longer needed
+            for (int blk = tid; blk < TNC * m.MW; blk += kTileThreads) {
+                const int j = blk % TNC, w = blk / TNC, rot = (a.rot_step * j) & 31;
+                u32 rows[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rows[i] = Pdst[(size_t)(32 * j + ((i + rot) & 31)) * PS + w];
+                transpose32(rows);
+#pragma unroll
+                for (int b = 0; b < 32; ++b) PT[(size_t)(b * m.MW + w) * TNC + j] = __funnelshift_l(rows[b], rows[b], rot);
+            }
+            for (int j = tid; j < TNC; j += kTileThreads) {
+                PT[(size_t)(32 * m.MW) * TNC + j] = kFull;
+                PT[(size_t)(32 * m.MW + 1) * TNC + j] = 0u;
+            }
+            __syncthreads();
+            if (d + 1 < m.D - 1) {                    // the next layer sends messages too: its marks go where Pdst was
+                for (int i = tid; i < TN * PS; i += kTileThreads) Pdst[i] = 0u;
+                __syncthreads();
+            }
+            T = PT;
+            Pm = Pdst;
+        }
+
+        // ---- class sums of the tile's graphs (only those inside the requested range) ----
+        for (int i = tid; i < ng * m.K; i += kTileThreads) {
+            const int gl = i / m.K, k = i - gl * m.K;
+            const int64_t gi = (int64_t)g0 + gl;
+            if (gi >= a.first && gi < a.first + a.count) a.class_sums[(size_t)(gi - a.first) * m.K + k] = sums[gl * KP + k];
+        }
+        __syncthreads();                              // the shared tables are rewritten by the next tile
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static int tile_krow(int K) { return (K + 3) & ~3; }
+
+template <int KP>
+static const void *tile_kernel_ptr() { return (const void *)tile_score_kernel<KP>; }
+
+static const void *tile_kernel_for(int K)
+{
+    if (K <= 2) return tile_kernel_ptr<2>();
+    if (K <= 4) return tile_kernel_ptr<4>();
+    if (K <= 8) return tile_kernel_ptr<8>();
+    if (K <= 10) return tile_kernel_ptr<10>();
+    if (K <= 12) return tile_kernel_ptr<12>();
+    return tile_kernel_ptr<16>();
+}
+
+static int tile_kp(int K) { return K <= 2 ? 2 : K <= 4 ? 4 : K <= 8 ? 8 : K <= 10 ? 10 : K <= 12 ? 12 : 16; }
+
+int tile_model_create(TileModel *tm, const DevModel &d)
+{
+    tm->applicable = false;
+    tm->D = d.D;
+    if (d.K > kTileMaxK) return GTM_OK;
+    if (32 * (size_t)std::max(d.L0, d.D > 1 ? d.MW : 0) + 2 > 65535) return GTM_OK;     // row numbers are 16 bits
+    tm->KROW = tile_krow(d.K);
+    GTM_TRY(dev_alloc(&tm->cnt, 2 * (size_t)d.C));
+    GTM_TRY(dev_alloc(&tm->Wt, (size_t)d.C * tm->KROW));
+    GTM_TRY(dev_alloc(&tm->hvm, (size_t)d.C * d.MB));
+    GTM_TRY(dev_alloc(&tm->layers, (size_t)d.D));
+    for (int l = 0; l < d.D; ++l) GTM_TRY(dev_alloc(&tm->off[l], 2 * (size_t)d.C + 1));
+    GTM_CU(cudaMallocHost((void **)&tm->total_host, sizeof(int)));
+    tm->applicable = true;
+    return GTM_OK;
+}
+
+void tile_model_destroy(TileModel *tm)
+{
+    cudaFree(tm->cnt); cudaFree(tm->Wt); cudaFree(tm->hvm); cudaFree(tm->layers);
+    for (int l = 0; l < kMaxDepth; ++l) { cudaFree(tm->off[l]); cudaFree(tm->list[l]); }
+    if (tm->total_host) cudaFreeHost(tm->total_host);
+    *tm = TileModel();
+}
+
+// Rebuilds the included-literal lists of every layer (and the clause-major weights) from the current state.  The list
+// buffers grow to the length the state needs, which takes one host round trip per layer.
+int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s)
+{
+    if (!tm->applicable) return GTM_OK;
+    const int blocks = (d.C + 255) / 256;
+    TileLayer host_layers[kMaxDepth];
+    for (int l = 0; l < d.D; ++l) {
+        tile_count_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt);
+        tile_scan_kernel<<<1, 1024, 0, s>>>(tm->cnt, tm->off[l], 2 * d.C, tm->total_host);
+        GTM_CU(cudaGetLastError());
+        GTM_CU(cudaStreamSynchronize(s));
+        const size_t need = (size_t)*tm->total_host + 8;
+        if (need > tm->list_cap[l]) {
+            cudaFree(tm->list[l]);
+            tm->list[l] = nullptr;
+            tm->list_cap[l] = 0;
+            const size_t cap = need + need / 4;
+            GTM_TRY(dev_alloc(&tm->list[l], cap));
+            tm->list_cap[l] = cap;
+        }
+        tile_fill_kernel<<<blocks, 256, 0, s>>>(d, l, tm->off[l], tm->list[l], tm->Wt, tm->KROW, tm->hvm);
+        GTM_CU(cudaGetLastError());
+        host_layers[l].off = tm->off[l];
+        host_layers[l].list = tm->list[l];
+    }
+    GTM_CU(cudaMemcpyAsync(tm->layers, host_layers, (size_t)d.D * sizeof(TileLayer), cudaMemcpyHostToDevice, s));
+    GTM_CU(cudaStreamSynchronize(s));                 // host_layers goes out of scope
+    return GTM_OK;
+}
+
+// Shared-memory plan for tiles of TNC node words; 0 bytes when the shape cannot be served.
+struct TilePlan { int words_a = 0, words_b = 0, stage_rows = 0, PS = 0; size_t bytes = 0; };
+
+static TilePlan tile_plan(const DevModel &d, int TNC, int gmax)
+{
+    TilePlan p;
+    const int TN = TNC * 32;
+    p.PS = d.MW | 1;
+    const size_t xt = (size_t)(32 * d.L0 + 2) * TNC;
+    const size_t pm = d.D > 1 ? (size_t)TN * p.PS : 0, pt = d.D > 1 ? (size_t)(32 * d.MW + 2) * TNC : 0;
+    // staging: whole groups of 32 literal rows, up to 16 KB (or whatever the message rows need anyway), + 8 words of slack
+    size_t stage = (size_t)32 * d.L0 * std::max<size_t>(1, std::min<size_t>(TNC, 4096 / ((size_t)32 * d.L0))) + 8;
+    const size_t wa = (std::max(xt, std::max(pm, pt)) + 3) & ~(size_t)3;
+    const size_t wb = (std::max(stage, std::max(pm, pt)) + 3) & ~(size_t)3;
+    p.words_a = (int)wa;
+    p.words_b = (int)wb;
+    p.stage_rows = (int)std::min<size_t>(TN, ((wb - 8) / d.L0) / 32 * 32);
+    const size_t words = wa + wb + (size_t)kTileMaxTypes * TNC + 2 * (size_t)TN + 4 * (size_t)gmax + (size_t)gmax * tile_kp(d.K) +
+                         12 + 16 + 4 + 2;
+    p.bytes = words * sizeof(u32) + (size_t)((gmax + 3) & ~3) + (size_t)TN;
+    return p;
+}
+
+int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const gtm_graphs_view *v, int sm_count, cudaStream_t s)
+{
+    td->supported = 0;
+    if (!tm.applicable || v->max_number_of_graph_nodes > kQuadNodes) return GTM_OK;    // a graph must fit one quad
+    const int64_t N = v->number_of_graphs;
+    u32 n_min = ~0u, n_max = 0;
+    for (int64_t gi = 0; gi < N; ++gi) {
+        const u32 n = v->number_of_graph_nodes[gi];
+        n_min = std::min(n_min, n);
+        n_max = std::max(n_max, n);
+    }
+    if (n_min < 1 || n_max > (u32)kQuadNodes) return GTM_OK;
+    const void *fn = tile_kernel_for(d.K);
+    // node words per tile: the largest that lets two CTAs share an SM, else the largest that fits at all
+    int TNC = 0;
+    TilePlan plan;
+    for (int pass = 0; pass < 2 && TNC == 0; ++pass)
+        for (int cand = 32; cand >= 4; cand >>= 1) {
+            const int gbound = (int)std::min<int64_t>(kTileMaxGraphs, std::min<int64_t>(N, cand * 32 / n_min));
+            const TilePlan p = tile_plan(d, cand, gbound);
+            if (p.bytes <= (pass == 0 ? (size_t)112 * 1024 : (size_t)224 * 1024)) { TNC = cand; plan = p; break; }
+        }
+    if (TNC == 0) return GTM_OK;
+    const int TN = TNC * 32, Q = TNC / 4;
+    td->TNC = TNC;
+    td->uniform_n = n_min == n_max ? (int)n_min : 0;
+    td->tile_graph_host.clear();
+    td->tile_graph = nullptr;
+    td->gpos = nullptr;
+    td->stream = s;
+    if (td->uniform_n > 0) {
+        td->graphs_per_tile = std::min(kTileMaxGraphs, (kQuadNodes / td->uniform_n) * Q);
+        td->n_tiles = (int)((N + td->graphs_per_tile - 1) / td->graphs_per_tile);
+        td->gmax = (int)std::min<int64_t>(td->graphs_per_tile, N);
+    } else {
+        // greedy packing: consecutive graphs, a graph never straddles a quad, a tile never exceeds TN slots
+        std::vector<unsigned short> gpos((size_t)N);
+        std::vector<int> &tg = td->tile_graph_host;
+        tg.push_back(0);
+        int cur = 0, in_tile = 0, gmax = 0;
+        for (int64_t gi = 0; gi < N; ++gi) {
+            const int n = (int)v->number_of_graph_nodes[gi];
+            int pos = cur;
+            if ((pos & (kQuadNodes - 1)) + n > kQuadNodes) pos = (pos + kQuadNodes - 1) & ~(kQuadNodes - 1);
+            if (pos + n > TN || in_tile >= kTileMaxGraphs) {
+                tg.push_back((int)gi);
+                gmax = std::max(gmax, in_tile);
+                pos = 0;
+                in_tile = 0;
+            }
+            gpos[(size_t)gi] = (unsigned short)pos;
+            cur = pos + n;
+            ++in_tile;
+        }
+        gmax = std::max(gmax, in_tile);
+        tg.push_back((int)N);
+        td->graphs_per_tile = 0;
+        td->n_tiles = (int)tg.size() - 1;
+        td->gmax = gmax;
+        GTM_TRY(pool_alloc(&td->tile_graph, tg.size(), s));
+        GTM_CU(cudaMemcpyAsync(td->tile_graph, tg.data(), tg.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+        GTM_TRY(pool_alloc(&td->gpos, (size_t)N, s));
+        GTM_CU(cudaMemcpyAsync(td->gpos, gpos.data(), (size_t)N * sizeof(unsigned short), cudaMemcpyHostToDevice, s));
+        GTM_CU(cudaStreamSynchronize(s));             // gpos goes out of scope
+    }
+    plan = tile_plan(d, TNC, td->gmax);
+    td->PS = plan.PS;
+    td->words_a = plan.words_a;
+    td->words_b = plan.words_b;
+    td->stage_rows = plan.stage_rows;
+    td->smem = plan.bytes;
+    GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)td->smem));
+    int per_sm = 0;
+    GTM_CU(cudaOccupancyMaxActiveBlocksPerMultiprocessorWithFlags(&per_sm, fn, kTileThreads, td->smem, 0));
+    if (per_sm < 1) { tile_data_destroy(td); return GTM_OK; }
+    td->grid = std::max(1, std::min(sm_count * per_sm, td->n_tiles));
+    GTM_TRY(pool_alloc(&td->tile_counter, 1, s));
+    td->n_graphs = N;
+    td->supported = 1;
+    return GTM_OK;
+}
+
+void tile_data_destroy(TileData *td)
+{
+    if (td->tile_graph) cudaFreeAsync(td->tile_graph, td->stream);
+    if (td->gpos) cudaFreeAsync(td->gpos, td->stream);
+    if (td->tile_counter) cudaFreeAsync(td->tile_counter, td->stream);
+    if (td->surv_c) cudaFreeAsync(td->surv_c, td->stream);
+    if (td->surv_r) cudaFreeAsync(td->surv_r, td->stream);
+    td->tile_graph = nullptr; td->gpos = nullptr; td->tile_counter = nullptr; td->surv_c = nullptr; td->surv_r = nullptr;
+    td->supported = 0;
+}
+
+bool tile_supported(const TileData &td, int n_types) { return td.supported != 0 && n_types <= kTileMaxTypes; }
+
+int tile_score(const TileModel &tm, TileData &td, const DevModel &d, const DevGraphs &dg, int n_types, int64_t first,
+               int64_t count, int *sums_dev, int *error_dev, cudaStream_t s)
+{
+    const int Q = td.TNC / 4;
+    if (!td.surv_c) {          // survivor lists: one pair per resident CTA, allocated on first use
+        const size_t entries = (size_t)td.grid * 2 * Q * d.C;
+        GTM_TRY(pool_alloc(&td.surv_c, entries, s));
+        GTM_TRY(pool_alloc(&td.surv_r, entries, s));
+    }
+    DevGraphs g = dg;
+    g.n_types = n_types;
+    TileArgs a;
+    a.tile_graph = td.tile_graph;
+    a.gpos = td.gpos;
+    a.uniform_n = td.uniform_n;
+    a.graphs_per_tile = td.graphs_per_tile;
+    int lo, hi;
+    if (td.graphs_per_tile > 0) {
+        lo = (int)(first / td.graphs_per_tile);
+        hi = (int)((first + count + td.graphs_per_tile - 1) / td.graphs_per_tile);
+    } else {
+        const std::vector<int> &tg = td.tile_graph_host;
+        lo = (int)(std::upper_bound(tg.begin(), tg.end(), (int)first) - tg.begin()) - 1;
+        hi = (int)(std::lower_bound(tg.begin(), tg.end(), (int)(first + count)) - tg.begin());
+    }
+    a.tile_lo = lo; a.tile_hi = hi;
+    a.first = first; a.count = count; a.n_graphs = td.n_graphs;
+    a.class_sums = sums_dev; a.tile_counter = td.tile_counter;
+    a.TNC = td.TNC; a.PS = td.PS; a.words_a = td.words_a; a.words_b = td.words_b; a.stage_rows = td.stage_rows; a.gmax = td.gmax;
+    int inv = 1;                                       // inverse of the (odd) message row stride modulo 32
+    while ((td.PS * inv) % 32 != 1) inv += 2;
+    a.rot_step = ((32 / td.TNC) * inv) & 31;
+    a.layers = tm.layers; a.Wt = tm.Wt; a.KROW = tm.KROW; a.hvm = tm.hvm;
+    a.surv_c = td.surv_c; a.surv_r = td.surv_r;
+    a.error = error_dev;
+    GTM_CU(cudaMemsetAsync(td.tile_counter, 0, sizeof(unsigned), s));
+    const int grid = std::max(1, std::min(td.grid, hi - lo));
+    DevModel dm = d;
+    void *args[] = {&dm, &g, &a};
+    GTM_CU(cudaLaunchKernel(tile_kernel_for(d.K), dim3(grid), dim3(kTileThreads), args, td.smem, s));
+    return GTM_OK;
+}
+
+}  // namespace gtm

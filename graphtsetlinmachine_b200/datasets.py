@@ -16,7 +16,7 @@ import numpy as np
 from .graphs import Graphs
 
 __all__ = ["noisy_xor", "vanilla_images", "convolution_images", "sequences", "random_multigraphs",
-           "image_prototypes", "sample_images", "replicate"]
+           "image_prototypes", "sample_images", "replicate", "RepeatedGraphs"]
 
 
 def _new(n, symbols, hv_size, hv_bits, init_with):
@@ -225,3 +225,39 @@ def replicate(graphs, times):
     out.graph_node_id = _LazyNodeIds(out.number_of_graph_nodes)
     out.encode()
     return out
+
+
+class RepeatedGraphs:
+    """`times` copies of `base` back to back, WITHOUT materialising them: a large global graph set for sharded
+    scoring (``sharding.GraphShardScorer``), of which every rank only ever builds its own contiguous range.
+
+    It has the attributes the scorer reads (``number_of_graphs``, ``number_of_graph_nodes``, ``signature``) and
+    ``self[first:stop]``, which returns an ordinary ``Graphs`` holding copies of graphs ``first..stop-1`` of the
+    repeated sequence (graph ``i`` is ``base[i % len(base)]``), equal to the same slice of ``replicate(base, times)``."""
+
+    def __init__(self, base, times):
+        import hashlib
+
+        self.base = base
+        self.times = int(times)
+        self.number_of_graphs = int(base.number_of_graphs) * self.times
+        self.number_of_graph_nodes = np.tile(base.number_of_graph_nodes, self.times)
+        self.max_number_of_graph_nodes = base.max_number_of_graph_nodes
+        self.signature = hashlib.sha256(bytes(base.signature) + b"x%d" % self.times).digest()
+
+    def __len__(self):
+        return self.number_of_graphs
+
+    def number_of_node_types(self):
+        return self.base.number_of_node_types()
+
+    def __getitem__(self, index):
+        if not isinstance(index, slice):
+            raise TypeError("RepeatedGraphs supports contiguous slices only")
+        first, stop, step = index.indices(self.number_of_graphs)
+        if step != 1 or stop <= first:
+            raise ValueError("RepeatedGraphs supports non-empty slices with step 1 only")
+        n = int(self.base.number_of_graphs)
+        if first % n == 0 and stop - first == n:
+            return self.base                                    # exactly one copy: no need to build anything
+        return self.base[np.arange(first, stop) % n]

@@ -303,8 +303,12 @@ class Graphs:
                      one_hot_encoding=self.one_hot_encoding, init_with=self)
         idx = np.asarray(indices, dtype=np.int64)
         sub.number_of_graph_nodes[:] = self.number_of_graph_nodes[idx]
-        sub.graph_node_id = [self.graph_node_id[i] for i in indices]
+        lazy_ids = isinstance(self.graph_node_id, _LazyNodeIds)     # bulk-built sets: node i of a graph is named i
+        if not lazy_ids:
+            sub.graph_node_id = [self.graph_node_id[i] for i in indices]
         sub.prepare_node_configuration()
+        if lazy_ids:
+            sub.graph_node_id = _LazyNodeIds(sub.number_of_graph_nodes)
         counts = self.number_of_graph_nodes[idx].astype(np.int64)
         # source row of every node of the subset, in subset order
         starts = self.node_index[idx].astype(np.int64)

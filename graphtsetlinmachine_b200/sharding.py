@@ -54,24 +54,46 @@ def gather_rows(local_rows, counts, group=None):
 
 
 class GraphShardScorer:
-    """``score(graphs)`` over all ranks of the default process group.  Every rank holds the same model and the same
-    ``graphs`` object; each uploads and scores only its own range (``graphs[first:first+count]``)."""
+    """``score(graphs)`` over all ranks of a process group.  Every rank holds the same model and the same ``graphs``
+    object (a ``Graphs``, or a ``datasets.RepeatedGraphs``); each builds, uploads and scores only its own contiguous
+    range, chosen so that the ranks get equal numbers of nodes.  The rank's slice is kept until a graph set with another
+    signature arrives, so repeated calls copy and score, but do not slice again."""
 
     def __init__(self, tm, group=None):
         self.tm = tm
         self.group = group
+        self._signature = None
+        self._ranges = None
+        self._local = None
 
-    def score(self, graphs):
+    def shard(self, graphs):
+        """(ranges of all ranks, this rank's graphs or None when its range is empty)."""
         import torch.distributed as dist
 
-        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        ranges = balanced_ranges(graphs.number_of_graph_nodes, world)
-        first, count = ranges[rank]
-        if count:
-            local = self.tm.score(graphs[first:first + count])
-        else:
-            local = np.zeros((0, self.tm.number_of_outputs), dtype=np.int32)
-        return gather_rows(local, [c for _, c in ranges], self.group)
+        if self._signature is None or not np.array_equal(self._signature, graphs.signature):
+            world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+            self._ranges = balanced_ranges(graphs.number_of_graph_nodes, world)
+            first, count = self._ranges[rank]
+            self._local = graphs[first:first + count] if count else None
+            self._signature = graphs.signature
+        return self._ranges, self._local
+
+    def score_local(self, graphs, out=None):
+        """Class sums of this rank's range only: ((first, count), int32[count][K]); no communication at all.
+        `out` (optional, e.g. page-locked) receives the rows in place."""
+        import torch.distributed as dist
+
+        ranges, local = self.shard(graphs)
+        first, count = ranges[dist.get_rank(self.group)]
+        if not count:
+            return (first, 0), np.zeros((0, self.tm.number_of_outputs), dtype=np.int32)
+        rows = self.tm.score(local) if out is None else self.tm.score(local, out=out)
+        return (first, count), rows
+
+    def score(self, graphs):
+        """Class sums of all graphs on every rank (the ranks' rows gathered in rank order)."""
+        (_, _), local = self.score_local(graphs)
+        return gather_rows(local, [c for _, c in self._ranges], self.group)
 
     def predict(self, graphs):
         return np.argmax(self.score(graphs), axis=1)

@@ -88,7 +88,8 @@ int gtm_set_stream(gtm_model *model, void *cuda_stream);
 
 /* Kernel selection (the reference has one code path; its only launch knobs are grid/block, tm.py:53-54).
  *   "fit_kernel":   0 = automatic, 1 = learning kernel with state in global memory, 2 = state-resident kernel
- *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel
+ *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel (depth 1), 3 = tile kernel (any depth,
+ *                   graphs of at most 128 nodes); set it before the graph set is created
  *   "fit_timers":   1 = the learning kernels time their phases for gtm_debug_fit_phase_cycles (default 0)
  * Forcing a kernel that cannot serve the model makes the next fit / score call fail with GTM_ERR_ARG. */
 int gtm_set_option(gtm_model *model, const char *name, int value);

@@ -14,6 +14,7 @@ import pytest
 
 from cases import make_case
 from graphtsetlinmachine_b200 import _lib
+from oracle.oracle import OracleTM
 from util import EngineTM, encode_labels, random_graphs
 
 pytestmark = pytest.mark.gpu
@@ -46,6 +47,13 @@ def test_static_scratch_scoring_matches_allocating_entry_point(engine_lib, name)
     tm.prepare()
     tm.fit(encY)
     want = tm.score()                                   # existing entry point (allocates scratch and result)
+    cpu = OracleTM(**kw)                                # and the CPU checker, from the same state
+    cpu.set_graphs(graphs)
+    cpu.ta_state[...] = tm.ta_state
+    for mine, theirs in zip(cpu.message_ta_state, tm.message_ta_state):
+        mine[...] = theirs
+    cpu.clause_weights[...] = tm.clause_weights
+    assert np.array_equal(cpu.score(), want)
     view, keep = device_view(graphs, torch)
     n, K = graphs.number_of_graphs, kw["classes"]
     out = torch.full((n, K), -12345, dtype=torch.int32, device="cuda")
@@ -87,4 +95,69 @@ def test_static_scratch_rejects_sizes_beyond_its_capacity(engine_lib):
     out = torch.zeros((2, 2), dtype=torch.int32, device="cuda")
     status = engine_lib.gtm_score_static_scratch(tm.model, C.byref(view), 1, 0, 2, C.c_void_p(out.data_ptr()))
     assert status == 1 and b"built-in scratch" in engine_lib.gtm_last_error()
+    tm.close()
+
+
+def test_static_scratch_refuses_misaligned_literal_rows(engine_lib):
+    """Literal rows that are a multiple of 16 bytes are read with 128-bit loads, so a caller that carves X out of its
+    own pool at a 4-byte offset is told so (status 1, nothing launched) instead of faulting on the device."""
+    import torch
+
+    kw, graphs, encY, _ = make_case("case_d")           # 128 literals: 4 words = 16 bytes per row
+    tm = EngineTM(**kw)
+    tm.set_graphs(graphs)
+    tm.prepare()
+    view, keep = device_view(graphs, torch)
+    n, K = graphs.number_of_graphs, kw["classes"]
+    x_host = np.ascontiguousarray(graphs.X, dtype=np.uint32)
+    shifted = torch.zeros(x_host.size + 8, dtype=torch.int32, device="cuda")
+    shifted[1:1 + x_host.size] = torch.from_numpy(x_host.view(np.int32).ravel()).cuda()
+    view.X = shifted.data_ptr() + 4
+    out = torch.zeros((n, K), dtype=torch.int32, device="cuda")
+    status = engine_lib.gtm_score_static_scratch(tm.model, C.byref(view), tm.n_types, 0, n, C.c_void_p(out.data_ptr()))
+    assert status == 1 and b"16-byte aligned" in engine_lib.gtm_last_error()
+    view.X = shifted.data_ptr() + 16                     # the same rows at an aligned address are fine
+    shifted[4:4 + x_host.size] = torch.from_numpy(x_host.view(np.int32).ravel()).cuda()
+    _lib.check(engine_lib.gtm_score_static_scratch(tm.model, C.byref(view), tm.n_types, 0, n, C.c_void_p(out.data_ptr())))
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), tm.score())
+    tm.close()
+
+
+def test_static_scratch_skips_graphs_that_do_not_fit(engine_lib):
+    """Graph arrays in device memory cannot be checked by the host.  A graph that claims more nodes than
+    max_number_of_graph_nodes (its rows would leave the block's scratch slice) or a node range past total_nodes is
+    skipped by the kernel - class sums zero, every other graph unaffected - and gtm_check_skipped_graphs reports it."""
+    import torch
+
+    kw, graphs, encY, _ = make_case("case_a")
+    tm = EngineTM(**kw)
+    tm.set_graphs(graphs)
+    tm.prepare()
+    tm.fit(encY)
+    want = tm.score()
+    view, dev = device_view(graphs, torch)
+    n, K = graphs.number_of_graphs, kw["classes"]
+    out = torch.zeros((n, K), dtype=torch.int32, device="cuda")
+    flag = C.c_int(-1)
+    _lib.check(engine_lib.gtm_score_static_scratch(tm.model, C.byref(view), tm.n_types, 0, n, C.c_void_p(out.data_ptr())))
+    _lib.check(engine_lib.gtm_check_skipped_graphs(tm.model, C.byref(flag)))
+    assert flag.value == 0 and np.array_equal(out.cpu().numpy(), want)
+    n_nodes = dev[6]
+    n_nodes[3] = 1000                                    # far more than max_number_of_graph_nodes
+    n_nodes[n - 1] = int(graphs.max_number_of_graph_nodes)
+    dev[5][n - 1] = view.total_nodes - 1                 # node range runs past total_nodes
+    out.fill_(-7)
+    _lib.check(engine_lib.gtm_score_static_scratch(tm.model, C.byref(view), tm.n_types, 0, n, C.c_void_p(out.data_ptr())))
+    _lib.check(engine_lib.gtm_check_skipped_graphs(tm.model, C.byref(flag)))
+    got = out.cpu().numpy()
+    assert flag.value == 1
+    keepers = np.ones(n, dtype=bool)
+    keepers[[3, n - 1]] = False
+    assert np.array_equal(got[keepers], want[keepers])
+    assert not got[3].any()
+    if int(graphs.max_number_of_graph_nodes) > 1:
+        assert not got[n - 1].any()
+    _lib.check(engine_lib.gtm_check_skipped_graphs(tm.model, C.byref(flag)))
+    assert flag.value == 0                               # cleared by the call that reported it
     tm.close()
