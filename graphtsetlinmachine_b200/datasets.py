@@ -260,4 +260,4 @@ class RepeatedGraphs:
         n = int(self.base.number_of_graphs)
         if first % n == 0 and stop - first == n:
             return self.base                                    # exactly one copy: no need to build anything
-        return self.base[np.arange(first, stop) % n]
+        return self.base._create_subset(np.arange(first, stop) % n)

@@ -53,6 +53,15 @@ def gather_rows(local_rows, counts, group=None):
     return np.concatenate([parts[r][:counts[r]].cpu().numpy() for r in range(world)], axis=0)
 
 
+def _world_and_rank(group=None):
+    """(world size, rank) of the group; (1, 0) in a process that has not joined any process group."""
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
 class GraphShardScorer:
     """``score(graphs)`` over all ranks of a process group.  Every rank holds the same model and the same ``graphs``
     object (a ``Graphs``, or a ``datasets.RepeatedGraphs``); each builds, uploads and scores only its own contiguous
@@ -68,10 +77,8 @@ class GraphShardScorer:
 
     def shard(self, graphs):
         """(ranges of all ranks, this rank's graphs or None when its range is empty)."""
-        import torch.distributed as dist
-
         if self._signature is None or not np.array_equal(self._signature, graphs.signature):
-            world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+            world, rank = _world_and_rank(self.group)
             self._ranges = balanced_ranges(graphs.number_of_graph_nodes, world)
             first, count = self._ranges[rank]
             self._local = graphs[first:first + count] if count else None
@@ -81,10 +88,8 @@ class GraphShardScorer:
     def score_local(self, graphs, out=None):
         """Class sums of this rank's range only: ((first, count), int32[count][K]); no communication at all.
         `out` (optional, e.g. page-locked) receives the rows in place."""
-        import torch.distributed as dist
-
         ranges, local = self.shard(graphs)
-        first, count = ranges[dist.get_rank(self.group)]
+        first, count = ranges[_world_and_rank(self.group)[1]]
         if not count:
             return (first, 0), np.zeros((0, self.tm.number_of_outputs), dtype=np.int32)
         rows = self.tm.score(local) if out is None else self.tm.score(local, out=out)
@@ -93,6 +98,8 @@ class GraphShardScorer:
     def score(self, graphs):
         """Class sums of all graphs on every rank (the ranks' rows gathered in rank order)."""
         (_, _), local = self.score_local(graphs)
+        if _world_and_rank(self.group)[0] == 1:
+            return local
         return gather_rows(local, [c for _, c in self._ranges], self.group)
 
     def predict(self, graphs):

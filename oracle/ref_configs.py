@@ -9,6 +9,14 @@ CONFIGS = {
                       message_size=256, message_bits=2),
     # MNIST-shaped single-node graphs: the benchmark workload
     "vanilla_images": dict(classes=10, clauses=2500, literals=256, threshold=3125, max_nodes=1),
+    # the other benchmark configurations: convolution-shaped images (361 nodes), sequences (1,000-node paths, depth 3),
+    # random multigraphs (8..32 nodes, depth 3, 20,000 clauses)
+    "convolution_images": dict(classes=10, clauses=2500, literals=256, threshold=3125, max_nodes=361),
+    "sequences": dict(classes=2, clauses=2000, literals=512, threshold=2000, max_nodes=1000, message_size=512, message_bits=2),
+    "multigraphs": dict(classes=10, clauses=20000, literals=2048, threshold=10000, max_nodes=32, message_size=1024,
+                        message_bits=2),
+    # a 33..1,024-node shape for the transposed evaluation (tests/test_gpu_reference_kernels.py)
+    "mid_graphs": dict(classes=3, clauses=300, literals=128, threshold=150, max_nodes=200, message_size=128, message_bits=2),
     # small differential-test sets (tests/cases.py)
     "case_a": dict(classes=2, clauses=20, literals=64, threshold=20, max_nodes=5, message_size=64, message_bits=2),
     "case_b": dict(classes=3, clauses=33, literals=80, threshold=30, max_nodes=40, message_size=50, message_bits=2,
@@ -21,4 +29,4 @@ CONFIGS = {
 }
 
 # sets that are also built for the GPU (the reference's kernels on the same B200, launched like the reference does)
-GPU_CONFIGS = ("noisy_xor", "vanilla_images", "case_b", "case_e")
+GPU_CONFIGS = ("noisy_xor", "vanilla_images", "convolution_images", "sequences", "multigraphs", "mid_graphs", "case_b", "case_e")

@@ -122,3 +122,75 @@ def test_noisy_xor_learning_is_statistically_equivalent():
     print("noisy XOR accuracy: engine", a, "reference kernels", b)
     assert a.max() >= 0.99 and b.max() >= 0.99
     assert abs(a.mean() - b.mean()) <= 0.25
+
+
+def _benchmark_shape(name):
+    """(model kwargs, training graphs, labels, test graphs, passes) at the model sizes of the benchmark configurations."""
+    from graphtsetlinmachine_b200 import datasets
+    from util import random_graphs
+
+    np.random.seed(5)
+    if name == "convolution_images":
+        protos = datasets.image_prototypes(1)
+        train, y = datasets.convolution_images(60, 2, protos)
+        test, _ = datasets.convolution_images(40, 3, protos, init_with=train)
+        kw = dict(clauses=2500, classes=10, literals=256, threshold=3125, s=10.0, depth=1, max_nodes=361)
+    elif name == "sequences":
+        train, y = datasets.sequences(12, 2)
+        test, _ = datasets.sequences(8, 3, init_with=train)
+        kw = dict(clauses=2000, classes=2, literals=512, threshold=2000, s=5.0, depth=3, message_size=512, message_bits=2,
+                  max_nodes=1000)
+    elif name == "multigraphs":
+        train, y = datasets.random_multigraphs(40, 2, min_nodes=8, max_nodes=32)
+        test, _ = datasets.random_multigraphs(30, 3, init_with=train)
+        kw = dict(clauses=20000, classes=10, literals=2048, threshold=10000, s=10.0, depth=3, message_size=1024,
+                  message_bits=2, max_nodes=32)
+    else:                                               # 33..1,024 nodes: the transposed evaluation of the general kernels
+        rng = np.random.default_rng(17)
+        train = random_graphs(30, rng, hv_size=64, max_nodes=200, node_types=2, edge_types=3, max_degree=3)
+        test = random_graphs(24, rng, max_nodes=200, node_types=2, edge_types=3, max_degree=3, init_with=train)
+        y = rng.integers(0, 3, size=30)
+        kw = dict(clauses=300, classes=3, literals=128, threshold=150, s=3.0, depth=3, message_size=128, message_bits=2,
+                  max_nodes=200)
+    rng = np.random.default_rng(9)
+    hv = np.stack([rng.choice(kw.get("message_size", 256), size=2, replace=False) for _ in range(kw["clauses"])]).astype(np.uint32)
+    return dict(kw, hypervectors=hv, seed=13), train, y, test
+
+
+@pytest.mark.parametrize("name", ["convolution_images", "sequences", "multigraphs", "mid_graphs"])
+def test_benchmark_shapes_match_reference_kernels_on_the_gpu(name):
+    """Benchmark configurations 3, 4 and 5 and a 33..1,024-node shape: after three learning passes the engine's class
+    sums (every scoring kernel that serves the shape), node outputs per layer, messages and include counts equal what
+    the reference's own kernels compute on the same GPU from the same state."""
+    kw, train, y, test = _benchmark_shape(name)
+    engine = EngineTM(**kw)
+    engine.set_graphs(train)
+    engine.prepare()
+    engine.fit(encode_labels(y, kw["classes"], kw["threshold"]), epochs=3)
+    ref = _reference(kw)
+    ref.load_from(engine)
+    ref.set_graphs(test)
+    engine.set_graphs(test)
+    want = ref.score()
+    assert np.abs(want).sum() > 0
+    np.testing.assert_array_equal(engine.score(), want, err_msg="automatic scoring kernel")
+    np.testing.assert_array_equal(engine.transform()[1], want, err_msg="general scoring kernel")
+    for e in range(0, test.number_of_graphs, max(1, test.number_of_graphs // 4)):
+        a = ref.evaluate_graph(e)
+        for path in (0, 1):
+            b = engine.evaluate_graph(e, path=path)
+            np.testing.assert_array_equal(a["cno"], b["cno"], err_msg="node outputs, graph %d path %d" % (e, path))
+            for d in range(kw["depth"] - 1):
+                np.testing.assert_array_equal(a["messages"][d], b["messages"][d], err_msg="messages, graph %d layer %d" % (e, d))
+            np.testing.assert_array_equal(a["n_inc"], b["n_inc"])
+            np.testing.assert_array_equal(a["class_sum"], b["class_sum"])
+    if kw["max_nodes"] <= 128:
+        tile = EngineTM(**kw, options={"score_kernel": 3})
+        tile.set_graphs(test)
+        for d in range(kw["depth"]):
+            tile.set_ta(d, engine.get_ta(d))
+        tile.set_weights(engine.clause_weights)
+        np.testing.assert_array_equal(tile.score(), want, err_msg="tile scoring kernel")
+        tile.close()
+    engine.close()
+    ref.close()
