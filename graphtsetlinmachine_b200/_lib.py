@@ -68,6 +68,7 @@ PROTOTYPES = {
     "gtm_shard_connect": [C.c_void_p, C.c_void_p, C.c_void_p],
     "gtm_fit": [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int],
     "gtm_transform": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p],
+    "gtm_transform_nodewise": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p],
     "gtm_debug_evaluate": [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
                            C.c_void_p, C.c_void_p],
     "gtm_debug_last_feedback": [C.c_void_p, C.c_void_p, C.c_void_p],

@@ -196,13 +196,12 @@ extern "C" int gtm_set_ta_state(gtm_model *m, int layer, const uint32_t *ta)
     const int W = layer_words(m, layer);
     const size_t total = (size_t)d.C * d.SB * W;
     u32 *tmp;
-    GTM_TRY(dev_alloc(&tmp, total));
+    GTM_TRY(pool_alloc(&tmp, total, m->stream));      // stream-ordered: no device-wide synchronisation
     cudaError_t e = cudaMemcpyAsync(tmp, ta, total * sizeof(u32), cudaMemcpyHostToDevice, m->stream);
-    if (e == cudaSuccess) {
+    if (e == cudaSuccess)
         planes_from_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(tmp, layer_planes(m, layer), d.C, d.SB, W);
-        e = cudaStreamSynchronize(m->stream);
-    }
-    cudaFree(tmp);
+    cudaFreeAsync(tmp, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     GTM_CU(e);
     m->has_state = true;
     m->lists_dirty = true; ++m->state_version;
@@ -218,11 +217,11 @@ extern "C" int gtm_get_ta_state(gtm_model *m, int layer, uint32_t *out)
     const int W = layer_words(m, layer);
     const size_t total = (size_t)d.C * d.SB * W;
     u32 *tmp;
-    GTM_TRY(dev_alloc(&tmp, total));
+    GTM_TRY(pool_alloc(&tmp, total, m->stream));
     planes_to_reference_kernel<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, m->stream>>>(layer_planes(m, layer), tmp, d.C, d.SB, W);
     cudaError_t e = cudaMemcpyAsync(out, tmp, total * sizeof(u32), cudaMemcpyDeviceToHost, m->stream);
+    cudaFreeAsync(tmp, m->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
-    cudaFree(tmp);
     GTM_CU(e);
     return GTM_OK;
 }
@@ -526,13 +525,14 @@ static int ensure_score_scratch(gtm_dataset *ds)
 }
 
 static int launch_score_general(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
-                                int *sums_dev, int *clause_out_dev)
+                                int *sums_dev, int *clause_out_dev, int *node_out_dev = nullptr, int node_stride = 0)
 {
     GTM_TRY(ensure_score_scratch(ds));
     DevGraphs g = ds->dg;
     g.n_types = n_types;
     ScoreArgs a;
     a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = clause_out_dev;
+    a.node_outputs = node_out_dev; a.node_stride = node_stride;
     a.cno_stride = ds->cno_stride; a.P_stride = ds->P_stride; a.ninc_stride = ds->ninc_stride;
     a.part_words = ds->score_part_words; a.t_stride = ds->score_t_stride;
     const int grid = (int)std::min<int64_t>(ds->score_grid, (count + ds->score_units - 1) / ds->score_units);
@@ -692,24 +692,44 @@ extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v,
     return GTM_OK;
 }
 
-extern "C" int gtm_transform(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
-                             int32_t *clause_out, int32_t *sums_out)
+// clause outputs per graph and / or per node through the general scoring kernel; results land in host arrays
+static int transform_common(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count, int32_t *clause_out,
+                            int32_t *node_out, int node_stride, int32_t *sums_out)
 {
     GTM_TRY(bind(m));
     GTM_TRY(check_range(m, ds, n_types, first, count));
     if (count == 0) return GTM_OK;
-    int *sums_dev = nullptr, *co_dev = nullptr;
-    GTM_TRY(dev_alloc(&sums_dev, (size_t)count * m->dm.K));
-    int st = dev_alloc(&co_dev, (size_t)count * m->dm.C);
-    if (st == GTM_OK) st = launch_score_general(m, ds, n_types, first, count, sums_dev, co_dev);
+    int *sums_dev = nullptr, *co_dev = nullptr, *no_dev = nullptr;
+    const size_t n_sums = (size_t)count * m->dm.K, n_co = (size_t)count * m->dm.C, n_no = n_co * (size_t)node_stride;
+    int st = pool_alloc(&sums_dev, n_sums, m->stream);
+    if (st == GTM_OK && clause_out) st = pool_alloc(&co_dev, n_co, m->stream);
+    if (st == GTM_OK && node_out) st = pool_alloc(&no_dev, n_no, m->stream);
+    if (st == GTM_OK) st = launch_score_general(m, ds, n_types, first, count, sums_dev, co_dev, no_dev, node_stride);
     cudaError_t e = cudaSuccess;
-    if (st == GTM_OK && sums_out) e = cudaMemcpyAsync(sums_out, sums_dev, (size_t)count * m->dm.K * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
-    if (st == GTM_OK && e == cudaSuccess && clause_out) e = cudaMemcpyAsync(clause_out, co_dev, (size_t)count * m->dm.C * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (st == GTM_OK && sums_out) e = cudaMemcpyAsync(sums_out, sums_dev, n_sums * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (st == GTM_OK && e == cudaSuccess && clause_out) e = cudaMemcpyAsync(clause_out, co_dev, n_co * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (st == GTM_OK && e == cudaSuccess && node_out) e = cudaMemcpyAsync(node_out, no_dev, n_no * sizeof(int), cudaMemcpyDeviceToHost, m->stream);
+    if (sums_dev) cudaFreeAsync(sums_dev, m->stream);
+    if (co_dev) cudaFreeAsync(co_dev, m->stream);
+    if (no_dev) cudaFreeAsync(no_dev, m->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
-    cudaFree(sums_dev); cudaFree(co_dev);
     if (st != GTM_OK) return st;
     GTM_CU(e);
     return GTM_OK;
+}
+
+extern "C" int gtm_transform(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
+                             int32_t *clause_out, int32_t *sums_out)
+{
+    return transform_common(m, ds, n_types, first, count, clause_out, nullptr, 0, sums_out);
+}
+
+extern "C" int gtm_transform_nodewise(gtm_model *m, gtm_dataset *ds, int n_types, int64_t first, int64_t count,
+                                      int node_stride, int32_t *node_out, int32_t *sums_out)
+{
+    if (!node_out) return fail(GTM_ERR_ARG, "node_outputs_out is null");
+    if (!ds || node_stride < ds->max_nodes) return fail(GTM_ERR_ARG, "node_stride must be at least the largest graph's node count");
+    return transform_common(m, ds, n_types, first, count, nullptr, node_out, node_stride, sums_out);
 }
 
 // --------------------------------------------------------------------------------------------- learning
@@ -771,7 +791,7 @@ extern "C" int gtm_debug_evaluate(gtm_model *m, gtm_dataset *ds, int n_types, in
         int *sums;
         GTM_TRY(dev_alloc(&sums, (size_t)d.K));
         ScoreArgs a;
-        a.first = graph; a.count = 1; a.class_sums = sums; a.clause_outputs = nullptr;
+        a.first = graph; a.count = 1; a.class_sums = sums; a.clause_outputs = nullptr; a.node_outputs = nullptr; a.node_stride = 0;
         a.cno_stride = a.P_stride = a.ninc_stride = 0;
         a.part_words = 0; a.t_stride = 0;
         EvalScratch sc = ds->fit_sc;
@@ -942,7 +962,7 @@ extern "C" int gtm_score_static_scratch(gtm_model *m, const gtm_graphs_view *v, 
     sc.n_inc = reinterpret_cast<int *>(scratch_base + cno_words + p_words);
     sc.NC = NC; sc.cno_slots = 2; sc.max_nodes = v->max_number_of_graph_nodes;
     ScoreArgs a;
-    a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr;
+    a.first = first; a.count = count; a.class_sums = sums_dev; a.clause_outputs = nullptr; a.node_outputs = nullptr; a.node_stride = 0;
     a.cno_stride = a.P_stride = a.ninc_stride = per_cta;                             // one contiguous slice per CTA
     a.part_words = 0; a.t_stride = 0;
     score_graphs_kernel<true><<<grid, 256, (size_t)d.K * sizeof(int), m->stream>>>(d, g, sc, a);

@@ -65,6 +65,8 @@ struct ScoreArgs {
     int64_t first, count;
     int *class_sums;      // [count][K]
     int *clause_outputs;  // optional [count][C] (transform)
+    int *node_outputs;    // optional [count][C][node_stride] per-node clause outputs of the last layer (transform_nodewise)
+    int node_stride;
     size_t cno_stride, P_stride, ninc_stride;  // per-CTA scratch strides (elements)
     int part_words;       // > 0: shared-memory words (after the vote partial) that accumulate one layer's messages
     int t_stride;         // > 0: a transposed-graph buffer follows, with this (odd) row stride (TransposedGraph)
@@ -142,6 +144,15 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
             }
         }
         for (int k = threadIdx.x; k < m.K; k += blockDim.x) a.class_sums[(size_t)i * m.K + k] = s_sum[k];
+        if (a.node_outputs) {
+            // the last layer's node-output words, one int per (clause, node) as kernels.py:693-709 unpacks them
+            const int stride = a.node_stride;
+            for (size_t t = threadIdx.x; t < (size_t)m.C * stride; t += blockDim.x) {
+                const int c = (int)(t / stride), v = (int)(t - (size_t)c * stride);
+                const u32 word = v < n ? cno_row(sc, m.C, m.D - 1, c)[v >> 5] : 0u;
+                a.node_outputs[((size_t)i * m.C + c) * stride + v] = (int)((word >> (v & 31)) & 1u);
+            }
+        }
         __syncthreads();
     }
 }
@@ -204,6 +215,14 @@ __global__ void __launch_bounds__(256, 5) score_small_graphs_kernel(DevModel m, 
             }
         }
         for (int k = lane; k < m.K; k += 32) a.class_sums[(size_t)i * m.K + k] = s_sum[k];
+        if (a.node_outputs) {
+            const int stride = a.node_stride;
+            for (int t = lane; t < m.C * stride; t += 32) {
+                const int c = t / stride, v = t - c * stride;
+                const u32 word = v < n ? cno_row(sc, m.C, m.D - 1, c)[v >> 5] : 0u;
+                a.node_outputs[((size_t)i * m.C + c) * stride + v] = (int)((word >> (v & 31)) & 1u);
+            }
+        }
         __syncwarp();
     }
 }

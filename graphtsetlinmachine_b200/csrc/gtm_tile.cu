@@ -7,22 +7,23 @@
 //   1. the tile's literal rows - one contiguous piece of X - arrive through a bulk asynchronous copy
 //      (cp.async.bulk, completion on an mbarrier) and are transposed into XT[literal][node word]
 //      (bit i of word j = that literal on node slot 32j+i);
-//   2. layer 0: a thread evaluates one clause on one quad, r = type/valid mask AND the rows of the clause's INCLUDED
-//      literals (one 128-bit shared load per literal and 128 nodes; included-literal lists are rebuilt from the
-//      include planes whenever the automata changed), leaving as soon as r is empty; an empty clause is true
-//      (kernels.py:443-460);
-//   3. clauses that are still true somewhere go to a per-quad survivor list (clause, node bits) and mark their
-//      hypervector bits on the SOURCE nodes (node-major rows P[slot]); later layers only visit survivors, which is
-//      what "layer d is ANDed with layer d-1" (kernels.py:525-527) comes to;
-//   4. one pass over the tile's edges ORs the source rows, rotated by the edge type ((hv + type) mod MS,
-//      kernels.py:581), into the destination rows, and the result is transposed into PT[message bit][node word], the
-//      literal rows of the next layer (a negated message literal ANDs the complement of its row);
+//   2. layer 0: a thread evaluates one clause on a PAIR of quads, r = type/valid mask AND the rows of the clause's
+//      INCLUDED literals (one 128-bit shared load per literal and 128 nodes), leaving as soon as r is empty; an empty
+//      clause is true (kernels.py:443-460).  The included-literal lists are rebuilt from the include planes whenever
+//      the automata changed and are stored interleaved per 32 clauses, so that a warp reads them with coalesced loads;
+//   3. clauses that are still true somewhere go to a survivor list (clause, node bits) and OR their node bits into the
+//      rows of their hypervector bits in a bit-major mark buffer (one 128-bit OR per hypervector bit and quad); later
+//      layers only visit survivors, which is what "layer d is ANDed with layer d-1" (kernels.py:525-527) comes to;
+//   4. the marks are transposed to node-major rows (the message each node SENDS), one pass over the tile's edges ORs
+//      them, rotated by the edge type ((hv + type) mod MS, kernels.py:581), into the destination rows, and those are
+//      transposed back into PT[message bit][node word], the literal rows of the next layer (a negated message literal
+//      ANDs the complement of its row);
 //   5. after the last layer, per graph and warp, the weights of the clauses that fired are summed over the warp with
 //      redux.sync and added to the graph's class sums in shared memory (kernels.py:279-317, unclamped).
 //
-// The two big buffers swap roles from layer to layer (literal rows <-> message rows), so the footprint is one
-// transposed tile plus one node-major message tile.  Global scratch: the survivor lists (L2 traffic proportional
-// to the clauses that are still true).
+// Shared memory: one buffer of literal rows (transposed literals, then transposed messages) and one that serves as
+// staging area, mark buffer and destination rows in turn.  Global scratch: the survivor lists (L2 traffic
+// proportional to the clauses that are still true).
 #include "../../include/gtm_b200.h"
 
 #include <cuda_runtime.h>
@@ -48,9 +49,10 @@ __device__ __forceinline__ const u32 *include_plane(const DevModel &m, int layer
                       : m.tam + (((size_t)(layer - 1) * m.C + c) * m.SB + (m.SB - 1)) * m.M;
 }
 
-// cnt[2c] / cnt[2c+1]: literals of clause c that are tested as they are / complemented, padded to multiples of 4.
+// Included literals of a clause layer, counted in groups of four: those tested as they are / complemented.
 // Layer 0 has both polarities of a feature as literals of its own (graphs.py:150-159), so nothing is complemented;
 // a message layer's literal l >= MS is the complement of message bit l - MS (kernels.py:544-545).
+// cnt[c] = plain groups | complemented groups << 16.
 __global__ void tile_count_kernel(DevModel m, int layer, int *cnt)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -70,36 +72,44 @@ __global__ void tile_count_kernel(DevModel m, int layer, int *cnt)
             negated += __popc(bits >> split);
         }
     }
-    cnt[2 * c] = (plain + 3) & ~3;
-    cnt[2 * c + 1] = (negated + 3) & ~3;
+    cnt[c] = ((plain + 3) >> 2) | (((negated + 3) >> 2) << 16);
 }
 
-// Exclusive scan of cnt[0..n) into off[0..n], one block.
-__global__ void tile_scan_kernel(const int *cnt, int *off, int n, int *total_out)
+// The lists of 32 consecutive clauses are stored interleaved - group g of the block's clause l is the 8-byte element
+// blk_off[block] + 32*g + l - so that a warp whose lanes hold those clauses fetches group g of all of them with one
+// coalesced 256-byte load.  A block takes 32 * (its longest list) elements.  One CUDA block computes all offsets.
+__global__ void tile_block_offsets_kernel(const int *cnt, int C, int *blk_off, int *total_out)
 {
     __shared__ int s_part[1024];
-    const int per = (n + blockDim.x - 1) / blockDim.x;
-    const int lo = min(n, (int)threadIdx.x * per), hi = min(n, lo + per);
+    const int nblk = (C + 31) >> 5;
+    const int per = (nblk + blockDim.x - 1) / blockDim.x;
+    const int lo = min(nblk, (int)threadIdx.x * per), hi = min(nblk, lo + per);
+    auto block_len = [&](int b) {
+        int longest = 0;
+        for (int c = 32 * b; c < min(C, 32 * b + 32); ++c) longest = max(longest, (cnt[c] & 0xffff) + (cnt[c] >> 16));
+        return 32 * longest;
+    };
     int sum = 0;
-    for (int i = lo; i < hi; ++i) sum += cnt[i];
+    for (int b = lo; b < hi; ++b) sum += block_len(b);
     s_part[threadIdx.x] = sum;
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
         for (int t = 0; t < (int)blockDim.x; ++t) { const int v = s_part[t]; s_part[t] = run; run += v; }
-        off[n] = run;
+        blk_off[nblk] = run;
         *total_out = run;
     }
     __syncthreads();
     int run = s_part[threadIdx.x];
-    for (int i = lo; i < hi; ++i) { off[i] = run; run += cnt[i]; }
+    for (int b = lo; b < hi; ++b) { blk_off[b] = run; run += block_len(b); }
 }
 
 // Row of literal bit p in the transposed buffer whose source rows have W words: bit b of word w lives in row b*W + w
 // (so that the threads that transpose adjacent words write adjacent rows); rows 32*W and 32*W+1 are all ones / zeros.
 __device__ __forceinline__ unsigned short tile_row(int p, int W) { return (unsigned short)((p & 31) * W + (p >> 5)); }
 
-__global__ void tile_fill_kernel(DevModel m, int layer, const int *off, unsigned short *list, int *Wt, int KROW, u32 *hvm)
+__global__ void tile_fill_kernel(DevModel m, int layer, const int *cnt, const int *blk_off, unsigned short *list, int *Wt,
+                                 int KROW, u32 *hvm)
 {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= m.C) return;
@@ -107,18 +117,22 @@ __global__ void tile_fill_kernel(DevModel m, int layer, const int *off, unsigned
     const int WS = layer == 0 ? m.L0 : m.MW;           // words of a source row (literal row / positive message bits)
     const u32 last = layer == 0 ? m.lit_mask : m.msg_mask;
     const u32 *inc = include_plane(m, layer, c);
-    int at_plain = off[2 * c], at_neg = off[2 * c + 1];
+    const int n_plain = cnt[c] & 0xffff, n_neg = cnt[c] >> 16;
+    // entry e (four per group) of this clause's list: element blk_off + 32*(e/4) + lane, slot e%4
+    unsigned short *base = list + ((size_t)blk_off[c >> 5] + (c & 31)) * 4;
+    auto slot = [&](int e) -> unsigned short & { return base[(size_t)(e >> 2) * 128 + (e & 3)]; };
+    int at_plain = 0, at_neg = 4 * n_plain;
     for (int w = 0; w < W; ++w) {
         u32 bits = inc[w] & (w == W - 1 ? last : kFull);
         while (bits) {
             const int l = 32 * w + __ffs(bits) - 1;
             bits &= bits - 1;
-            if (layer == 0 || l < m.MS) list[at_plain++] = tile_row(l, WS);
-            else list[at_neg++] = tile_row(l - m.MS, WS);
+            if (layer == 0 || l < m.MS) slot(at_plain++) = tile_row(l, WS);
+            else slot(at_neg++) = tile_row(l - m.MS, WS);
         }
     }
-    while (at_plain < off[2 * c + 1]) list[at_plain++] = (unsigned short)(32 * WS);        // all ones: no effect on an AND
-    while (at_neg < off[2 * c + 2]) list[at_neg++] = (unsigned short)(32 * WS + 1);        // all zeros: no effect when complemented
+    while (at_plain < 4 * n_plain) slot(at_plain++) = (unsigned short)(32 * WS);             // all ones: no effect on an AND
+    while (at_neg < 4 * (n_plain + n_neg)) slot(at_neg++) = (unsigned short)(32 * WS + 1);   // all zeros: no effect when complemented
     if (layer == 0) {
         for (int k = 0; k < KROW; ++k) Wt[(size_t)c * KROW + k] = k < m.K ? m.weights[(size_t)k * m.C + c] : 0;
         for (int b = 0; b < m.MB; ++b) hvm[(size_t)c * m.MB + b] = m.hv[(size_t)c * m.MB + b] % (u32)m.MS;
@@ -141,8 +155,8 @@ struct TileArgs {
     const int *Wt;
     int KROW;
     const u32 *hvm;
-    int *surv_c;                        // [grid][2][Q][C]
-    uint4 *surv_r;
+    int *surv_c;                        // [grid][2][quad pairs][C] clauses still true after a layer ...
+    uint4 *surv_r;                      // ... and their node bits on the pair's two quads
     int *error;                         // raised (2) when the wait for a bulk copy gave up
 };
 
@@ -191,33 +205,45 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity)
     }
 }
 
-// Node bits of a clause on one quad after ANDing the rows of its included literals (plain, then complemented).
-// tq: shared address of the quad's first word in row 0; a row is `1 << rowshift` bytes.
-__device__ __forceinline__ uint4 tile_eval(uint4 r, const TileLayer &L, int c, unsigned tq, int rowshift)
+// Node bits of a clause on a PAIR of quads after ANDing the rows of its included literals: `plain` groups of four rows
+// as they are, then `negated` groups complemented.  lp: the clause's first list element (elements of one clause are 32
+// apart, see tile_block_offsets_kernel); tq: shared address of the first quad's words in row 0 (the second quad's
+// follow 16 bytes later); a row is `1 << rowshift` bytes.  `two`: the second quad exists (warp-uniform).
+__device__ __forceinline__ void tile_eval(uint4 &ra, uint4 &rb, const uint2 *lp, int plain, int negated, unsigned tq,
+                                          int rowshift, bool two)
 {
-    const int o0 = L.off[2 * c] >> 2, o1 = L.off[2 * c + 1] >> 2, o2 = L.off[2 * c + 2] >> 2;
-    const uint2 *lp = reinterpret_cast<const uint2 *>(L.list);       // four 16-bit row numbers per load
-    for (int q = o0; q < o1; ++q) {
-        if ((r.x | r.y | r.z | r.w) == 0) return r;
-        const uint2 four = __ldg(lp + q);
-        const uint4 x0 = tile_lds128(tq + ((four.x & 0xffffu) << rowshift));
-        const uint4 x1 = tile_lds128(tq + ((four.x >> 16) << rowshift));
-        const uint4 x2 = tile_lds128(tq + ((four.y & 0xffffu) << rowshift));
-        const uint4 x3 = tile_lds128(tq + ((four.y >> 16) << rowshift));
-        r.x &= x0.x & x1.x; r.y &= x0.y & x1.y; r.z &= x0.z & x1.z; r.w &= x0.w & x1.w;
-        r.x &= x2.x & x3.x; r.y &= x2.y & x3.y; r.z &= x2.z & x3.z; r.w &= x2.w & x3.w;
+    for (int gI = 0; gI < plain; ++gI) {
+        if ((ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) == 0) return;
+        const uint2 four = __ldg(lp + 32 * gI);
+        const unsigned o0 = tq + ((four.x & 0xffffu) << rowshift), o1 = tq + ((four.x >> 16) << rowshift),
+                       o2 = tq + ((four.y & 0xffffu) << rowshift), o3 = tq + ((four.y >> 16) << rowshift);
+        {
+            const uint4 x0 = tile_lds128(o0), x1 = tile_lds128(o1), x2 = tile_lds128(o2), x3 = tile_lds128(o3);
+            ra.x &= x0.x & x1.x; ra.y &= x0.y & x1.y; ra.z &= x0.z & x1.z; ra.w &= x0.w & x1.w;
+            ra.x &= x2.x & x3.x; ra.y &= x2.y & x3.y; ra.z &= x2.z & x3.z; ra.w &= x2.w & x3.w;
+        }
+        if (two) {
+            const uint4 x0 = tile_lds128(o0 + 16), x1 = tile_lds128(o1 + 16), x2 = tile_lds128(o2 + 16), x3 = tile_lds128(o3 + 16);
+            rb.x &= x0.x & x1.x; rb.y &= x0.y & x1.y; rb.z &= x0.z & x1.z; rb.w &= x0.w & x1.w;
+            rb.x &= x2.x & x3.x; rb.y &= x2.y & x3.y; rb.z &= x2.z & x3.z; rb.w &= x2.w & x3.w;
+        }
     }
-    for (int q = o1; q < o2; ++q) {
-        if ((r.x | r.y | r.z | r.w) == 0) return r;
-        const uint2 four = __ldg(lp + q);
-        const uint4 x0 = tile_lds128(tq + ((four.x & 0xffffu) << rowshift));
-        const uint4 x1 = tile_lds128(tq + ((four.x >> 16) << rowshift));
-        const uint4 x2 = tile_lds128(tq + ((four.y & 0xffffu) << rowshift));
-        const uint4 x3 = tile_lds128(tq + ((four.y >> 16) << rowshift));
-        r.x &= ~(x0.x | x1.x); r.y &= ~(x0.y | x1.y); r.z &= ~(x0.z | x1.z); r.w &= ~(x0.w | x1.w);
-        r.x &= ~(x2.x | x3.x); r.y &= ~(x2.y | x3.y); r.z &= ~(x2.z | x3.z); r.w &= ~(x2.w | x3.w);
+    for (int gI = plain; gI < plain + negated; ++gI) {
+        if ((ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) == 0) return;
+        const uint2 four = __ldg(lp + 32 * gI);
+        const unsigned o0 = tq + ((four.x & 0xffffu) << rowshift), o1 = tq + ((four.x >> 16) << rowshift),
+                       o2 = tq + ((four.y & 0xffffu) << rowshift), o3 = tq + ((four.y >> 16) << rowshift);
+        {
+            const uint4 x0 = tile_lds128(o0), x1 = tile_lds128(o1), x2 = tile_lds128(o2), x3 = tile_lds128(o3);
+            ra.x &= ~(x0.x | x1.x); ra.y &= ~(x0.y | x1.y); ra.z &= ~(x0.z | x1.z); ra.w &= ~(x0.w | x1.w);
+            ra.x &= ~(x2.x | x3.x); ra.y &= ~(x2.y | x3.y); ra.z &= ~(x2.z | x3.z); ra.w &= ~(x2.w | x3.w);
+        }
+        if (two) {
+            const uint4 x0 = tile_lds128(o0 + 16), x1 = tile_lds128(o1 + 16), x2 = tile_lds128(o2 + 16), x3 = tile_lds128(o3 + 16);
+            rb.x &= ~(x0.x | x1.x); rb.y &= ~(x0.y | x1.y); rb.z &= ~(x0.z | x1.z); rb.w &= ~(x0.w | x1.w);
+            rb.x &= ~(x2.x | x3.x); rb.y &= ~(x2.y | x3.y); rb.z &= ~(x2.z | x3.z); rb.w &= ~(x2.w | x3.w);
+        }
     }
-    return r;
 }
 
 // Bits [lo, lo+n) of a 128-bit quad.
@@ -254,8 +280,8 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
     unsigned char *pflag = gquad + ((a.gmax + 3) & ~3);             // [TN] slot's message row has bits
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kTileThreads / 32;
     const unsigned bar = smem_u32(mbar_mem);
-    int *surv_c = a.surv_c + (size_t)blockIdx.x * 2 * Q * m.C;
-    uint4 *surv_r = a.surv_r + (size_t)blockIdx.x * 2 * Q * m.C;
+    int *surv_c = a.surv_c + (size_t)blockIdx.x * 2 * ((Q + 1) >> 1) * m.C;          // [2][quad pairs][C]
+    uint4 *surv_r = a.surv_r + (size_t)blockIdx.x * 4 * ((Q + 1) >> 1) * m.C;        // two quads per entry
     const size_t x_words = (size_t)g.total_nodes * m.L0;
 
     if (tid == 0) mbar_init(bar, 1);
@@ -347,50 +373,76 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
             }
         }
         if (m.D > 1)
-            for (int i = tid; i < TN * PS; i += kTileThreads) bufB[i] = 0u;
+            for (int i = tid; i < 32 * m.MW * TNC; i += kTileThreads) bufB[i] = 0u;
         __syncthreads();
 
         // ---- layers ----
-        u32 *T = bufA, *Pm = bufB;
+        // bufA always holds the literal rows of the current layer (the transposed literals, then the transposed
+        // messages); bufB takes, in turn, the message bits that the layer's true clauses mark on their nodes (bit-major,
+        // the layout of the literal rows) and the node-major destination rows of the edge pass.
+        const int U = (Q + 1) >> 1;                   // quad pairs: a thread evaluates a clause on two quads at a time
+        const unsigned t32 = smem_u32(bufA);
         for (int d = 0; d < m.D; ++d) {
             const bool last = d == m.D - 1;
             const TileLayer L = a.layers[d];
             const int wr = d & 1, rd = wr ^ 1;        // survivor list written by this layer / read by it
-            const unsigned t32 = smem_u32(T);
 
-            // one warp pass: lanes hold (clause, node bits on quad q) before the layer; evaluates and hands the result on
-            auto pass = [&](int c, uint4 r, int q) {
-                if (c >= 0) r = tile_eval(r, L, c, t32 + q * 16, rowshift);
-                const bool alive = (r.x | r.y | r.z | r.w) != 0;
+            // OR of node bits r into row `dst` (four words of one quad) of the mark buffer; most bits are there already
+            auto mark = [&](u32 *dst, const uint4 r) {
+                const uint4 old = tile_lds128(smem_u32(dst));
+                if (r.x & ~old.x) atomicOr(dst, r.x);
+                if (r.y & ~old.y) atomicOr(dst + 1, r.y);
+                if (r.z & ~old.z) atomicOr(dst + 2, r.z);
+                if (r.w & ~old.w) atomicOr(dst + 3, r.w);
+            };
+            // votes of one quad: per graph, the weights of the lanes that fired, summed over the warp
+            auto vote = [&](int q, const uint4 r, const int (&w)[KP]) {
+                const u32 ax = __reduce_or_sync(kFull, r.x), ay = __reduce_or_sync(kFull, r.y),
+                          az = __reduce_or_sync(kFull, r.z), aw = __reduce_or_sync(kFull, r.w);
+                if ((ax | ay | az | aw) == 0) return;
+                for (int gl = gq_first[q]; gl < gq_first[q + 1]; ++gl) {
+                    const uint4 gm = gmask[gl];
+                    if (((ax & gm.x) | (ay & gm.y) | (az & gm.z) | (aw & gm.w)) == 0) continue;    // nobody fired on this graph
+                    const bool f = ((r.x & gm.x) | (r.y & gm.y) | (r.z & gm.z) | (r.w & gm.w)) != 0;
+                    int mine = 0;
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) {
+                        const int sk = __reduce_add_sync(kFull, f ? w[k] : 0);
+                        if (lane == k) mine = sk;
+                    }
+                    if (lane < m.K) atomicAdd(&sums[gl * KP + lane], mine);
+                }
+            };
+            // one warp pass: lanes hold (clause, node bits on the quads of pair u) as they were before the layer
+            auto pass = [&](int c, uint4 ra, uint4 rb, int u) {
+                const int qa = 2 * u;
+                const bool two = qa + 1 < Q;
+                if (c >= 0) {
+                    const int packed = L.cnt[c];
+                    tile_eval(ra, rb, reinterpret_cast<const uint2 *>(L.list) + L.blk_off[c >> 5] + (c & 31), packed & 0xffff,
+                              packed >> 16, t32 + qa * 16, rowshift, two);
+                }
+                const bool alive = (ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) != 0;
                 const u32 amask = __ballot_sync(kFull, alive);
                 if (amask == 0) return;
                 if (!last) {
                     int base = 0;
-                    if (lane == 0) base = atomicAdd(&cnt[wr * 8 + q], __popc(amask));
+                    if (lane == 0) base = atomicAdd(&cnt[wr * 8 + u], __popc(amask));
                     base = __shfl_sync(kFull, base, 0);
                     if (alive) {
-                        const size_t at = (size_t)(wr * Q + q) * m.C + base + __popc(amask & ((1u << lane) - 1u));
+                        const size_t at = (size_t)(wr * U + u) * m.C + base + __popc(amask & ((1u << lane) - 1u));
                         surv_c[at] = c;
-                        surv_r[at] = r;
-                        // the clause's hypervector bits on every node it is true on (the SOURCE side of kernels.py:571-588)
-                        const u32 wd[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) {
-                            u32 bits = wd[wi];
-                            while (bits) {
-                                const int slot = q * kQuadNodes + wi * 32 + __ffs(bits) - 1;
-                                bits &= bits - 1;
-                                u32 *row = Pm + (size_t)slot * PS;
-                                for (int b = 0; b < m.MB; ++b) {
-                                    const u32 bit = a.hvm[(size_t)c * m.MB + b];
-                                    const u32 mbit = 1u << (bit & 31);
-                                    if (!(*(volatile u32 *)(row + (bit >> 5)) & mbit)) atomicOr(row + (bit >> 5), mbit);
-                                }
-                            }
+                        surv_r[2 * at] = ra;
+                        surv_r[2 * at + 1] = rb;
+                        // the clause's hypervector bits on every node it is true on (the SOURCE side of kernels.py:571-588):
+                        // in the bit-major buffer that is one 128-bit OR per hypervector bit and quad
+                        for (int b = 0; b < m.MB; ++b) {
+                            u32 *row = bufB + (size_t)tile_row((int)a.hvm[(size_t)c * m.MB + b], m.MW) * TNC + 4 * qa;
+                            mark(row, ra);
+                            if (two) mark(row + 4, rb);
                         }
                     }
                 } else {
-                    // votes: per graph of the quad, the weights of the lanes that fired, summed over the warp
                     int w[KP];
 #pragma unroll
                     for (int k = 0; k < KP; ++k) w[k] = 0;
@@ -405,45 +457,37 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                             if (4 * k4 + 3 < KP) w[4 * k4 + 3] = t.w;
                         }
                     }
-                    const u32 ax = __reduce_or_sync(kFull, r.x), ay = __reduce_or_sync(kFull, r.y),
-                              az = __reduce_or_sync(kFull, r.z), aw = __reduce_or_sync(kFull, r.w);
-                    for (int gl = gq_first[q]; gl < gq_first[q + 1]; ++gl) {
-                        const uint4 gm = gmask[gl];
-                        if (((ax & gm.x) | (ay & gm.y) | (az & gm.z) | (aw & gm.w)) == 0) continue;    // nobody fired on this graph
-                        const bool f = ((r.x & gm.x) | (r.y & gm.y) | (r.z & gm.z) | (r.w & gm.w)) != 0;
-                        int mine = 0;
-#pragma unroll
-                        for (int k = 0; k < KP; ++k) {
-                            const int s = __reduce_add_sync(kFull, f ? w[k] : 0);
-                            if (lane == k) mine = s;
-                        }
-                        if (lane < m.K) atomicAdd(&sums[gl * KP + lane], mine);
-                    }
+                    vote(qa, ra, w);
+                    if (two) vote(qa + 1, rb, w);
                 }
             };
 
             if (d == 0) {
                 const int cblocks = (m.C + 31) >> 5;
-                for (int task = warp; task < cblocks * Q; task += nwarps) {
-                    const int q = task % Q;
-                    int c = (task / Q) * 32 + lane;
-                    uint4 r = make_uint4(0u, 0u, 0u, 0u);
-                    if (c < m.C) r = *reinterpret_cast<const uint4 *>(TMV + (c % g.n_types) * TNC + 4 * q);
-                    else c = -1;
-                    pass(c, r, q);
+                for (int task = warp; task < cblocks * U; task += nwarps) {
+                    const int u = task % U;
+                    int c = (task / U) * 32 + lane;
+                    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+                    if (c < m.C) {
+                        const u32 *tm_row = TMV + (c % g.n_types) * TNC + 8 * u;
+                        ra = *reinterpret_cast<const uint4 *>(tm_row);
+                        if (2 * u + 1 < Q) rb = *reinterpret_cast<const uint4 *>(tm_row + 4);
+                    } else c = -1;
+                    pass(c, ra, rb, u);
                 }
             } else {
-                for (int q = 0; q < Q; ++q) {
-                    const int n_ent = cnt[rd * 8 + q];
+                for (int u = 0; u < U; ++u) {
+                    const int n_ent = cnt[rd * 8 + u];
                     for (int base = warp * 32; base < n_ent; base += nwarps * 32) {
                         int c = -1;
-                        uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                        uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
                         if (base + lane < n_ent) {
-                            const size_t at = (size_t)(rd * Q + q) * m.C + base + lane;
+                            const size_t at = (size_t)(rd * U + u) * m.C + base + lane;
                             c = surv_c[at];
-                            r = surv_r[at];
+                            ra = surv_r[2 * at];
+                            rb = surv_r[2 * at + 1];
                         }
-                        pass(c, r, q);
+                        pass(c, ra, rb, u);
                     }
                 }
             }
@@ -452,54 +496,68 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
 
             // ---- messages of this layer -> literal rows of the next ----
             int survivors = 0;
-            for (int q = 0; q < Q; ++q) survivors += cnt[wr * 8 + q];
+            for (int u = 0; u < U; ++u) survivors += cnt[wr * 8 + u];
             if (survivors == 0) break;                // no clause is true anywhere: nothing can fire in later layers
-            u32 *Pdst = T;                            // the literal rows are no longer needed
-            for (int i = tid; i < TN * PS; i += kTileThreads) Pdst[i] = 0u;
-            for (int u = tid; u < TN; u += kTileThreads) {
-                u32 any = 0;
-                if (tnode[u] != ~0u)
-                    for (int w = 0; w < m.MW; ++w) any |= Pm[(size_t)u * PS + w];
-                pflag[u] = any != 0;
-            }
-            if (tid < 8) cnt[rd * 8 + tid] = 0;      // the list the next layer writes
-            __syncthreads();
-            for (int i = tid; i < TN * m.MW; i += kTileThreads) {
-                const int u = i / m.MW, w = i - u * m.MW;
-                if (!pflag[u]) continue;              // a source row without bits sends nothing
-                const u32 nd = tnode[u], info = pinfo[u];
-                const u32 base = info & 0xffffu, n = info >> 16;
-                const u32 deg = g.degree[nd], e0 = g.edge_index[nd];
-                const u32 *row = Pm + (size_t)u * PS;
-                for (u32 k = 0; k < deg && e0 + k < g.total_edges; ++k) {
-                    const u32 dst = g.edge[2 * (size_t)(e0 + k)], ty = g.edge[2 * (size_t)(e0 + k) + 1];
-                    if (dst >= n) continue;           // malformed edge: ignore, never fault
-                    const u32 val = rotated_word(row, w, ty >= (u32)m.MS ? ty % (u32)m.MS : ty, m.MS, m.MW);
-                    if (val) atomicOr(&Pdst[(size_t)(base + dst) * PS + w], val);
-                }
-            }
-            __syncthreads();
-            u32 *PT = Pm;                             // the source rows are no longer needed
+            // (1) marked bits, bit-major in bufB -> node-major source rows in bufA (its literal rows are no longer needed)
             for (int blk = tid; blk < TNC * m.MW; blk += kTileThreads) {
                 const int j = blk % TNC, w = blk / TNC, rot = (a.rot_step * j) & 31;
                 u32 rows[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) rows[i] = Pdst[(size_t)(32 * j + ((i + rot) & 31)) * PS + w];
-                transpose32(rows);
+                for (int b = 0; b < 32; ++b) {
+                    const u32 x = bufB[(size_t)(b * m.MW + w) * TNC + j];
+                    rows[b] = __funnelshift_r(x, x, rot);
+                }
+                transpose32(rows);                    // rows[i] = word w of the node in slot 32j + ((i + rot) & 31)
 #pragma unroll
-                for (int b = 0; b < 32; ++b) PT[(size_t)(b * m.MW + w) * TNC + j] = __funnelshift_l(rows[b], rows[b], rot);
+                for (int i = 0; i < 32; ++i) bufA[(size_t)(32 * j + ((i + rot) & 31)) * PS + w] = rows[i];
             }
-            for (int j = tid; j < TNC; j += kTileThreads) {
-                PT[(size_t)(32 * m.MW) * TNC + j] = kFull;
-                PT[(size_t)(32 * m.MW + 1) * TNC + j] = 0u;
+            if (tid < 8) cnt[rd * 8 + tid] = 0;      // the list the next layer writes
+            __syncthreads();
+            // (2) destination rows start empty; source rows without bits are skipped by the edge pass
+            for (int i = tid; i < TN * PS; i += kTileThreads) bufB[i] = 0u;
+            for (int u = tid; u < TN; u += kTileThreads) {
+                u32 any = 0;
+                if (tnode[u] != ~0u)
+                    for (int w = 0; w < m.MW; ++w) any |= bufA[(size_t)u * PS + w];
+                pflag[u] = any != 0;
             }
             __syncthreads();
-            if (d + 1 < m.D - 1) {                    // the next layer sends messages too: its marks go where Pdst was
-                for (int i = tid; i < TN * PS; i += kTileThreads) Pdst[i] = 0u;
+            // (3) edge pass: a node's bits arrive at the destination rotated by the edge type (kernels.py:581)
+            for (int i = tid; i < TN * m.MW; i += kTileThreads) {
+                const int u = i / m.MW, w = i - u * m.MW;
+                if (!pflag[u]) continue;
+                const u32 nd = tnode[u], info = pinfo[u];
+                const u32 base = info & 0xffffu, n = info >> 16;
+                const u32 deg = g.degree[nd], e0 = g.edge_index[nd];
+                const u32 *row = bufA + (size_t)u * PS;
+                for (u32 k = 0; k < deg && e0 + k < g.total_edges; ++k) {
+                    const u32 dst = g.edge[2 * (size_t)(e0 + k)], ty = g.edge[2 * (size_t)(e0 + k) + 1];
+                    if (dst >= n) continue;           // malformed edge: ignore, never fault
+                    const u32 val = rotated_word(row, w, ty >= (u32)m.MS ? ty % (u32)m.MS : ty, m.MS, m.MW);
+                    if (val) atomicOr(&bufB[(size_t)(base + dst) * PS + w], val);
+                }
+            }
+            __syncthreads();
+            // (4) destination rows, node-major in bufB -> literal rows of the next layer, bit-major in bufA
+            for (int blk = tid; blk < TNC * m.MW; blk += kTileThreads) {
+                const int j = blk % TNC, w = blk / TNC, rot = (a.rot_step * j) & 31;
+                u32 rows[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rows[i] = bufB[(size_t)(32 * j + ((i + rot) & 31)) * PS + w];
+                transpose32(rows);
+#pragma unroll
+                for (int b = 0; b < 32; ++b) bufA[(size_t)(b * m.MW + w) * TNC + j] = __funnelshift_l(rows[b], rows[b], rot);
+            }
+            for (int j = tid; j < TNC; j += kTileThreads) {
+                bufA[(size_t)(32 * m.MW) * TNC + j] = kFull;
+                bufA[(size_t)(32 * m.MW + 1) * TNC + j] = 0u;
+            }
+            __syncthreads();
+            // (5) bufB is the mark buffer of the next layer, if that one sends messages too
+            if (d + 1 < m.D - 1) {
+                for (int i = tid; i < 32 * m.MW * TNC; i += kTileThreads) bufB[i] = 0u;
                 __syncthreads();
             }
-            T = PT;
-            Pm = Pdst;
         }
 
         // ---- class sums of the tile's graphs (only those inside the requested range) ----
@@ -537,11 +595,13 @@ int tile_model_create(TileModel *tm, const DevModel &d)
     if (d.K > kTileMaxK) return GTM_OK;
     if (32 * (size_t)std::max(d.L0, d.D > 1 ? d.MW : 0) + 2 > 65535) return GTM_OK;     // row numbers are 16 bits
     tm->KROW = tile_krow(d.K);
-    GTM_TRY(dev_alloc(&tm->cnt, 2 * (size_t)d.C));
     GTM_TRY(dev_alloc(&tm->Wt, (size_t)d.C * tm->KROW));
     GTM_TRY(dev_alloc(&tm->hvm, (size_t)d.C * d.MB));
     GTM_TRY(dev_alloc(&tm->layers, (size_t)d.D));
-    for (int l = 0; l < d.D; ++l) GTM_TRY(dev_alloc(&tm->off[l], 2 * (size_t)d.C + 1));
+    for (int l = 0; l < d.D; ++l) {
+        GTM_TRY(dev_alloc(&tm->cnt[l], (size_t)d.C));
+        GTM_TRY(dev_alloc(&tm->blk_off[l], (size_t)((d.C + 31) / 32) + 1));
+    }
     GTM_CU(cudaMallocHost((void **)&tm->total_host, sizeof(int)));
     tm->applicable = true;
     return GTM_OK;
@@ -549,8 +609,8 @@ int tile_model_create(TileModel *tm, const DevModel &d)
 
 void tile_model_destroy(TileModel *tm)
 {
-    cudaFree(tm->cnt); cudaFree(tm->Wt); cudaFree(tm->hvm); cudaFree(tm->layers);
-    for (int l = 0; l < kMaxDepth; ++l) { cudaFree(tm->off[l]); cudaFree(tm->list[l]); }
+    cudaFree(tm->Wt); cudaFree(tm->hvm); cudaFree(tm->layers);
+    for (int l = 0; l < kMaxDepth; ++l) { cudaFree(tm->cnt[l]); cudaFree(tm->blk_off[l]); cudaFree(tm->list[l]); }
     if (tm->total_host) cudaFreeHost(tm->total_host);
     *tm = TileModel();
 }
@@ -563,11 +623,11 @@ int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s)
     const int blocks = (d.C + 255) / 256;
     TileLayer host_layers[kMaxDepth];
     for (int l = 0; l < d.D; ++l) {
-        tile_count_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt);
-        tile_scan_kernel<<<1, 1024, 0, s>>>(tm->cnt, tm->off[l], 2 * d.C, tm->total_host);
+        tile_count_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt[l]);
+        tile_block_offsets_kernel<<<1, 1024, 0, s>>>(tm->cnt[l], d.C, tm->blk_off[l], tm->total_host);
         GTM_CU(cudaGetLastError());
         GTM_CU(cudaStreamSynchronize(s));
-        const size_t need = (size_t)*tm->total_host + 8;
+        const size_t need = 4 * (size_t)*tm->total_host + 8;          // 16-bit row numbers, four per element
         if (need > tm->list_cap[l]) {
             cudaFree(tm->list[l]);
             tm->list[l] = nullptr;
@@ -576,9 +636,10 @@ int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s)
             GTM_TRY(dev_alloc(&tm->list[l], cap));
             tm->list_cap[l] = cap;
         }
-        tile_fill_kernel<<<blocks, 256, 0, s>>>(d, l, tm->off[l], tm->list[l], tm->Wt, tm->KROW, tm->hvm);
+        tile_fill_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt[l], tm->blk_off[l], tm->list[l], tm->Wt, tm->KROW, tm->hvm);
         GTM_CU(cudaGetLastError());
-        host_layers[l].off = tm->off[l];
+        host_layers[l].cnt = tm->cnt[l];
+        host_layers[l].blk_off = tm->blk_off[l];
         host_layers[l].list = tm->list[l];
     }
     GTM_CU(cudaMemcpyAsync(tm->layers, host_layers, (size_t)d.D * sizeof(TileLayer), cudaMemcpyHostToDevice, s));
@@ -595,6 +656,7 @@ static TilePlan tile_plan(const DevModel &d, int TNC, int gmax)
     const int TN = TNC * 32;
     p.PS = d.MW | 1;
     const size_t xt = (size_t)(32 * d.L0 + 2) * TNC;
+    // node-major message rows / bit-major message rows (+ the all-ones and all-zeros rows)
     const size_t pm = d.D > 1 ? (size_t)TN * p.PS : 0, pt = d.D > 1 ? (size_t)(32 * d.MW + 2) * TNC : 0;
     // staging: whole groups of 32 literal rows, up to 16 KB (or whatever the message rows need anyway), + 8 words of slack
     size_t stage = (size_t)32 * d.L0 * std::max<size_t>(1, std::min<size_t>(TNC, 4096 / ((size_t)32 * d.L0))) + 8;
@@ -707,11 +769,11 @@ bool tile_supported(const TileData &td, int n_types) { return td.supported != 0 
 int tile_score(const TileModel &tm, TileData &td, const DevModel &d, const DevGraphs &dg, int n_types, int64_t first,
                int64_t count, int *sums_dev, int *error_dev, cudaStream_t s)
 {
-    const int Q = td.TNC / 4;
+    const int U = (td.TNC / 4 + 1) / 2;
     if (!td.surv_c) {          // survivor lists: one pair per resident CTA, allocated on first use
-        const size_t entries = (size_t)td.grid * 2 * Q * d.C;
+        const size_t entries = (size_t)td.grid * 2 * U * d.C;
         GTM_TRY(pool_alloc(&td.surv_c, entries, s));
-        GTM_TRY(pool_alloc(&td.surv_r, entries, s));
+        GTM_TRY(pool_alloc(&td.surv_r, 2 * entries, s));
     }
     DevGraphs g = dg;
     g.n_types = n_types;

@@ -8,20 +8,21 @@
 
 namespace gtm {
 
-// One layer's included-literal lists as the kernel reads them (device memory).
+// One layer's included-literal lists as the kernel reads them (device memory).  The lists of 32 consecutive clauses
+// are interleaved: group g (four 16-bit row numbers, 8 bytes) of clause c is element blk_off[c / 32] + 32 * g + c % 32.
 struct TileLayer {
-    const int *off;               // [2C+1] multiples of 4: clause c tests rows list[off[2c] .. off[2c+1]) as they are and
-                                  //        rows list[off[2c+1] .. off[2c+2]) complemented (negated message literals)
+    const int *cnt;               // [C] groups tested as they are | groups tested complemented << 16 (negated message literals)
+    const int *blk_off;           // [ceil(C/32)+1] first element of every block of 32 clauses
     const unsigned short *list;   // row numbers in the transposed tile buffer, padded with the all-ones / all-zeros row
 };
 
 struct TileModel {
     bool applicable = false;
     int D = 0, KROW = 0;
-    int *off[kMaxDepth] = {};
+    int *cnt[kMaxDepth] = {};
+    int *blk_off[kMaxDepth] = {};
     unsigned short *list[kMaxDepth] = {};
     size_t list_cap[kMaxDepth] = {};
-    int *cnt = nullptr;           // [2C] scratch of the scan
     int *Wt = nullptr;            // [C][KROW] weights, clause-major
     u32 *hvm = nullptr;           // [C][MB] hypervector bits reduced modulo the message size
     TileLayer *layers = nullptr;  // [D] device copy of the pointers above
@@ -42,8 +43,8 @@ struct TileData {
     unsigned short *gpos = nullptr;     // [N] first node slot of every graph inside its tile (NULL for uniform sets)
     std::vector<int> tile_graph_host;
     unsigned *tile_counter = nullptr;
-    int *surv_c = nullptr;              // [grid][2][Q][C] clauses still true after a layer ...
-    uint4 *surv_r = nullptr;            //                 ... and their node bits on the quad
+    int *surv_c = nullptr;              // [grid][2][quad pairs][C] clauses still true after a layer ...
+    uint4 *surv_r = nullptr;            //                          ... and their node bits on the pair's two quads
     cudaStream_t stream = nullptr;
     int grid = 0;
     size_t smem = 0;

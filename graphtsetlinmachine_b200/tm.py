@@ -366,15 +366,8 @@ class CommonTsetlinMachine:
         n_max = int(np.max(graphs.number_of_graph_nodes))
         class_sum = np.zeros((graphs.number_of_graphs, self.number_of_outputs), dtype=np.int32)
         transformed_X = np.zeros((graphs.number_of_graphs, self.number_of_clauses, n_max), dtype=np.int32)
-        nt = int(graphs.number_of_node_types())
-        for e in range(graphs.number_of_graphs):
-            n = int(graphs.number_of_graph_nodes[e])
-            words = (n - 1) // 32 + 1
-            cno = np.zeros((self.depth, self.number_of_clauses, words), dtype=np.uint32)
-            _lib.check(self._lib.gtm_debug_evaluate(self._model, self._test_set.handle, nt, e, 0, _ptr(cno), None, None,
-                                                    _ptr(class_sum[e])))
-            bits = np.unpackbits(cno[self.depth - 1].view(np.uint8), axis=1, bitorder="little")[:, :n]
-            transformed_X[e, :, :n] = bits
+        _lib.check(self._lib.gtm_transform_nodewise(self._model, self._test_set.handle, int(graphs.number_of_node_types()),
+                                                    0, int(graphs.number_of_graphs), n_max, _ptr(transformed_X), _ptr(class_sum)))
         return transformed_X, class_sum
 
     # ---------------------------------------------------------------------------------------- introspection

@@ -210,6 +210,12 @@ int gtm_shard_connect(gtm_model *model, gtm_dataset *dataset, const unsigned cha
 int gtm_transform(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
                   int32_t *clause_outputs_out, int32_t *class_sums_out);
 
+/* Replaces tm.py:853-900 (transform_nodewise; kernels.py:693-709): per-node clause outputs of the last layer,
+ * int32[count][CLAUSES][node_stride] (0/1; entries beyond a graph's node count are 0), node_stride >= the largest
+ * graph's node count, and the class sums (may be NULL).  One launch for the whole range. */
+int gtm_transform_nodewise(gtm_model *model, gtm_dataset *dataset, int number_of_node_types, int64_t first, int64_t count,
+                           int node_stride, int32_t *node_outputs_out, int32_t *class_sums_out);
+
 /* Differential-test taps (no counterpart call in the reference; they expose the buffers its kernels leave in
  * device memory between launches of tm.py:563-747).
  *  gtm_debug_evaluate: inference on one graph through the scoring kernel (path 0) or through the learning
