@@ -10,6 +10,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "gtm_handles.h"
@@ -124,7 +125,7 @@ extern "C" int gtm_create(const gtm_config *cfg, gtm_model **out)
     // learning grid: all CTAs must be co-resident (cooperative launch); no more warps than clauses
     st = fit_grid_for_global_state(d, m->sm_count, m->fit_block, &m->fit_grid);
     if (st != GTM_OK) { gtm_destroy(m); return st; }
-    st = dev_alloc(&m->exchange, 2 * (size_t)(2 * m->sm_count) * d.K);
+    st = dev_alloc(&m->exchange, exchange_bytes(1, d.K) / sizeof(unsigned long long) + 1);
     if (st == GTM_OK) st = stream_model_create(&m->sm, d);
     if (st == GTM_OK) st = tile_model_create(&m->tm, d);
     if (st != GTM_OK) { gtm_destroy(m); return fail(st, "device allocation failed"); }
@@ -161,6 +162,8 @@ extern "C" int gtm_set_option(gtm_model *m, const char *name, int value)
     if (!strcmp(name, "fit_kernel") && value >= 0 && value <= 2) { m->opt_fit_kernel = value; return GTM_OK; }
     if (!strcmp(name, "score_kernel") && value >= 0 && value <= 3) { m->opt_score_kernel = value; return GTM_OK; }
     if (!strcmp(name, "fit_timers") && value >= 0 && value <= 1) { m->opt_fit_timers = value; return GTM_OK; }
+    if (!strcmp(name, "fit_wait_ms") && value >= 1 && value <= 600000) { m->opt_fit_wait_ms = value; return GTM_OK; }
+    if (!strcmp(name, "fit_missing_cta") && value >= 0 && value <= 1) { m->opt_fit_missing_cta = value; return GTM_OK; }
     return fail(GTM_ERR_ARG, "unknown option '%s' or value %d out of range", name, value);
 }
 
@@ -310,34 +313,73 @@ static int scratch(gtm_dataset *ds, T **dev, size_t count)
     return GTM_OK;
 }
 
+__global__ void graph_edge_ranges_kernel(const u32 *node_index, const u32 *n_nodes, const u32 *edge_index, const u32 *degree,
+                                         int64_t n_graphs, u32 *e0, u32 *ne)
+{
+    for (int64_t gi = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; gi < n_graphs; gi += (int64_t)gridDim.x * blockDim.x) {
+        const u32 first = node_index[gi], last = first + n_nodes[gi] - 1;
+        const u32 start = edge_index[first];
+        e0[gi] = start;
+        ne[gi] = edge_index[last] + degree[last] - start;
+    }
+}
+
 // Host arrays must have the layout that graphs.py produces: node_index and edge_index are exclusive prefix sums of the
 // node counts and out-degrees (graphs.py:101-102,127-128), every graph has 1..max_number_of_graph_nodes nodes.  The
 // kernels size their scratch rows from max_number_of_graph_nodes and index the arrays with these values, so anything
 // else is refused here.  Checks graphs [g_lo, g_hi) and their nodes.
-static int validate_graphs(const gtm_graphs_view *v, int64_t g_lo, int64_t g_hi)
+struct GraphChecks { u32 bad_count = 0, bad_index = 0, bad_edges = 0, n_min = ~0u, n_max = 0; };
+
+static void check_graph_span(const gtm_graphs_view *v, int64_t g_lo, int64_t g_hi, GraphChecks *out)
 {
     const int64_t N = v->number_of_graphs;
     const u32 max_nodes = (u32)v->max_number_of_graph_nodes;
-    if (g_lo == 0 && v->node_index[0] != 0) return fail(GTM_ERR_ARG, "node_index[0] must be 0");
-    u32 bad_count = 0, bad_index = 0;
+    GraphChecks c;
     for (int64_t gi = g_lo; gi < g_hi; ++gi) {
         const u32 n = v->number_of_graph_nodes[gi];
         const uint64_t end = (uint64_t)v->node_index[gi] + n;
         const uint64_t want = gi + 1 < N ? (uint64_t)v->node_index[gi + 1] : (uint64_t)v->total_nodes;
-        bad_count |= (u32)(n - 1u >= max_nodes);
-        bad_index |= (u32)(end != want);
+        c.bad_count |= (u32)(n - 1u >= max_nodes);
+        c.bad_index |= (u32)(end != want);
+        c.n_min = std::min(c.n_min, n);
+        c.n_max = std::max(c.n_max, n);
     }
-    if (bad_count) return fail(GTM_ERR_ARG, "a graph has no nodes or more than max_number_of_graph_nodes = %d", v->max_number_of_graph_nodes);
-    if (bad_index) return fail(GTM_ERR_ARG, "node_index is not the running sum of number_of_graph_nodes (or exceeds total_nodes)");
-    const int64_t v_lo = v->node_index[g_lo], v_hi = g_hi < N ? (int64_t)v->node_index[g_hi] : v->total_nodes;
-    if (v_lo == 0 && v->edge_index[0] != 0) return fail(GTM_ERR_ARG, "edge_index[0] must be 0");
-    u32 bad_edges = 0;
-    for (int64_t vi = v_lo; vi < v_hi; ++vi) {
-        const uint64_t end = (uint64_t)v->edge_index[vi] + v->number_of_graph_node_edges[vi];
-        const uint64_t want = vi + 1 < v->total_nodes ? (uint64_t)v->edge_index[vi + 1] : (uint64_t)v->total_edges;
-        bad_edges |= (u32)(end != want);
+    if (!c.bad_count && !c.bad_index) {          // node ranges are sound: the span's nodes
+        const int64_t v_lo = v->node_index[g_lo], v_hi = g_hi < N ? (int64_t)v->node_index[g_hi] : v->total_nodes;
+        for (int64_t vi = v_lo; vi < v_hi; ++vi) {
+            const uint64_t end = (uint64_t)v->edge_index[vi] + v->number_of_graph_node_edges[vi];
+            const uint64_t want = vi + 1 < v->total_nodes ? (uint64_t)v->edge_index[vi + 1] : (uint64_t)v->total_edges;
+            c.bad_edges |= (u32)(end != want);
+        }
     }
-    if (bad_edges) return fail(GTM_ERR_ARG, "edge_index is not the running sum of number_of_graph_node_edges (or exceeds total_edges)");
+    *out = c;
+}
+
+static int validate_graphs(const gtm_graphs_view *v, int64_t g_lo, int64_t g_hi, u32 *n_min_out = nullptr, u32 *n_max_out = nullptr)
+{
+    if (g_lo == 0 && (v->node_index[0] != 0 || v->edge_index[0] != 0)) return fail(GTM_ERR_ARG, "node_index[0] and edge_index[0] must be 0");
+    // large sets are checked by a few threads side by side (the arrays are only read)
+    const int64_t span = g_hi - g_lo;
+    const int workers = (int)std::max<int64_t>(1, std::min<int64_t>(8, span / (1 << 18)));
+    std::vector<GraphChecks> parts((size_t)workers);
+    if (workers == 1) {
+        check_graph_span(v, g_lo, g_hi, &parts[0]);
+    } else {
+        std::vector<std::thread> threads;
+        for (int w = 0; w < workers; ++w)
+            threads.emplace_back(check_graph_span, v, g_lo + span * w / workers, g_lo + span * (w + 1) / workers, &parts[(size_t)w]);
+        for (std::thread &t : threads) t.join();
+    }
+    GraphChecks all;
+    for (const GraphChecks &c : parts) {
+        all.bad_count |= c.bad_count; all.bad_index |= c.bad_index; all.bad_edges |= c.bad_edges;
+        all.n_min = std::min(all.n_min, c.n_min); all.n_max = std::max(all.n_max, c.n_max);
+    }
+    if (all.bad_count) return fail(GTM_ERR_ARG, "a graph has no nodes or more than max_number_of_graph_nodes = %d", v->max_number_of_graph_nodes);
+    if (all.bad_index) return fail(GTM_ERR_ARG, "node_index is not the running sum of number_of_graph_nodes (or exceeds total_nodes)");
+    if (all.bad_edges) return fail(GTM_ERR_ARG, "edge_index is not the running sum of number_of_graph_node_edges (or exceeds total_edges)");
+    if (n_min_out) *n_min_out = all.n_min;
+    if (n_max_out) *n_max_out = all.n_max;
     return GTM_OK;
 }
 
@@ -380,17 +422,15 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
         GTM_TRY(scratch(ds, &zeros, (size_t)v->number_of_graphs));
         GTM_CU(cudaMemsetAsync(zeros, 0, (size_t)v->number_of_graphs * sizeof(u32), s));
         ds->dg.graph_edge0 = ds->dg.graph_edges = zeros;
-    } else {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows)
-        std::vector<u32> e0((size_t)v->number_of_graphs), ne((size_t)v->number_of_graphs);
-        for (int64_t gi = 0; gi < v->number_of_graphs; ++gi) {
-            const u32 nb = v->node_index[gi], nn = v->number_of_graph_nodes[gi];
-            e0[gi] = v->edge_index[nb];
-            const u32 last = nb + nn - 1;
-            ne[gi] = v->edge_index[last] + v->number_of_graph_node_edges[last] - e0[gi];
-        }
-        GTM_TRY(upload(ds, &ds->dg.graph_edge0, e0.data(), e0.size(), s));
-        GTM_TRY(upload(ds, &ds->dg.graph_edges, ne.data(), ne.size(), s));
-        GTM_CU(cudaStreamSynchronize(s));   // the vectors go out of scope
+    } else {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows): derived on the device
+        u32 *e0, *ne;
+        GTM_TRY(scratch(ds, &e0, (size_t)v->number_of_graphs));
+        GTM_TRY(scratch(ds, &ne, (size_t)v->number_of_graphs));
+        graph_edge_ranges_kernel<<<(unsigned)std::min<int64_t>((v->number_of_graphs + 255) / 256, 4096), 256, 0, s>>>(
+            ds->dg.node_index, ds->dg.n_nodes, ds->dg.edge_index, ds->dg.degree, v->number_of_graphs, e0, ne);
+        GTM_CU(cudaGetLastError());
+        ds->dg.graph_edge0 = e0;
+        ds->dg.graph_edges = ne;
     }
     ds->dg.n_types = 1;
     ds->dg.total_nodes = (u32)v->total_nodes; ds->dg.total_edges = (u32)v->total_edges;
@@ -449,7 +489,7 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
 
     GTM_TRY(stream_data_create(&ds->sd, m->sm, d, ds->dg, v, m->sm_count, s));
     // tiles of whole graphs for the tile kernel: deeper models, or sets the node-stream kernel does not cover
-    if (d.D > 1 || !ds->sd.supported || m->opt_score_kernel == 3) GTM_TRY(tile_data_create(&ds->td, m->tm, d, v, m->sm_count, s));
+    if (d.D > 1 || !ds->sd.supported || m->opt_score_kernel == 3) GTM_TRY(tile_data_create(&ds->td, m->tm, d, v, ds->n_min, ds->n_max, m->sm_count, s));
     GTM_CU(cudaStreamSynchronize(s));
     return GTM_OK;
 }
@@ -467,7 +507,7 @@ static int dataset_create(gtm_model *m, const gtm_graphs_view *v, gtm_dataset **
     ds->max_nodes = v->max_number_of_graph_nodes;
     ds->NC = words_for(ds->max_nodes);
     // the pipelined caller validates chunk by chunk, just before each chunk is copied
-    int st = copy_arrays ? validate_graphs(v, 0, v->number_of_graphs) : GTM_OK;
+    int st = copy_arrays ? validate_graphs(v, 0, v->number_of_graphs, &ds->n_min, &ds->n_max) : GTM_OK;
     if (st == GTM_OK) st = dataset_build(m, v, ds, copy_arrays);
     if (st != GTM_OK) { gtm_dataset_destroy(ds); return st; }
     *out = ds;

@@ -486,6 +486,100 @@ __device__ __forceinline__ u32 eval_node_words(const DevModel &m, const GraphVie
     return any;
 }
 
+// eval_clause_layer for a graph of at most 32 nodes, with the lanes spread over the layer's include WORDS instead of
+// over nodes: per candidate node (a node of the clause's type that was true in the layer below) every lane loads its
+// words of the node's row - one coalesced load per 32 words - tests (include & ~row) and the warp votes.  A small
+// graph has few candidates and every one costs W/32 loads, where the node-parallel form walks the include words one
+// after the other in a chain of dependent loads.  Four candidates are in flight at a time.  Same results: node-output
+// word in out[0], include count, messages through `scatter`.
+__device__ __forceinline__ u32 eval_clause_layer_small(const DevModel &m, const GraphView &gv, int n_types, const ClauseView &cv,
+                                                       int c, int d, const u32 *prev, u32 *out, const u32 *Pread,
+                                                       const ScatterTargets *scatter, int lane)
+{
+    const int n = gv.n;
+    const int W = d == 0 ? m.L0 : m.M;
+    const u32 *inc = cv.ta(d) + (size_t)(m.SB - 1) * W;
+    const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;
+    const u32 my_type = (u32)(c % n_types);
+    const bool candidate = lane < n && gv.type[lane] == my_type && (d == 0 || ((prev[0] >> lane) & 1u));
+    u32 cand = __ballot_sync(kFull, candidate);
+    const bool fast_msg = (m.MS & 31) == 0;
+    auto row_word = [&](int v, int w) -> u32 {          // word w of node v's literal vector of this layer
+        if (d == 0) return gv.X[(size_t)v * W + w];
+        const u32 *prow = Pread + (size_t)v * m.MW;
+        if (fast_msg) return w < m.MW ? prow[w] : ~prow[w - m.MW];
+        return msg_word(prow, w, m.MS, m.MW);
+    };
+    int cnt = 0;
+    u32 result = 0;
+    for (int w0 = 0; w0 < W; w0 += 128) {               // include words in registers, 128 words (4 per lane) at a time
+        u32 iw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int w = w0 + 32 * q + lane;
+            iw[q] = w < W ? inc[w] & (w == W - 1 ? last_mask : kFull) : 0u;
+            cnt += __popc(iw[q]);
+        }
+        u32 todo = cand, still = 0;                      // candidates that pass this stretch of words
+        while (todo) {
+            int v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                v[t] = todo ? __ffs(todo) - 1 : -1;
+                todo &= todo - 1;
+            }
+            bool fail[4] = {false, false, false, false};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int w = w0 + 32 * q + lane;
+                if (w0 + 32 * q < W) {                   // warp-uniform
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                        if (v[t] >= 0 && w < W) fail[t] = fail[t] || (iw[q] & ~row_word(v[t], w)) != 0;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                if (v[t] >= 0 && !__any_sync(kFull, fail[t])) still |= 1u << v[t];
+        }
+        cand = still;
+    }
+    result = cand;
+    cnt = __reduce_add_sync(kFull, cnt);
+    if (lane == 0) {
+        *cv.n_inc = (d == 0 ? 0 : *cv.n_inc) + cnt;
+        out[0] = result;
+    }
+    if (scatter && ((result >> lane) & 1u)) {
+        const int v = lane;
+        if (scatter->local) {
+            // mark the clause's hypervector bits on this (source) node; most are there already
+            for (int b = 0; b < m.MB; ++b) {
+                u32 bit = cv.hv[b];
+                if (bit >= (u32)m.MS) bit %= (u32)m.MS;
+                u32 *addr = local_row(*scatter, v, m.MW) + (bit >> 5);
+                const u32 mbit = 1u << (bit & 31);
+                if (!(*(volatile u32 *)addr & mbit)) atomicOr(addr, mbit);
+            }
+        } else {
+            const u32 e0 = gv.eidx[v] - gv.e_off, deg = gv.degree[v];
+            for (u32 k = 0; k < deg && e0 + k < gv.e_cnt; ++k) {
+                const u32 dst = gv.edge[2 * (size_t)(e0 + k)], t = gv.edge[2 * (size_t)(e0 + k) + 1];
+                if (dst >= (u32)n) continue;                              // malformed edge: ignore, never fault
+                for (int b = 0; b < m.MB; ++b) {
+                    u32 bit = cv.hv[b] + t;                               // (hv + edge type) mod MS without a 64-bit division
+                    if (bit >= (u32)m.MS || bit < t) bit = (u32)(((u64)cv.hv[b] + t) % (u32)m.MS);
+                    const u32 mbit = 1u << (bit & 31);
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                        if (r < scatter->world) atomicOr(scatter->base[r] + (size_t)dst * m.MW + (bit >> 5), mbit);
+                }
+            }
+        }
+    }
+    return result;
+}
+
 // One warp evaluates a clause at layer `d` over all nodes of a graph (lanes = the 32 nodes of a node word) and
 // writes the node-output words out[0..ceil(n/32)).  Layer 0 tests the node's literal row, layer d >= 1 the node's
 // message row ANDed with the node's bit of layer d-1 in `prev` (kernels.py:407-530).  Returns the OR of the words
@@ -499,6 +593,7 @@ __device__ __forceinline__ u32 eval_clause_layer(const DevModel &m, const GraphV
                                                  const ScatterTargets *scatter, int lane)
 {
     const int n = gv.n;
+    if (!kBatchNodes && n <= 32) return eval_clause_layer_small(m, gv, n_types, cv, c, d, prev, out, Pread, scatter, lane);
     const int W = d == 0 ? m.L0 : m.M;
     const u32 *inc = cv.ta(d) + (size_t)(m.SB - 1) * W;
     const u32 last_mask = d == 0 ? m.lit_mask : m.msg_mask;

@@ -11,7 +11,7 @@ struct FitArgs {
     const int *Y;           // [N][K] +-T targets, absolute graph ids
     int64_t first, count;
     int epochs;
-    unsigned long long *exchange;   // [2][gridDim.x][K] (vote partial << 32 | step tag), ping-pong by graph parity
+    unsigned long long *exchange;   // this rank's vote exchange area, see exchange_class_sums
     u32 *P_pair[2];         // message buffers, ping-pong by graph parity ([D-1][max_nodes][MW] each)
     int max_nodes;
     unsigned *barrier;      // monotonically increasing arrival counter (zeroed before launch)
@@ -33,21 +33,37 @@ struct FitArgs {
     int p_smem_words;       // solo and depth > 1: message buffers (words per parity) live in that CTA's shared memory
     // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits
     // and barrier arrivals go to every rank's buffers through peer pointers.  world == 1: everything is local.
+    unsigned long long wait_ns;   // budget of one device-side wait (grid barrier, vote exchange)
+    int missing;            // test hook: every wait expects this many arrivals more than there are CTAs, so it runs out
     int world, rank;
     int c_begin, c_end;
     u32 tag_base;           // step tags of this launch are tag_base + step + 1
     unsigned barrier_base;  // value of the arrival counters before this launch
-    unsigned long long *exchange_peer[kMaxRanks];   // [2][world][gridDim.x][K] on every rank
+    unsigned long long *exchange_peer[kMaxRanks];   // the exchange areas of all ranks
     unsigned *barrier_peer[kMaxRanks];
     u32 *P_peer[kMaxRanks][2];
 };
 
-constexpr unsigned kSpinLimit = 1u << 22;
+// Every device-side wait (grid barrier, vote exchange) is bounded by wall time: FitArgs::wait_ns, set from the model
+// option "fit_wait_ms".  A wait that runs out raises *error; the kernel then returns and the host reports GTM_ERR_TIMEOUT.
+struct WaitClock {
+    unsigned long long t0 = 0;
+    unsigned spins = 0;
+    // true when the budget is used up; reads the clock only every 64 polls
+    __device__ __forceinline__ bool expired(unsigned long long budget_ns)
+    {
+        if ((++spins & 63u) != 0) return false;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) { t0 = now; return false; }
+        return now - t0 > budget_ns;
+    }
+};
 
 // Barrier over all co-resident CTAs of all ranks (cooperative launch per rank; ranks of a clause-sharded fit run the
 // same step sequence).  Every CTA adds one arrival to the counter of EVERY rank (release; system scope when peers are
 // involved) and polls its own rank's counter (acquire).  Counters only grow, `target` is compared wrap-safely.  The
-// wait is bounded: after kSpinLimit polls the CTA raises *error and gives up.  Returns false once any CTA gave up.
+// wait is bounded (WaitClock): when it runs out the CTA raises *error and gives up.  Returns false once any CTA gave up.
 __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
 {
     __syncthreads();
@@ -59,59 +75,73 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
             for (int r = 0; r < kMaxRanks; ++r)      // constant indices: kernel parameters must not be indexed dynamically
                 if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
         }
-        unsigned spins = 0;
+        WaitClock clock;
+        const unsigned expected = target + (unsigned)a.missing;       // test hook: an arrival that never comes
         while (true) {
             unsigned seen;
             if (a.world == 1) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
             else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
-            if ((int)(seen - target) >= 0) break;
+            if ((int)(seen - expected) >= 0) break;
             if (*(volatile int *)a.error) break;
-            if (++spins > kSpinLimit) { atomicExch(a.error, 1); break; }
+            if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
         }
     }
     __syncthreads();
     return *(volatile int *)a.error == 0;
 }
 
-// Class sums of one graph from per-CTA vote partials, in one round: every CTA publishes its K partials as 64-bit
-// words that carry the step tag next to the value (an aligned 8-byte store is single-copy atomic, also through a
-// peer pointer, so a reader that sees the tag sees the value) into the slot array of EVERY rank, then reads all
-// world*gridDim.x*K words of its own rank's array, eight independent loads per thread in flight, re-polling only
-// words whose tag is still old.  Slots alternate by graph parity: a slot is rewritten two steps later, which its owner
-// can only reach after every CTA of every rank has read the current step.
+// Class sums of one graph from per-CTA vote partials, in two levels.
+//   Inside a rank: every CTA adds its K partials to the rank's accumulator of the step's parity (device-scope atomics) and
+//   then arrives on a counter; the CTA whose arrival completes the count takes the sums out of the accumulator (leaving
+//   zeros for the step after next) and
+//   between ranks: publishes them as K 64-bit words that carry the step tag next to the value (an aligned 8-byte store is
+//   single-copy atomic, also through a peer pointer, so a reader that sees the tag sees the value) into slot
+//   [parity][own rank] of EVERY rank.  All CTAs then poll the world*K words of their own rank's slots.
+// A CTA thus sends K atomics and one arrival and reads world*K words per graph, whatever the grid size.
+// Parities alternate by step: a slot or accumulator is touched again two steps later, which any CTA can only reach after
+// every CTA of every rank has read the current step.  Layout of `exchange` (8-byte units): slots [2][world][K], then the
+// accumulators int[2][K] and the arrival counters unsigned[2] (both zeroed by the host before every launch).
 // Call with s_sum complete (after a __syncthreads); leaves totals in s_total, clears s_sum.  Bounded polls.
-__device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, int par, u32 tag, int *s_sum, int *s_total, int K)
+__device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_sum,
+                                                    int *s_total, int K)
 {
-    const size_t mine = (((size_t)par * a.world + a.rank) * gridDim.x + blockIdx.x) * K;
+    __shared__ int s_completes;
+    int *acc_base = reinterpret_cast<int *>(a.exchange + (size_t)2 * a.world * K);
+    int *acc = acc_base + par * K;
+    unsigned *arrive = reinterpret_cast<unsigned *>(acc_base + 2 * K) + par;
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        const unsigned long long word = ((unsigned long long)(u32)s_sum[k] << 32) | tag;
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < a.world) *(volatile unsigned long long *)(a.exchange_peer[r] + mine + k) = word;
+        const int v = s_sum[k];
+        if (v != 0) atomicAdd(acc + k, v);
         s_sum[k] = 0;
         s_total[k] = 0;
     }
+    __threadfence();
     __syncthreads();
-    volatile unsigned long long *all = a.exchange + (size_t)par * a.world * gridDim.x * K;
-    const int total = a.world * (int)gridDim.x * K;
-    for (int t0 = threadIdx.x; t0 < total; t0 += 8 * blockDim.x) {
-        unsigned long long v[8];
+    if (threadIdx.x == 0) {
+        const unsigned target = (gridDim.x + (unsigned)a.missing) * (unsigned)(step / 2 + 1);     // arrivals of this parity so far, this launch
+        s_completes = atomicAdd(arrive, 1u) + 1u == target;
+    }
+    __syncthreads();
+    if (s_completes) {
+        __threadfence();
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const int v = atomicExch(acc + k, 0);
+            const unsigned long long word = ((unsigned long long)(u32)v << 32) | tag;
+            const size_t slot = ((size_t)par * a.world + a.rank) * K + k;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int t = t0 + j * blockDim.x;
-            v[j] = t < total ? all[t] : (unsigned long long)tag;
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < a.world) *(volatile unsigned long long *)(a.exchange_peer[r] + slot) = word;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int t = t0 + j * blockDim.x;
-            if (t >= total) continue;
-            unsigned spins = 0;
-            while ((u32)v[j] != tag) {
-                if (++spins > kSpinLimit || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
-                v[j] = all[t];
-            }
-            atomicAdd(&s_total[t % K], (int)(u32)(v[j] >> 32));
+    }
+    volatile unsigned long long *mine = a.exchange + (size_t)par * a.world * K;
+    for (int t = threadIdx.x; t < a.world * K; t += blockDim.x) {
+        unsigned long long v = mine[t];
+        WaitClock clock;
+        while ((u32)v != tag) {
+            if (clock.expired(a.wait_ns) || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
+            v = mine[t];
         }
+        atomicAdd(&s_total[t % K], (int)(u32)(v >> 32));
     }
     __syncthreads();
     if (blockIdx.x == 0)

@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
             }
             __syncthreads();
             GTM_LAP(t_eval);
-            if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
+            if (!exchange_class_sums(a, step, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
             GTM_LAP(t_tot);
             if (!eval_only) {
                 class_decision_inputs(m, s_total, a.Y + (size_t)e * m.K, s_target, s_thr);

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 s_sum[k] = 0;
             }
             __syncthreads();
-        } else if (!exchange_class_sums(a, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
+        } else if (!exchange_class_sums(a, step, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
         GTM_LAP(t_tot);
         class_decision_inputs(m, s_total, y, s_target, s_thr);
         __syncthreads();
@@ -440,6 +440,13 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
 
 static int shard_size(int C, int world) { return (C + world - 1) / world; }
 
+// Bytes of one rank's vote exchange area: tagged slots [2][world][K], accumulators int[2][K], arrival counters [2]
+// (exchange_class_sums).
+size_t exchange_bytes(int world, int K)
+{
+    return (size_t)2 * world * K * sizeof(unsigned long long) + (size_t)2 * K * sizeof(int) + 2 * sizeof(unsigned) + 8;
+}
+
 int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
                int epochs, int eval_only)
 {
@@ -459,6 +466,8 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     a.class_sum_tap = m->class_sum_tap;
     a.phase_cycles = m->phase_cycles;
     a.timers = m->opt_fit_timers;
+    a.wait_ns = (unsigned long long)m->opt_fit_wait_ms * 1000000ull;
+    a.missing = eval_only ? 0 : m->opt_fit_missing_cta;
     a.NC = ds->NC;
     const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
     GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
@@ -479,6 +488,10 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             a.P_peer[r][0] = (u32 *)(base + cm.P_off[0]);
             a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
         }
+        // accumulators and arrival counters of the vote exchange start every launch at zero (they are this rank's own;
+        // the slots that peers write keep their tags)
+        GTM_CU(cudaMemsetAsync((char *)cm.block + cm.exchange_off + (size_t)2 * cm.world * d.K * sizeof(unsigned long long), 0,
+                               (size_t)2 * d.K * sizeof(int) + 2 * sizeof(unsigned), m->stream));
         resident = cm.resident; grid = cm.grid;
         a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride;
         smem = cm.smem;
@@ -488,7 +501,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         a.barrier_peer[0] = m->barrier; a.exchange_peer[0] = m->exchange;
         a.P_peer[0][0] = ds->P_pair[0]; a.P_peer[0][1] = ds->P_pair[1];
         GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
-        GTM_CU(cudaMemsetAsync(m->exchange, 0, 2 * (size_t)(2 * m->sm_count) * d.K * sizeof(unsigned long long), m->stream));
+        GTM_CU(cudaMemsetAsync(m->exchange, 0, exchange_bytes(1, d.K), m->stream));
         if (d.D > 1) {
             GTM_CU(cudaMemsetAsync(ds->P_pair[0], 0, p_bytes, m->stream));
             GTM_CU(cudaMemsetAsync(ds->P_pair[1], 0, p_bytes, m->stream));
@@ -573,7 +586,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     }
     const size_t p_bytes = ((size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32) + 255) & ~(size_t)255;
     cm.exchange_off = 256;
-    const size_t ex_bytes = ((size_t)2 * world * cm.grid * d.K * sizeof(unsigned long long) + 255) & ~(size_t)255;
+    const size_t ex_bytes = (exchange_bytes(world, d.K) + 255) & ~(size_t)255;
     cm.P_off[0] = cm.exchange_off + ex_bytes;
     cm.P_off[1] = cm.P_off[0] + p_bytes;
     cm.bytes = cm.P_off[1] + p_bytes;

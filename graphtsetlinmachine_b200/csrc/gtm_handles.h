@@ -22,8 +22,10 @@ struct gtm_model {
     int *flag_host = nullptr;                 // page-locked landing place of score_error
     int *score_error = nullptr;               // raised by scoring kernels that skipped a malformed graph (device-pointer inputs)
     int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
-    unsigned long long *exchange = nullptr;   // [2][2*sm_count][K] vote exchange slots
+    unsigned long long *exchange = nullptr;   // vote exchange area of a single-GPU fit (exchange_bytes(1, K))
     int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
+    int opt_fit_wait_ms = 2000;               // budget of one device-side wait of the learning kernels
+    int opt_fit_missing_cta = 0;              // test hook: waits expect one arrival that never comes (they must run out cleanly)
     int opt_fit_timers = 0;                   // 1: the learning kernels time their phases (gtm_debug_fit_phase_cycles)
     int opt_score_kernel = 0;                 // 0 auto, 1 general kernel, 2 node-stream kernel, 3 tile kernel
     unsigned *barrier = nullptr;
@@ -57,6 +59,7 @@ struct gtm_dataset {
     DevGraphs dg;
     int64_t n_graphs, total_nodes, total_edges;
     int max_nodes, NC;
+    u32 n_min = 0, n_max = 0;      // smallest / largest graph (0: not known, e.g. a set that is copied chunk by chunk)
     std::vector<void *> owned;
     // learning scratch (every layer kept) and its message ping-pong
     EvalScratch fit_sc;
@@ -86,3 +89,4 @@ int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *g
 int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count, int epochs,
                int eval_only);
 void fit_comm_release(gtm_dataset *ds);
+size_t exchange_bytes(int world, int K);

@@ -16,8 +16,8 @@
 //      layers only visit survivors, which is what "layer d is ANDed with layer d-1" (kernels.py:525-527) comes to;
 //   4. the marks are transposed to node-major rows (the message each node SENDS), one pass over the tile's edges ORs
 //      them, rotated by the edge type ((hv + type) mod MS, kernels.py:581), into the destination rows, and those are
-//      transposed back into PT[message bit][node word], the literal rows of the next layer (a negated message literal
-//      ANDs the complement of its row);
+//      transposed back into PT[message bit][node word] and its complement (the negated message literals), the literal
+//      rows of the next layer;
 //   5. after the last layer, per graph and warp, the weights of the clauses that fired are summed over the warp with
 //      redux.sync and added to the graph's class sums in shared memory (kernels.py:279-317, unclamped).
 //
@@ -49,90 +49,76 @@ __device__ __forceinline__ const u32 *include_plane(const DevModel &m, int layer
                       : m.tam + (((size_t)(layer - 1) * m.C + c) * m.SB + (m.SB - 1)) * m.M;
 }
 
-// Included literals of a clause layer, counted in groups of four: those tested as they are / complemented.
-// Layer 0 has both polarities of a feature as literals of its own (graphs.py:150-159), so nothing is complemented;
-// a message layer's literal l >= MS is the complement of message bit l - MS (kernels.py:544-545).
-// cnt[c] = plain groups | complemented groups << 16.
-__global__ void tile_count_kernel(DevModel m, int layer, int *cnt)
+// Row of bit p in a transposed buffer whose source rows have W words: bit b of word w lives in row b*W + w (so that
+// the threads that transpose adjacent words write adjacent rows).  Layer 0: row(l) for literal l (both polarities of a
+// feature are literals of their own, graphs.py:150-159).  Message layers: rows 0 .. 32*MW-1 hold the message bits, rows
+// 32*MW .. 64*MW-1 their complements - literal l >= MS of a message layer is the complement of message bit l - MS
+// (kernels.py:544-545).  After the literal rows come four rows of ones (list padding, one per residue class).
+__device__ __forceinline__ int tile_row(int p, int W) { return (p & 31) * W + (p >> 5); }
+constexpr int kTilePadRows = 4;
+__host__ __device__ __forceinline__ int tile_literal_rows(int layer, int L0, int MW) { return layer == 0 ? 32 * L0 : 64 * MW; }
+
+// Visits the rows of the included literals of a clause layer.
+template <class F>
+__device__ __forceinline__ void tile_for_each_included(const DevModel &m, int layer, int c, F f)
 {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= m.C) return;
     const int W = layer == 0 ? m.L0 : m.M;
     const u32 last = layer == 0 ? m.lit_mask : m.msg_mask;
     const u32 *inc = include_plane(m, layer, c);
-    int plain = 0, negated = 0;
-    for (int w = 0; w < W; ++w) {
-        const u32 bits = inc[w] & (w == W - 1 ? last : kFull);
-        const int lo = 32 * w;
-        if (layer == 0 || lo + 32 <= m.MS) plain += __popc(bits);
-        else if (lo >= m.MS) negated += __popc(bits);
-        else {
-            const int split = m.MS - lo;
-            plain += __popc(bits & ((1u << split) - 1u));
-            negated += __popc(bits >> split);
-        }
-    }
-    cnt[c] = ((plain + 3) >> 2) | (((negated + 3) >> 2) << 16);
-}
-
-// The lists of 32 consecutive clauses are stored interleaved - group g of the block's clause l is the 8-byte element
-// blk_off[block] + 32*g + l - so that a warp whose lanes hold those clauses fetches group g of all of them with one
-// coalesced 256-byte load.  A block takes 32 * (its longest list) elements.  One CUDA block computes all offsets.
-__global__ void tile_block_offsets_kernel(const int *cnt, int C, int *blk_off, int *total_out)
-{
-    __shared__ int s_part[1024];
-    const int nblk = (C + 31) >> 5;
-    const int per = (nblk + blockDim.x - 1) / blockDim.x;
-    const int lo = min(nblk, (int)threadIdx.x * per), hi = min(nblk, lo + per);
-    auto block_len = [&](int b) {
-        int longest = 0;
-        for (int c = 32 * b; c < min(C, 32 * b + 32); ++c) longest = max(longest, (cnt[c] & 0xffff) + (cnt[c] >> 16));
-        return 32 * longest;
-    };
-    int sum = 0;
-    for (int b = lo; b < hi; ++b) sum += block_len(b);
-    s_part[threadIdx.x] = sum;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int t = 0; t < (int)blockDim.x; ++t) { const int v = s_part[t]; s_part[t] = run; run += v; }
-        blk_off[nblk] = run;
-        *total_out = run;
-    }
-    __syncthreads();
-    int run = s_part[threadIdx.x];
-    for (int b = lo; b < hi; ++b) { blk_off[b] = run; run += block_len(b); }
-}
-
-// Row of literal bit p in the transposed buffer whose source rows have W words: bit b of word w lives in row b*W + w
-// (so that the threads that transpose adjacent words write adjacent rows); rows 32*W and 32*W+1 are all ones / zeros.
-__device__ __forceinline__ unsigned short tile_row(int p, int W) { return (unsigned short)((p & 31) * W + (p >> 5)); }
-
-__global__ void tile_fill_kernel(DevModel m, int layer, const int *cnt, const int *blk_off, unsigned short *list, int *Wt,
-                                 int KROW, u32 *hvm)
-{
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= m.C) return;
-    const int W = layer == 0 ? m.L0 : m.M;
-    const int WS = layer == 0 ? m.L0 : m.MW;           // words of a source row (literal row / positive message bits)
-    const u32 last = layer == 0 ? m.lit_mask : m.msg_mask;
-    const u32 *inc = include_plane(m, layer, c);
-    const int n_plain = cnt[c] & 0xffff, n_neg = cnt[c] >> 16;
-    // entry e (four per group) of this clause's list: element blk_off + 32*(e/4) + lane, slot e%4
-    unsigned short *base = list + ((size_t)blk_off[c >> 5] + (c & 31)) * 4;
-    auto slot = [&](int e) -> unsigned short & { return base[(size_t)(e >> 2) * 128 + (e & 3)]; };
-    int at_plain = 0, at_neg = 4 * n_plain;
     for (int w = 0; w < W; ++w) {
         u32 bits = inc[w] & (w == W - 1 ? last : kFull);
         while (bits) {
             const int l = 32 * w + __ffs(bits) - 1;
             bits &= bits - 1;
-            if (layer == 0 || l < m.MS) slot(at_plain++) = tile_row(l, WS);
-            else slot(at_neg++) = tile_row(l - m.MS, WS);
+            if (layer == 0) f(tile_row(l, m.L0));
+            else f(l < m.MS ? tile_row(l, m.MW) : 32 * m.MW + tile_row(l - m.MS, m.MW));
         }
     }
-    while (at_plain < 4 * n_plain) slot(at_plain++) = (unsigned short)(32 * WS);             // all ones: no effect on an AND
-    while (at_neg < 4 * (n_plain + n_neg)) slot(at_neg++) = (unsigned short)(32 * WS + 1);   // all zeros: no effect when complemented
+}
+
+// The list of the clause at position p of its layer's order (see tile_fill_kernel) is arranged so that its entry e
+// names a row of residue class (p + e) mod 4 (row number mod 4), with
+// padding rows where a class runs dry: the eight lanes that share a shared-memory wavefront of a 128-bit load hold
+// eight consecutive positions, so at every step they read rows of four different classes, which with 32-byte rows
+// (tiles of 8 node words) and the two quads taken in opposite order by the two halves are eight different bank
+// groups - no bank conflicts, whatever literals the clauses include.  A list therefore takes as many groups of
+// four entries as its fullest class has rows: cnt[c].
+__global__ void tile_count_kernel(DevModel m, int layer, int *cnt)
+{
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= m.C) return;
+    int n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+    tile_for_each_included(m, layer, c, [&](int row) {
+        const int r = row & 3;
+        n0 += r == 0; n1 += r == 1; n2 += r == 2; n3 += r == 3;
+    });
+    cnt[c] = max(max(n0, n1), max(n2, n3));
+}
+
+// Clauses are evaluated in an order of their own per layer: by decreasing list length (`order[p]` = clause at position
+// p), so that the 32 clauses a warp takes together have lists of about the same length and no lane waits long for
+// the longest.  The lists of the 32 clauses of a block of positions are stored interleaved - group g of position p is
+// the 8-byte element blk_off[p / 32] + 32*g + p % 32 - so that the warp fetches group g of all of them with one
+// coalesced 256-byte load; a block takes 32 * (its longest list) elements.  Order and offsets are made on the host
+// (tile_model_refresh).
+__global__ void tile_fill_kernel(DevModel m, int layer, const int *order, const int *cnt, const int *blk_off,
+                                 unsigned short *list, int *Wt, int KROW, u32 *hvm)
+{
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= m.C) return;
+    const int c = order[p];
+    const int groups = cnt[c], pad = tile_literal_rows(layer, m.L0, m.MW);
+    // entry e (four per group) of this position's list: element blk_off + 32*(e/4) + lane, slot e%4
+    unsigned short *base = list + ((size_t)blk_off[p >> 5] + (p & 31)) * 4;
+    auto slot = [&](int e) -> unsigned short & { return base[(size_t)(e >> 2) * 128 + (e & 3)]; };
+    // padding first: entry e belongs to class (p + e) mod 4; a row of ones has no effect on an AND
+    for (int e = 0; e < 4 * groups; ++e) slot(e) = (unsigned short)(pad + ((p + e) & 3));
+    int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    tile_for_each_included(m, layer, c, [&](int row) {
+        const int r = row & 3;
+        const int k = r == 0 ? s0++ : r == 1 ? s1++ : r == 2 ? s2++ : s3++;
+        slot(4 * k + ((r - p) & 3)) = (unsigned short)row;        // the k-th entry of class r
+    });
     if (layer == 0) {
         for (int k = 0; k < KROW; ++k) Wt[(size_t)c * KROW + k] = k < m.K ? m.weights[(size_t)k * m.C + c] : 0;
         for (int b = 0; b < m.MB; ++b) hvm[(size_t)c * m.MB + b] = m.hv[(size_t)c * m.MB + b] % (u32)m.MS;
@@ -155,8 +141,7 @@ struct TileArgs {
     const int *Wt;
     int KROW;
     const u32 *hvm;
-    int *surv_c;                        // [grid][2][quad pairs][C] clauses still true after a layer ...
-    uint4 *surv_r;                      // ... and their node bits on the pair's two quads
+    uint4 *surv_r;                      // [grid][2][quad pairs][C][2] node bits of every clause on the pair's two quads after a layer
     int *error;                         // raised (2) when the wait for a bulk copy gave up
 };
 
@@ -205,44 +190,44 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity)
     }
 }
 
-// Node bits of a clause on a PAIR of quads after ANDing the rows of its included literals: `plain` groups of four rows
-// as they are, then `negated` groups complemented.  lp: the clause's first list element (elements of one clause are 32
-// apart, see tile_block_offsets_kernel); tq: shared address of the first quad's words in row 0 (the second quad's
-// follow 16 bytes later); a row is `1 << rowshift` bytes.  `two`: the second quad exists (warp-uniform).
-__device__ __forceinline__ void tile_eval(uint4 &ra, uint4 &rb, const uint2 *lp, int plain, int negated, unsigned tq,
-                                          int rowshift, bool two)
+// r &= two rows of one quad (128-bit shared loads at a0 and a1).
+__device__ __forceinline__ void tile_and_rows(uint4 &r, unsigned a0, unsigned a1)
 {
-    for (int gI = 0; gI < plain; ++gI) {
-        if ((ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) == 0) return;
-        const uint2 four = __ldg(lp + 32 * gI);
-        const unsigned o0 = tq + ((four.x & 0xffffu) << rowshift), o1 = tq + ((four.x >> 16) << rowshift),
-                       o2 = tq + ((four.y & 0xffffu) << rowshift), o3 = tq + ((four.y >> 16) << rowshift);
-        {
-            const uint4 x0 = tile_lds128(o0), x1 = tile_lds128(o1), x2 = tile_lds128(o2), x3 = tile_lds128(o3);
-            ra.x &= x0.x & x1.x; ra.y &= x0.y & x1.y; ra.z &= x0.z & x1.z; ra.w &= x0.w & x1.w;
-            ra.x &= x2.x & x3.x; ra.y &= x2.y & x3.y; ra.z &= x2.z & x3.z; ra.w &= x2.w & x3.w;
-        }
-        if (two) {
-            const uint4 x0 = tile_lds128(o0 + 16), x1 = tile_lds128(o1 + 16), x2 = tile_lds128(o2 + 16), x3 = tile_lds128(o3 + 16);
-            rb.x &= x0.x & x1.x; rb.y &= x0.y & x1.y; rb.z &= x0.z & x1.z; rb.w &= x0.w & x1.w;
-            rb.x &= x2.x & x3.x; rb.y &= x2.y & x3.y; rb.z &= x2.z & x3.z; rb.w &= x2.w & x3.w;
-        }
-    }
-    for (int gI = plain; gI < plain + negated; ++gI) {
-        if ((ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) == 0) return;
-        const uint2 four = __ldg(lp + 32 * gI);
-        const unsigned o0 = tq + ((four.x & 0xffffu) << rowshift), o1 = tq + ((four.x >> 16) << rowshift),
-                       o2 = tq + ((four.y & 0xffffu) << rowshift), o3 = tq + ((four.y >> 16) << rowshift);
-        {
-            const uint4 x0 = tile_lds128(o0), x1 = tile_lds128(o1), x2 = tile_lds128(o2), x3 = tile_lds128(o3);
-            ra.x &= ~(x0.x | x1.x); ra.y &= ~(x0.y | x1.y); ra.z &= ~(x0.z | x1.z); ra.w &= ~(x0.w | x1.w);
-            ra.x &= ~(x2.x | x3.x); ra.y &= ~(x2.y | x3.y); ra.z &= ~(x2.z | x3.z); ra.w &= ~(x2.w | x3.w);
-        }
-        if (two) {
-            const uint4 x0 = tile_lds128(o0 + 16), x1 = tile_lds128(o1 + 16), x2 = tile_lds128(o2 + 16), x3 = tile_lds128(o3 + 16);
-            rb.x &= ~(x0.x | x1.x); rb.y &= ~(x0.y | x1.y); rb.z &= ~(x0.z | x1.z); rb.w &= ~(x0.w | x1.w);
-            rb.x &= ~(x2.x | x3.x); rb.y &= ~(x2.y | x3.y); rb.z &= ~(x2.z | x3.z); rb.w &= ~(x2.w | x3.w);
-        }
+    const uint4 x0 = tile_lds128(a0), x1 = tile_lds128(a1);
+    r.x &= x0.x & x1.x; r.y &= x0.y & x1.y; r.z &= x0.z & x1.z; r.w &= x0.w & x1.w;
+}
+
+// Node bits of the warp's 32 clauses (lane = clause) on a PAIR of quads after ANDing the rows of their included
+// literals.  lp: the lane's first list element (elements of one clause are 32 apart, see tile_fill_kernel);
+// groups: its list length in groups of four rows (0 for a lane without a clause); pad4: four padding rows of the lane's
+// residue classes, packed like a list element; t0 / t1: shared addresses, in row 0, of the quad this lane takes first /
+// second (r0 / r1 are its node bits; lanes 4..7 of every eight take the pair in the opposite order, see
+// tile_count_kernel); a row is `1 << rowshift` bytes; `two`: the pair has a second quad (warp-uniform).
+// Called by all lanes of the warp, which stay in lockstep - that is what keeps their loads free of bank conflicts: the
+// trip count is the warp's, a lane whose list has ended reads padding rows (all ones), a lane whose bits are all gone
+// keeps reading its rows (a load costs nothing extra while the other lanes of its wavefront load anyway), and the warp
+// leaves together when no lane has work left.  The next group's row numbers are fetched while the current group's
+// rows are read.
+__device__ __forceinline__ void tile_eval(uint4 &r0, uint4 &r1, const uint2 *lp, int groups, uint2 pad4, unsigned t0,
+                                          unsigned t1, int rowshift, bool two)
+{
+    const int longest = __reduce_max_sync(kFull, groups);
+    const unsigned keep = 0xffffu << rowshift;
+    uint2 next = pad4;
+    if (groups > 0) next = __ldg(lp);
+#pragma unroll 1
+    for (int gI = 0; gI < longest; ++gI) {
+        const bool busy = gI < groups && (r0.x | r0.y | r0.z | r0.w | r1.x | r1.y | r1.z | r1.w) != 0;
+        if (!__any_sync(kFull, busy)) return;
+        const uint2 four = next;
+        next = pad4;
+        if (gI + 1 < groups) next = __ldg(lp + 32 * (gI + 1));
+        const unsigned o0 = (four.x << rowshift) & keep, o1 = (four.x >> (16 - rowshift)) & keep,
+                       o2 = (four.y << rowshift) & keep, o3 = (four.y >> (16 - rowshift)) & keep;
+        tile_and_rows(r0, t0 + o0, t0 + o1);
+        if (two) tile_and_rows(r1, t1 + o0, t1 + o1);
+        tile_and_rows(r0, t0 + o2, t0 + o3);
+        if (two) tile_and_rows(r1, t1 + o2, t1 + o3);
     }
 }
 
@@ -280,8 +265,8 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
     unsigned char *pflag = gquad + ((a.gmax + 3) & ~3);             // [TN] slot's message row has bits
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kTileThreads / 32;
     const unsigned bar = smem_u32(mbar_mem);
-    int *surv_c = a.surv_c + (size_t)blockIdx.x * 2 * ((Q + 1) >> 1) * m.C;          // [2][quad pairs][C]
-    uint4 *surv_r = a.surv_r + (size_t)blockIdx.x * 4 * ((Q + 1) >> 1) * m.C;        // two quads per entry
+    const int cblocks = (m.C + 31) >> 5;                                                // blocks of 32 clauses
+    uint4 *surv_r = a.surv_r + (size_t)blockIdx.x * 4 * ((Q + 1) >> 1) * m.C;         // [2][quad pairs][C][2 quads]
     const size_t x_words = (size_t)g.total_nodes * m.L0;
 
     if (tid == 0) mbar_init(bar, 1);
@@ -360,10 +345,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
             }
             __syncthreads();                          // the staging buffer is rewritten by the next round
         }
-        for (int j = tid; j < TNC; j += kTileThreads) {
-            bufA[(size_t)(32 * m.L0) * TNC + j] = kFull;
-            bufA[(size_t)(32 * m.L0 + 1) * TNC + j] = 0u;
-        }
+        for (int t = tid; t < kTilePadRows * TNC; t += kTileThreads) bufA[(size_t)(32 * m.L0) * TNC + t] = kFull;   // padding rows
         for (int j = warp; j < TNC; j += nwarps) {
             const u32 nd = tnode[32 * j + lane];
             const u32 ty = nd != ~0u ? g.node_type[nd] : ~0u;
@@ -413,27 +395,34 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                     if (lane < m.K) atomicAdd(&sums[gl * KP + lane], mine);
                 }
             };
-            // one warp pass: lanes hold (clause, node bits on the quads of pair u) as they were before the layer
-            auto pass = [&](int c, uint4 ra, uint4 rb, int u) {
+            // one warp pass over the 32 clauses at positions 32*block .. 32*block+31 of the layer's order (c: the lane's
+            // clause, -1: none) and the quads of pair u; ra / rb are the node bits as they were before the layer
+            auto pass = [&](int block, int c, uint4 ra, uint4 rb, int u) {
                 const int qa = 2 * u;
                 const bool two = qa + 1 < Q;
-                if (c >= 0) {
-                    const int packed = L.cnt[c];
-                    tile_eval(ra, rb, reinterpret_cast<const uint2 *>(L.list) + L.blk_off[c >> 5] + (c & 31), packed & 0xffff,
-                              packed >> 16, t32 + qa * 16, rowshift, two);
+                {
+                    const bool flip = two && (lane & 4);                  // lanes 4..7 of every eight take the second quad first
+                    const unsigned ta = t32 + qa * 16;
+                    uint4 r0 = flip ? rb : ra, r1 = flip ? ra : rb;
+                    const unsigned pad = (unsigned)tile_literal_rows(d, m.L0, m.MW);     // padding rows of classes lane, lane+1, ..
+                    const uint2 pad4 = make_uint2((pad + (lane & 3)) | ((pad + ((lane + 1) & 3)) << 16),
+                                                  (pad + ((lane + 2) & 3)) | ((pad + ((lane + 3) & 3)) << 16));
+                    tile_eval(r0, r1, reinterpret_cast<const uint2 *>(L.list) + L.blk_off[block] + lane, c >= 0 ? L.cnt[c] : 0, pad4,
+                              flip ? ta + 16 : ta, flip ? ta : ta + 16, rowshift, two);
+                    ra = flip ? r1 : r0;
+                    rb = flip ? r0 : r1;
                 }
                 const bool alive = (ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) != 0;
                 const u32 amask = __ballot_sync(kFull, alive);
-                if (amask == 0) return;
                 if (!last) {
-                    int base = 0;
-                    if (lane == 0) base = atomicAdd(&cnt[wr * 8 + u], __popc(amask));
-                    base = __shfl_sync(kFull, base, 0);
-                    if (alive) {
-                        const size_t at = (size_t)(wr * U + u) * m.C + base + __popc(amask & ((1u << lane) - 1u));
-                        surv_c[at] = c;
+                    // every clause's node bits (zeros included) for the next layer, which takes the clauses in its own order
+                    if (c >= 0) {
+                        const size_t at = (size_t)(wr * U + u) * m.C + c;
                         surv_r[2 * at] = ra;
                         surv_r[2 * at + 1] = rb;
+                    }
+                    if (amask != 0 && lane == 0) atomicAdd(&cnt[wr * 8 + u], __popc(amask));
+                    if (alive) {
                         // the clause's hypervector bits on every node it is true on (the SOURCE side of kernels.py:571-588):
                         // in the bit-major buffer that is one 128-bit OR per hypervector bit and quad
                         for (int b = 0; b < m.MB; ++b) {
@@ -442,7 +431,7 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                             if (two) mark(row + 4, rb);
                         }
                     }
-                } else {
+                } else if (amask != 0) {
                     int w[KP];
 #pragma unroll
                     for (int k = 0; k < KP; ++k) w[k] = 0;
@@ -462,34 +451,31 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                 }
             };
 
-            if (d == 0) {
-                const int cblocks = (m.C + 31) >> 5;
-                for (int task = warp; task < cblocks * U; task += nwarps) {
-                    const int u = task % U;
-                    int c = (task / U) * 32 + lane;
-                    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
-                    if (c < m.C) {
+            for (int task = warp; task < cblocks * U; task += nwarps) {
+                const int u = task % U, block = task / U, p = block * 32 + lane;
+                const int c = p < m.C ? L.order[p] : -1;
+                uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+                if (c >= 0) {
+                    if (d == 0) {
                         const u32 *tm_row = TMV + (c % g.n_types) * TNC + 8 * u;
                         ra = *reinterpret_cast<const uint4 *>(tm_row);
                         if (2 * u + 1 < Q) rb = *reinterpret_cast<const uint4 *>(tm_row + 4);
-                    } else c = -1;
-                    pass(c, ra, rb, u);
-                }
-            } else {
-                for (int u = 0; u < U; ++u) {
-                    const int n_ent = cnt[rd * 8 + u];
-                    for (int base = warp * 32; base < n_ent; base += nwarps * 32) {
-                        int c = -1;
-                        uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
-                        if (base + lane < n_ent) {
-                            const size_t at = (size_t)(rd * U + u) * m.C + base + lane;
-                            c = surv_c[at];
-                            ra = surv_r[2 * at];
-                            rb = surv_r[2 * at + 1];
-                        }
-                        pass(c, ra, rb, u);
+                    } else {
+                        const size_t at = (size_t)(rd * U + u) * m.C + c;
+                        ra = surv_r[2 * at];
+                        rb = surv_r[2 * at + 1];
                     }
                 }
+                if (d > 0 && !__any_sync(kFull, (ra.x | ra.y | ra.z | ra.w | rb.x | rb.y | rb.z | rb.w) != 0)) {
+                    // none of these clauses was true anywhere after the layer below: they stay false
+                    if (!last && c >= 0) {
+                        const size_t at = (size_t)(wr * U + u) * m.C + c;
+                        surv_r[2 * at] = ra;
+                        surv_r[2 * at + 1] = rb;
+                    }
+                    continue;
+                }
+                pass(block, c, ra, rb, u);
             }
             __syncthreads();
             if (last) break;
@@ -538,7 +524,8 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                 }
             }
             __syncthreads();
-            // (4) destination rows, node-major in bufB -> literal rows of the next layer, bit-major in bufA
+            // (4) destination rows, node-major in bufB -> literal rows of the next layer, bit-major in bufA: the message
+            //     bits and, 32*MW rows further, their complements (the negated message literals)
             for (int blk = tid; blk < TNC * m.MW; blk += kTileThreads) {
                 const int j = blk % TNC, w = blk / TNC, rot = (a.rot_step * j) & 31;
                 u32 rows[32];
@@ -546,12 +533,13 @@ __global__ void __launch_bounds__(kTileThreads, 2) tile_score_kernel(DevModel m,
                 for (int i = 0; i < 32; ++i) rows[i] = bufB[(size_t)(32 * j + ((i + rot) & 31)) * PS + w];
                 transpose32(rows);
 #pragma unroll
-                for (int b = 0; b < 32; ++b) bufA[(size_t)(b * m.MW + w) * TNC + j] = __funnelshift_l(rows[b], rows[b], rot);
+                for (int b = 0; b < 32; ++b) {
+                    const u32 x = __funnelshift_l(rows[b], rows[b], rot);
+                    bufA[(size_t)(b * m.MW + w) * TNC + j] = x;
+                    bufA[(size_t)(32 * m.MW + b * m.MW + w) * TNC + j] = ~x;
+                }
             }
-            for (int j = tid; j < TNC; j += kTileThreads) {
-                bufA[(size_t)(32 * m.MW) * TNC + j] = kFull;
-                bufA[(size_t)(32 * m.MW + 1) * TNC + j] = 0u;
-            }
+            for (int t = tid; t < kTilePadRows * TNC; t += kTileThreads) bufA[(size_t)(64 * m.MW) * TNC + t] = kFull;
             __syncthreads();
             // (5) bufB is the mark buffer of the next layer, if that one sends messages too
             if (d + 1 < m.D - 1) {
@@ -593,16 +581,16 @@ int tile_model_create(TileModel *tm, const DevModel &d)
     tm->applicable = false;
     tm->D = d.D;
     if (d.K > kTileMaxK) return GTM_OK;
-    if (32 * (size_t)std::max(d.L0, d.D > 1 ? d.MW : 0) + 2 > 65535) return GTM_OK;     // row numbers are 16 bits
+    if ((size_t)std::max(32 * d.L0, d.D > 1 ? 64 * d.MW : 0) + kTilePadRows > 65535) return GTM_OK;   // row numbers are 16 bits
     tm->KROW = tile_krow(d.K);
     GTM_TRY(dev_alloc(&tm->Wt, (size_t)d.C * tm->KROW));
     GTM_TRY(dev_alloc(&tm->hvm, (size_t)d.C * d.MB));
     GTM_TRY(dev_alloc(&tm->layers, (size_t)d.D));
     for (int l = 0; l < d.D; ++l) {
         GTM_TRY(dev_alloc(&tm->cnt[l], (size_t)d.C));
+        GTM_TRY(dev_alloc(&tm->order[l], (size_t)d.C));
         GTM_TRY(dev_alloc(&tm->blk_off[l], (size_t)((d.C + 31) / 32) + 1));
     }
-    GTM_CU(cudaMallocHost((void **)&tm->total_host, sizeof(int)));
     tm->applicable = true;
     return GTM_OK;
 }
@@ -610,24 +598,34 @@ int tile_model_create(TileModel *tm, const DevModel &d)
 void tile_model_destroy(TileModel *tm)
 {
     cudaFree(tm->Wt); cudaFree(tm->hvm); cudaFree(tm->layers);
-    for (int l = 0; l < kMaxDepth; ++l) { cudaFree(tm->cnt[l]); cudaFree(tm->blk_off[l]); cudaFree(tm->list[l]); }
-    if (tm->total_host) cudaFreeHost(tm->total_host);
+    for (int l = 0; l < kMaxDepth; ++l) { cudaFree(tm->cnt[l]); cudaFree(tm->order[l]); cudaFree(tm->blk_off[l]); cudaFree(tm->list[l]); }
     *tm = TileModel();
 }
 
-// Rebuilds the included-literal lists of every layer (and the clause-major weights) from the current state.  The list
-// buffers grow to the length the state needs, which takes one host round trip per layer.
+// Rebuilds the included-literal lists of every layer (and the clause-major weights) from the current state: list
+// lengths on the device, the order of the clauses (by decreasing length) and the block offsets on the host, the lists
+// on the device.  One host round trip per layer; the list buffers grow to the length the state needs.
 int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s)
 {
     if (!tm->applicable) return GTM_OK;
-    const int blocks = (d.C + 255) / 256;
+    const int blocks = (d.C + 255) / 256, cblocks = (d.C + 31) / 32;
     TileLayer host_layers[kMaxDepth];
+    std::vector<int> cnt((size_t)d.C), order((size_t)d.C), blk_off((size_t)cblocks + 1);
     for (int l = 0; l < d.D; ++l) {
         tile_count_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt[l]);
-        tile_block_offsets_kernel<<<1, 1024, 0, s>>>(tm->cnt[l], d.C, tm->blk_off[l], tm->total_host);
         GTM_CU(cudaGetLastError());
+        GTM_CU(cudaMemcpyAsync(cnt.data(), tm->cnt[l], (size_t)d.C * sizeof(int), cudaMemcpyDeviceToHost, s));
         GTM_CU(cudaStreamSynchronize(s));
-        const size_t need = 4 * (size_t)*tm->total_host + 8;          // 16-bit row numbers, four per element
+        for (int c = 0; c < d.C; ++c) order[(size_t)c] = c;
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cnt[(size_t)x] > cnt[(size_t)y]; });
+        size_t total = 0;
+        for (int b = 0; b < cblocks; ++b) {           // the first clause of a block has its longest list
+            blk_off[(size_t)b] = (int)total;
+            total += (size_t)32 * cnt[(size_t)order[(size_t)b * 32]];
+        }
+        blk_off[(size_t)cblocks] = (int)total;
+        if (total * 4 + 8 >= ((size_t)1 << 31)) return fail(GTM_ERR_ARG, "included-literal lists of layer %d are too long for the tile scoring kernel", l);
+        const size_t need = 4 * total + 8;            // 16-bit row numbers, four per element
         if (need > tm->list_cap[l]) {
             cudaFree(tm->list[l]);
             tm->list[l] = nullptr;
@@ -636,8 +634,12 @@ int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s)
             GTM_TRY(dev_alloc(&tm->list[l], cap));
             tm->list_cap[l] = cap;
         }
-        tile_fill_kernel<<<blocks, 256, 0, s>>>(d, l, tm->cnt[l], tm->blk_off[l], tm->list[l], tm->Wt, tm->KROW, tm->hvm);
+        GTM_CU(cudaMemcpyAsync(tm->order[l], order.data(), (size_t)d.C * sizeof(int), cudaMemcpyHostToDevice, s));
+        GTM_CU(cudaMemcpyAsync(tm->blk_off[l], blk_off.data(), blk_off.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+        tile_fill_kernel<<<blocks, 256, 0, s>>>(d, l, tm->order[l], tm->cnt[l], tm->blk_off[l], tm->list[l], tm->Wt, tm->KROW, tm->hvm);
         GTM_CU(cudaGetLastError());
+        GTM_CU(cudaStreamSynchronize(s));             // `order` and `blk_off` are reused for the next layer
+        host_layers[l].order = tm->order[l];
         host_layers[l].cnt = tm->cnt[l];
         host_layers[l].blk_off = tm->blk_off[l];
         host_layers[l].list = tm->list[l];
@@ -655,13 +657,14 @@ static TilePlan tile_plan(const DevModel &d, int TNC, int gmax)
     TilePlan p;
     const int TN = TNC * 32;
     p.PS = d.MW | 1;
-    const size_t xt = (size_t)(32 * d.L0 + 2) * TNC;
-    // node-major message rows / bit-major message rows (+ the all-ones and all-zeros rows)
-    const size_t pm = d.D > 1 ? (size_t)TN * p.PS : 0, pt = d.D > 1 ? (size_t)(32 * d.MW + 2) * TNC : 0;
+    const size_t xt = (size_t)(32 * d.L0 + kTilePadRows) * TNC;
+    // node-major message rows / bit-major message rows with their complements and the padding rows / mark buffer
+    const size_t pm = d.D > 1 ? (size_t)TN * p.PS : 0, pt = d.D > 1 ? (size_t)(64 * d.MW + kTilePadRows) * TNC : 0;
+    const size_t marks = d.D > 1 ? (size_t)32 * d.MW * TNC : 0;
     // staging: whole groups of 32 literal rows, up to 16 KB (or whatever the message rows need anyway), + 8 words of slack
     size_t stage = (size_t)32 * d.L0 * std::max<size_t>(1, std::min<size_t>(TNC, 4096 / ((size_t)32 * d.L0))) + 8;
     const size_t wa = (std::max(xt, std::max(pm, pt)) + 3) & ~(size_t)3;
-    const size_t wb = (std::max(stage, std::max(pm, pt)) + 3) & ~(size_t)3;
+    const size_t wb = (std::max(stage, std::max(pm, marks)) + 3) & ~(size_t)3;
     p.words_a = (int)wa;
     p.words_b = (int)wb;
     p.stage_rows = (int)std::min<size_t>(TN, ((wb - 8) / d.L0) / 32 * 32);
@@ -671,16 +674,20 @@ static TilePlan tile_plan(const DevModel &d, int TNC, int gmax)
     return p;
 }
 
-int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const gtm_graphs_view *v, int sm_count, cudaStream_t s)
+// n_min / n_max: node counts of the smallest and the largest graph when the caller knows them (0, 0 otherwise).
+int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const gtm_graphs_view *v, u32 n_min, u32 n_max,
+                     int sm_count, cudaStream_t s)
 {
     td->supported = 0;
     if (!tm.applicable || v->max_number_of_graph_nodes > kQuadNodes) return GTM_OK;    // a graph must fit one quad
     const int64_t N = v->number_of_graphs;
-    u32 n_min = ~0u, n_max = 0;
-    for (int64_t gi = 0; gi < N; ++gi) {
-        const u32 n = v->number_of_graph_nodes[gi];
-        n_min = std::min(n_min, n);
-        n_max = std::max(n_max, n);
+    if (n_max == 0) {
+        n_min = ~0u;
+        for (int64_t gi = 0; gi < N; ++gi) {
+            const u32 n = v->number_of_graph_nodes[gi];
+            n_min = std::min(n_min, n);
+            n_max = std::max(n_max, n);
+        }
     }
     if (n_min < 1 || n_max > (u32)kQuadNodes) return GTM_OK;
     const void *fn = tile_kernel_for(d.K);
@@ -688,7 +695,9 @@ int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const
     int TNC = 0;
     TilePlan plan;
     for (int pass = 0; pass < 2 && TNC == 0; ++pass)
-        for (int cand = 32; cand >= 4; cand >>= 1) {
+        // models with many clauses spend their time in the evaluation, whose shared-memory loads are free of bank
+        // conflicts with 32-byte rows (8 node words, see tile_count_kernel); small ones gain more from large tiles
+        for (int cand = d.C >= 256 ? 8 : 32; cand >= 4; cand >>= 1) {
             const int gbound = (int)std::min<int64_t>(kTileMaxGraphs, std::min<int64_t>(N, cand * 32 / n_min));
             const TilePlan p = tile_plan(d, cand, gbound);
             if (p.bytes <= (pass == 0 ? (size_t)112 * 1024 : (size_t)224 * 1024)) { TNC = cand; plan = p; break; }
@@ -758,9 +767,8 @@ void tile_data_destroy(TileData *td)
     if (td->tile_graph) cudaFreeAsync(td->tile_graph, td->stream);
     if (td->gpos) cudaFreeAsync(td->gpos, td->stream);
     if (td->tile_counter) cudaFreeAsync(td->tile_counter, td->stream);
-    if (td->surv_c) cudaFreeAsync(td->surv_c, td->stream);
     if (td->surv_r) cudaFreeAsync(td->surv_r, td->stream);
-    td->tile_graph = nullptr; td->gpos = nullptr; td->tile_counter = nullptr; td->surv_c = nullptr; td->surv_r = nullptr;
+    td->tile_graph = nullptr; td->gpos = nullptr; td->tile_counter = nullptr; td->surv_r = nullptr;
     td->supported = 0;
 }
 
@@ -770,11 +778,8 @@ int tile_score(const TileModel &tm, TileData &td, const DevModel &d, const DevGr
                int64_t count, int *sums_dev, int *error_dev, cudaStream_t s)
 {
     const int U = (td.TNC / 4 + 1) / 2;
-    if (!td.surv_c) {          // survivor lists: one pair per resident CTA, allocated on first use
-        const size_t entries = (size_t)td.grid * 2 * U * d.C;
-        GTM_TRY(pool_alloc(&td.surv_c, entries, s));
-        GTM_TRY(pool_alloc(&td.surv_r, 2 * entries, s));
-    }
+    if (!td.surv_r)            // node bits of every clause between layers, per resident CTA, layer parity and quad pair; allocated on first use
+        GTM_TRY(pool_alloc(&td.surv_r, 2 * (size_t)td.grid * 2 * U * d.C, s));
     DevGraphs g = dg;
     g.n_types = n_types;
     TileArgs a;
@@ -799,7 +804,7 @@ int tile_score(const TileModel &tm, TileData &td, const DevModel &d, const DevGr
     while ((td.PS * inv) % 32 != 1) inv += 2;
     a.rot_step = ((32 / td.TNC) * inv) & 31;
     a.layers = tm.layers; a.Wt = tm.Wt; a.KROW = tm.KROW; a.hvm = tm.hvm;
-    a.surv_c = td.surv_c; a.surv_r = td.surv_r;
+    a.surv_r = td.surv_r;
     a.error = error_dev;
     GTM_CU(cudaMemsetAsync(td.tile_counter, 0, sizeof(unsigned), s));
     const int grid = std::max(1, std::min(td.grid, hi - lo));

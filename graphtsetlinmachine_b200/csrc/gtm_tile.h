@@ -8,25 +8,27 @@
 
 namespace gtm {
 
-// One layer's included-literal lists as the kernel reads them (device memory).  The lists of 32 consecutive clauses
-// are interleaved: group g (four 16-bit row numbers, 8 bytes) of clause c is element blk_off[c / 32] + 32 * g + c % 32.
+// One layer's included-literal lists as the kernel reads them (device memory).  Clauses are taken in the layer's own
+// order (by decreasing list length); the lists of the 32 clauses of a block of positions are interleaved: group g
+// (four 16-bit row numbers, 8 bytes) of position p is element blk_off[p / 32] + 32 * g + p % 32.
 struct TileLayer {
-    const int *cnt;               // [C] groups tested as they are | groups tested complemented << 16 (negated message literals)
-    const int *blk_off;           // [ceil(C/32)+1] first element of every block of 32 clauses
-    const unsigned short *list;   // row numbers in the transposed tile buffer, padded with the all-ones / all-zeros row
+    const int *order;             // [C] clause at every position
+    const int *cnt;               // [C] list length of every CLAUSE in groups of four rows
+    const int *blk_off;           // [ceil(C/32)+1] first element of every block of 32 positions
+    const unsigned short *list;   // row numbers in the transposed tile buffer, padded with rows of ones
 };
 
 struct TileModel {
     bool applicable = false;
     int D = 0, KROW = 0;
     int *cnt[kMaxDepth] = {};
+    int *order[kMaxDepth] = {};
     int *blk_off[kMaxDepth] = {};
     unsigned short *list[kMaxDepth] = {};
     size_t list_cap[kMaxDepth] = {};
     int *Wt = nullptr;            // [C][KROW] weights, clause-major
     u32 *hvm = nullptr;           // [C][MB] hypervector bits reduced modulo the message size
     TileLayer *layers = nullptr;  // [D] device copy of the pointers above
-    int *total_host = nullptr;    // page-locked: list length of the layer being rebuilt
 };
 
 struct TileData {
@@ -43,8 +45,7 @@ struct TileData {
     unsigned short *gpos = nullptr;     // [N] first node slot of every graph inside its tile (NULL for uniform sets)
     std::vector<int> tile_graph_host;
     unsigned *tile_counter = nullptr;
-    int *surv_c = nullptr;              // [grid][2][quad pairs][C] clauses still true after a layer ...
-    uint4 *surv_r = nullptr;            //                          ... and their node bits on the pair's two quads
+    uint4 *surv_r = nullptr;            // [grid][2][quad pairs][C][2] node bits of every clause on the pair's two quads after a layer
     cudaStream_t stream = nullptr;
     int grid = 0;
     size_t smem = 0;
@@ -54,7 +55,8 @@ struct TileData {
 int tile_model_create(TileModel *tm, const DevModel &d);
 void tile_model_destroy(TileModel *tm);
 int tile_model_refresh(TileModel *tm, const DevModel &d, cudaStream_t s);
-int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const gtm_graphs_view *v, int sm_count, cudaStream_t s);
+int tile_data_create(TileData *td, const TileModel &tm, const DevModel &d, const gtm_graphs_view *v, u32 n_min, u32 n_max,
+                     int sm_count, cudaStream_t s);
 void tile_data_destroy(TileData *td);
 bool tile_supported(const TileData &td, int n_types);
 int tile_score(const TileModel &tm, TileData &td, const DevModel &d, const DevGraphs &dg, int n_types, int64_t first,

@@ -91,6 +91,13 @@ int gtm_set_stream(gtm_model *model, void *cuda_stream);
  *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel (depth 1), 3 = tile kernel (any depth,
  *                   graphs of at most 128 nodes); set it before the graph set is created
  *   "fit_timers":   1 = the learning kernels time their phases for gtm_debug_fit_phase_cycles (default 0)
+ *   "fit_wait_ms":  wall-time budget of ONE device-side wait of the learning kernels (grid barrier, vote exchange between
+ *                   thread blocks or GPUs), 1..600000 ms, default 2000.  A wait that runs out ends the launch; gtm_fit
+ *                   returns GTM_ERR_TIMEOUT, the CUDA context stays usable.  The state-resident kernel leaves the model as
+ *                   it was before the call; otherwise part of the call's updates may have been applied - restore a
+ *                   checkpoint (gtm_set_ta_state / gtm_set_weights / gtm_set_draw_positions) before learning on.
+ *   "fit_missing_cta": test hook, 1 = every wait of later gtm_fit calls expects one arrival more than there are thread
+ *                   blocks, i.e. a participant that never shows up: the waits run out (default 0)
  * Forcing a kernel that cannot serve the model makes the next fit / score call fail with GTM_ERR_ARG. */
 int gtm_set_option(gtm_model *model, const char *name, int value);
 

@@ -17,6 +17,8 @@ CONFIGS = {
                         message_bits=2),
     # a 33..1,024-node shape for the transposed evaluation (tests/test_gpu_reference_kernels.py)
     "mid_graphs": dict(classes=3, clauses=300, literals=128, threshold=150, max_nodes=200, message_size=128, message_bits=2),
+    # a single-output model (GraphTsetlinMachine class, tests/test_gpu_api.py)
+    "single_output": dict(classes=1, clauses=20, literals=64, threshold=20, max_nodes=5, message_size=64, message_bits=2),
     # small differential-test sets (tests/cases.py)
     "case_a": dict(classes=2, clauses=20, literals=64, threshold=20, max_nodes=5, message_size=64, message_bits=2),
     "case_b": dict(classes=3, clauses=33, literals=80, threshold=30, max_nodes=40, message_size=50, message_bits=2,

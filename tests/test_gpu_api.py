@@ -146,3 +146,91 @@ def test_pipelined_scoring_equals_resident_scoring(engine_lib):
     tm2.fit(other, y2, epochs=1, incremental=True)
     a = tm2.score(other).copy()
     assert np.array_equal(a, tm2.score(other))
+
+
+def _case_model(cls, name, **extra):
+    """A model class instance shaped like differential-test case `name`, its graphs and labels, and the reference's
+    kernels (host build) with the same hypervectors and draw streams."""
+    from cases import CASES, make_case
+    from oracle.ref_tm import RefTM
+
+    kw, graphs, encY, _ = make_case(name)
+    if build_ref.build(dict({k: v for k, v in kw.items() if k in ("classes", "clauses", "literals", "state_bits", "boost", "q",
+                             "max_included", "max_nodes", "message_size", "message_bits")}, threshold=kw["threshold"])) is None:
+        pytest.skip("prebuilt host version of the reference kernels did not travel")
+    np.random.seed(17)
+    tm = cls(kw["clauses"], kw["threshold"], kw["s"], depth=kw["depth"], message_size=kw["message_size"],
+             message_bits=kw["message_bits"], max_included_literals=kw.get("max_included"),
+             boost_true_positive_feedback=kw.get("boost", 1), number_of_state_bits=kw.get("state_bits", 8),
+             q=kw.get("q", 1.0), seed=23, **extra)
+    ref = RefTM(**dict(kw, hypervectors=tm.hypervectors, seed=23))
+    return tm, ref, kw, graphs, encY
+
+
+def test_introspection_and_transforms_match_reference_kernels(engine_lib):
+    """get_ta_states / get_hyperliterals (kernels.py:718-796), transform (kernels.py:671-691) and transform_nodewise
+    (kernels.py:693-709) against the reference's own kernels, from the same trained state: depth 3, 40-node graphs, two
+    node types, message size 50 (not a multiple of 32)."""
+    tm, ref, kw, graphs, encY = _case_model(MultiClassGraphTsetlinMachine, "case_b")
+    Y = encY.argmax(axis=1).astype(np.uint32)
+    Y[0], Y[1], Y[2] = 0, 1, 2                                   # every class present: the model sizes its outputs from max(Y)
+    enc = np.where(Y[:, None] == np.arange(kw["classes"])[None, :], kw["threshold"], -kw["threshold"]).astype(np.int32)
+    ref.set_graphs(graphs)
+    ref.prepare()
+    for _ in range(3):
+        tm.fit(graphs, Y, epochs=1, incremental=True)
+        ref.fit(enc)
+    assert np.array_equal(tm.score(graphs), ref.score())
+    for layer in range(kw["depth"]):
+        assert np.array_equal(tm.get_ta_states(layer), ref.get_ta_states(layer)), "automaton states, layer %d" % layer
+        assert np.array_equal(tm.get_hyperliterals(layer), ref.get_hyperliterals(layer)), "include actions, layer %d" % layer
+    assert np.array_equal(tm.get_weights(), ref.clause_weights)
+    co, cs = tm.transform(graphs)
+    nodewise, cs2 = tm.transform_nodewise(graphs)
+    assert np.array_equal(cs, ref.score()) and np.array_equal(cs2, cs)
+    for e in range(graphs.number_of_graphs):
+        n = int(graphs.number_of_graph_nodes[e])
+        assert np.array_equal(co[e], ref.transform_graph(e)), "clause outputs, graph %d" % e
+        assert np.array_equal(nodewise[e, :, :n], ref.transform_graph(e, nodewise=True)), "per-node outputs, graph %d" % e
+        assert not nodewise[e, :, n:].any()
+    assert co.any() and nodewise.any()
+
+
+def test_multi_output_and_single_output_classes_match_reference_kernels(engine_lib):
+    """MultiOutputGraphTsetlinMachine (tm.py:961-1017) and GraphTsetlinMachine (tm.py:1019-1072): label encoding, raw sums
+    and thresholded predictions against the reference's kernels driven with the same targets and draws."""
+    tm, ref, kw, graphs, encY = _case_model(MultiOutputGraphTsetlinMachine, "case_b")
+    rng = np.random.default_rng(5)
+    Y = rng.integers(0, 2, size=(graphs.number_of_graphs, kw["classes"])).astype(np.uint32)
+    enc = np.where(Y == 1, kw["threshold"], -kw["threshold"]).astype(np.int32)
+    ref.set_graphs(graphs)
+    ref.prepare()
+    for _ in range(2):
+        tm.fit(graphs, Y, epochs=1, incremental=True)
+        ref.fit(enc)
+    want = ref.score()
+    assert np.array_equal(tm.score(graphs), want)
+    assert np.array_equal(tm.predict(graphs), (want >= 0).astype(np.uint32))
+    assert np.array_equal(tm.get_state()[0].reshape(ref.ta_state.shape), ref.ta_state)
+
+    from oracle.ref_tm import RefTM
+    from util import random_graphs
+
+    params = dict(classes=1, clauses=20, literals=64, threshold=20, max_nodes=5, message_size=64, message_bits=2)
+    if build_ref.build(params) is None:
+        pytest.skip("prebuilt host version of the reference kernels did not travel")
+    np.random.seed(31)
+    g = random_graphs(80, np.random.default_rng(31), hv_size=32, max_nodes=5, edge_types=2)
+    y = np.random.default_rng(32).integers(0, 2, size=80).astype(np.uint32)
+    single = GraphTsetlinMachine(20, 20, 1.5, depth=2, message_size=64, message_bits=2, seed=29)
+    ref1 = RefTM(clauses=20, classes=1, literals=64, threshold=20, s=1.5, depth=2, message_size=64, message_bits=2,
+                 max_nodes=5, hypervectors=single.hypervectors, seed=29)
+    ref1.set_graphs(g)
+    ref1.prepare()
+    single.fit(g, y)                                             # the class runs the reference's default of 100 epochs (tm.py:1065)
+    enc1 = np.where(y == 1, 20, -20).astype(np.int32).reshape(-1, 1)
+    for _ in range(100):
+        ref1.fit(enc1)
+    want1 = ref1.score()[:, 0]
+    assert np.array_equal(single.score(g), want1)
+    assert np.array_equal(single.predict(g), want1 >= 0)

@@ -217,3 +217,42 @@ def test_node_stream_scoring(engine_lib, shape):
     for first, count in [(1, 1), (n // 3, n // 2), (n - 5, 5), (0, n - 1)]:
         assert np.array_equal(want[first:first + count], b.score(first, count)), "sub-range"
     b.close()
+
+
+def test_wait_that_runs_out_ends_the_launch_cleanly(engine_lib):
+    """Failure path of the learning kernels without a faulted GPU: with the test hook `fit_missing_cta` every device-side
+    wait expects an arrival that never comes (a thread block, or on several GPUs a rank, that does not show up).  The
+    waits are bounded by wall time, so the launch ends by itself, gtm_fit reports GTM_ERR_TIMEOUT, the CUDA context stays
+    usable, and after restoring the state the same model learns on, bit for bit like the checker."""
+    import ctypes as C
+    import time
+
+    from graphtsetlinmachine_b200 import _lib
+    from oracle.oracle import OracleTM
+
+    for name, fit_kernel in (("case_d", 0), ("case_b", 1), ("case_b", 2)):
+        kw, graphs, encY, _ = make_case(name)
+        kw = dict(kw, clauses=400)                       # several thread blocks, so that there is something to wait for
+        rng = np.random.default_rng(3)
+        kw["hypervectors"] = np.stack([rng.choice(kw["message_size"], size=kw["message_bits"], replace=False)
+                                       for _ in range(400)]).astype(np.uint32)
+        cpu, gpu = OracleTM(**kw), EngineTM(**kw, options={"fit_kernel": fit_kernel})
+        for tm in (cpu, gpu):
+            tm.set_graphs(graphs)
+            tm.prepare()
+            tm.fit(encY)
+        assert_same_state(cpu, gpu, kw["depth"], "before the failed launch")
+        _lib.check(engine_lib.gtm_set_option(gpu.model, b"fit_wait_ms", 30))
+        _lib.check(engine_lib.gtm_set_option(gpu.model, b"fit_missing_cta", 1))
+        t0 = time.perf_counter()
+        with pytest.raises(_lib.GtmError) as err:
+            gpu.fit(encY)
+        assert err.value.status == 4 and time.perf_counter() - t0 < 5.0          # GTM_ERR_TIMEOUT, promptly
+        _lib.check(engine_lib.gtm_set_option(gpu.model, b"fit_missing_cta", 0))
+        _lib.check(engine_lib.gtm_set_option(gpu.model, b"fit_wait_ms", 2000))
+        gpu.load_from(cpu)                                # restore the checkpoint (a global-state launch may have applied updates)
+        for tm in (cpu, gpu):
+            tm.fit(encY)
+        assert_same_state(cpu, gpu, kw["depth"], "after the failed launch")
+        assert np.array_equal(cpu.score(), gpu.score())
+        gpu.close()
