@@ -425,6 +425,8 @@ def run_config(idx, ctx, steps, warmup, headline):
     K, T = cfg["classes"], cfg["model"]["T"]
     depth = cfg["model"].get("depth", 1)
     t_cfg = time.perf_counter()
+    if args.fit_graphs > 0 or args.batch_graphs > 0:         # reduced sizes for captures under a profiler
+        cfg = dict(cfg, train=args.fit_graphs or cfg["train"], unique=args.batch_graphs or cfg["unique"])
     train, y_train, unique = build_sets(idx, cfg["train"], cfg["unique"])
     max_nodes = int(max(train.max_number_of_graph_nodes, unique.max_number_of_graph_nodes))
 
@@ -606,6 +608,9 @@ def main():
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--configs", default="1,2,3,4,5", help="configurations to run besides the headline one")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--only", type=int, default=0, help="run this configuration alone and print its record (profiling runs)")
+    ap.add_argument("--fit-graphs", type=int, default=0, help="training sample size of every configuration (profiling runs)")
+    ap.add_argument("--batch-graphs", type=int, default=0, help="distinct graphs of every scoring batch (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -633,6 +638,13 @@ def main():
     int_peak = measure_logic_op_rate(lib, local_rank)
 
     ctx = dict(rank=rank, world=world, local_rank=local_rank, lib=lib, args=args, barrier=barrier, int_peak=int_peak)
+    if args.only:
+        rec = run_config(args.only, ctx, args.steps, args.warmup, False)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     wanted = sorted({int(c) for c in args.configs.split(",") if c.strip()} | {HEADLINE})
     records = {}
     for idx in wanted:

@@ -324,6 +324,22 @@ __global__ void graph_edge_ranges_kernel(const u32 *node_index, const u32 *n_nod
     }
 }
 
+// Fills graph_edge0 / graph_edges from the uploaded arrays (queued on the model's stream).
+static int derive_edge_ranges(gtm_dataset *ds, int64_t n_graphs)
+{
+    cudaStream_t s = ds->model->stream;
+    u32 *e0 = const_cast<u32 *>(ds->dg.graph_edge0), *ne = const_cast<u32 *>(ds->dg.graph_edges);
+    if (ds->total_edges == 0) {
+        GTM_CU(cudaMemsetAsync(e0, 0, (size_t)n_graphs * sizeof(u32), s));
+        GTM_CU(cudaMemsetAsync(ne, 0, (size_t)n_graphs * sizeof(u32), s));
+        return GTM_OK;
+    }
+    graph_edge_ranges_kernel<<<(unsigned)std::min<int64_t>((n_graphs + 255) / 256, 4096), 256, 0, s>>>(
+        ds->dg.node_index, ds->dg.n_nodes, ds->dg.edge_index, ds->dg.degree, n_graphs, e0, ne);
+    GTM_CU(cudaGetLastError());
+    return GTM_OK;
+}
+
 // Host arrays must have the layout that graphs.py produces: node_index and edge_index are exclusive prefix sums of the
 // node counts and out-degrees (graphs.py:101-102,127-128), every graph has 1..max_number_of_graph_nodes nodes.  The
 // kernels size their scratch rows from max_number_of_graph_nodes and index the arrays with these values, so anything
@@ -414,23 +430,16 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     GTM_TRY(upload(ds, &ds->dg.node_type, v->node_type, (size_t)v->total_nodes, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.degree, v->number_of_graph_node_edges, (size_t)v->total_nodes, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.edge_index, v->edge_index, (size_t)v->total_nodes, s, copy_arrays));
-    GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s));
+    GTM_TRY(upload(ds, &ds->dg.edge, v->edge, 2 * (size_t)v->total_edges, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.node_index, v->node_index, (size_t)v->number_of_graphs, s, copy_arrays));
     GTM_TRY(upload(ds, &ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)v->number_of_graphs, s, copy_arrays));
-    if (v->total_edges == 0) {
-        u32 *zeros;
-        GTM_TRY(scratch(ds, &zeros, (size_t)v->number_of_graphs));
-        GTM_CU(cudaMemsetAsync(zeros, 0, (size_t)v->number_of_graphs * sizeof(u32), s));
-        ds->dg.graph_edge0 = ds->dg.graph_edges = zeros;
-    } else {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows): derived on the device
+    {   // first edge row and number of edge rows of every graph (graphs own consecutive CSR rows): derived on the device
         u32 *e0, *ne;
         GTM_TRY(scratch(ds, &e0, (size_t)v->number_of_graphs));
         GTM_TRY(scratch(ds, &ne, (size_t)v->number_of_graphs));
-        graph_edge_ranges_kernel<<<(unsigned)std::min<int64_t>((v->number_of_graphs + 255) / 256, 4096), 256, 0, s>>>(
-            ds->dg.node_index, ds->dg.n_nodes, ds->dg.edge_index, ds->dg.degree, v->number_of_graphs, e0, ne);
-        GTM_CU(cudaGetLastError());
         ds->dg.graph_edge0 = e0;
         ds->dg.graph_edges = ne;
+        if (copy_arrays) GTM_TRY(derive_edge_ranges(ds, v->number_of_graphs));      // else: once the caller has copied the arrays
     }
     ds->dg.n_types = 1;
     ds->dg.total_nodes = (u32)v->total_nodes; ds->dg.total_edges = (u32)v->total_edges;
@@ -643,10 +652,12 @@ extern "C" int gtm_score(gtm_model *m, gtm_dataset *ds, int n_types, int64_t fir
     return score_flag_status(m, *m->flag_host);
 }
 
-// Upload and scoring of a whole host graph set in one call.  Sets of single-node graphs that the node-stream kernel
-// covers are pipelined: the arrays go up in chunks of two full waves of tiles on a copy stream, each chunk is scored as
-// soon as it has landed, and its class sums go back on a second copy stream while the next chunk is scored.  Other
-// sets take gtm_dataset_create followed by gtm_score.  The dataset stays valid for later calls either way.
+// Upload and scoring of a whole host graph set in one call.  Sets that the node-stream kernel or the tile kernel covers
+// are pipelined: the graph arrays go up in chunks of whole tiles (two full waves of thread blocks) on a copy stream - a
+// chunk is the literal rows, per-node arrays and edge rows of a contiguous range of graphs - each chunk is scored as soon
+// as it has landed, and its class sums go back on a second copy stream while the next chunk is scored.  Host arrays are
+// validated chunk by chunk, just before they are copied.  Other sets take gtm_dataset_create followed by gtm_score.
+// The dataset stays valid for later calls either way.
 extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v, int n_types, int32_t *out,
                                          gtm_dataset **dataset_out)
 {
@@ -655,14 +666,18 @@ extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v,
     *dataset_out = nullptr;
     if (!m->has_state) return fail(GTM_ERR_STATE, "model has no state: call gtm_init_state or gtm_set_ta_state first");
     if (n_types < 1) return fail(GTM_ERR_ARG, "number_of_node_types must be positive");
-    const bool pipelined = v->max_number_of_graph_nodes == 1 && v->total_edges == 0 && v->total_nodes == v->number_of_graphs &&
-                           m->opt_score_kernel != 1 && m->sm.lit_off != nullptr && n_types <= 8;   // what the node-stream kernel may cover; stream_supported decides
+    GTM_TRY(check_view(v));
+    // what a tiled kernel may cover; stream_supported / tile_supported decide once the tiles are made
+    const bool pipelined = m->opt_score_kernel != 1 && n_types <= 8 && v->max_number_of_graph_nodes <= 1024 &&
+                           (m->sm.lit_off != nullptr || m->tm.applicable);
     gtm_dataset *ds = nullptr;
     GTM_TRY(dataset_create(m, v, &ds, !pipelined));
     const int64_t n = ds->n_graphs;
     int st = GTM_OK;
-    if (!pipelined || !stream_supported(ds->sd, n_types) || ds->sd.graphs_per_tile <= 0) {
-        if (pipelined) {   // the arrays were not copied, but the node-stream kernel turned out not to cover the set
+    const bool by_stream = pipelined && (m->opt_score_kernel == 0 || m->opt_score_kernel == 2) && stream_supported(ds->sd, n_types);
+    const bool by_tile = pipelined && !by_stream && (m->opt_score_kernel == 0 || m->opt_score_kernel == 3) && tile_supported(ds->td, n_types);
+    if (!by_stream && !by_tile) {
+        if (pipelined) {   // the arrays were not copied, but no tiled kernel turned out to cover the set
             gtm_dataset_destroy(ds);
             ds = nullptr;
             GTM_TRY(dataset_create(m, v, &ds, true));
@@ -674,13 +689,23 @@ extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v,
     }
 
     const DevModel &d = m->dm;
+    // tiles of the kernel that will run: first graph of tile t
+    const int n_tiles = by_stream ? ds->sd.n_tiles : ds->td.n_tiles;
+    const int uniform_gpt = by_stream ? ds->sd.graphs_per_tile : ds->td.graphs_per_tile;
+    const std::vector<int> &table = by_stream ? ds->sd.tile_graph_host : ds->td.tile_graph_host;
+    auto tile_first = [&](int t) -> int64_t {
+        if (t >= n_tiles) return n;
+        return uniform_gpt > 0 ? std::min<int64_t>((int64_t)t * uniform_gpt, n) : (int64_t)table[(size_t)t];
+    };
+    const int chunk_tiles = std::max(1, 2 * (by_stream ? ds->sd.grid : ds->td.grid));
     cudaStream_t in = nullptr, back = nullptr;
     std::vector<cudaEvent_t> events;
     int *dev = nullptr;
     auto body = [&]() -> int {
         GTM_CU(cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking));
         GTM_CU(cudaStreamCreateWithFlags(&back, cudaStreamNonBlocking));
-        GTM_TRY(refresh_lists(m));
+        if (by_stream) GTM_TRY(refresh_lists(m));
+        else GTM_TRY(refresh_tile_lists(m));
         GTM_TRY(pool_alloc(&dev, (size_t)n * d.K, m->stream));
         auto event = [&](cudaStream_t s, cudaEvent_t *e) -> int {
             GTM_CU(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
@@ -688,34 +713,43 @@ extern "C" int gtm_dataset_create_scored(gtm_model *m, const gtm_graphs_view *v,
             GTM_CU(cudaEventRecord(*e, s));
             return GTM_OK;
         };
+        auto up = [&](const u32 *dst, const u32 *src, size_t first, size_t count) -> int {
+            if (count) GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(dst) + first, src + first, count * sizeof(u32), cudaMemcpyHostToDevice, in));
+            return GTM_OK;
+        };
         cudaEvent_t ready;
-        GTM_TRY(event(m->stream, &ready));                 // allocations and literal lists are in stream order
+        GTM_TRY(event(m->stream, &ready));                 // allocations, tile tables and literal lists are in stream order
         GTM_CU(cudaStreamWaitEvent(in, ready, 0));
-        const int64_t chunk = std::max<int64_t>(1, (int64_t)ds->sd.grid * 2) * ds->sd.graphs_per_tile;
-        for (int64_t g0 = 0; g0 < n; g0 += chunk) {
-            const size_t cnt = (size_t)std::min<int64_t>(chunk, n - g0);
-            GTM_TRY(validate_graphs(v, g0, g0 + (int64_t)cnt));     // overlaps the copies of the chunks before
-            // one node per graph: node ranges are graph ranges
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.X) + (size_t)g0 * d.L0, v->X + (size_t)g0 * d.L0, cnt * d.L0 * sizeof(u32), cudaMemcpyHostToDevice, in));
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.node_type) + g0, v->node_type + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.degree) + g0, v->number_of_graph_node_edges + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.edge_index) + g0, v->edge_index + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+        for (int t0 = 0; t0 < n_tiles; t0 += chunk_tiles) {
+            const int64_t g0 = tile_first(t0), g1 = tile_first(t0 + chunk_tiles);
+            if (g1 <= g0) continue;
+            GTM_TRY(validate_graphs(v, g0, g1));            // overlaps the copies of the chunks before
+            const size_t cnt = (size_t)(g1 - g0);
+            const size_t v0 = v->node_index[g0], v1 = g1 < n ? (size_t)v->node_index[g1] : (size_t)v->total_nodes;
+            const size_t e0 = v->edge_index[v0], e1 = v1 < (size_t)v->total_nodes ? (size_t)v->edge_index[v1] : (size_t)v->total_edges;
+            GTM_TRY(up(ds->dg.X, v->X, v0 * d.L0, (v1 - v0) * d.L0));
+            GTM_TRY(up(ds->dg.node_type, v->node_type, v0, v1 - v0));
+            GTM_TRY(up(ds->dg.degree, v->number_of_graph_node_edges, v0, v1 - v0));
+            GTM_TRY(up(ds->dg.edge_index, v->edge_index, v0, v1 - v0));
+            if (e1 > e0) GTM_TRY(up(ds->dg.edge, v->edge, 2 * e0, 2 * (e1 - e0)));
             // one element more: a tile ends where the next graph's nodes begin
-            const size_t cnt_index = cnt + (g0 + (int64_t)cnt < n ? 1 : 0);
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.node_index) + g0, v->node_index + g0, cnt_index * sizeof(u32), cudaMemcpyHostToDevice, in));
-            GTM_CU(cudaMemcpyAsync(const_cast<u32 *>(ds->dg.n_nodes) + g0, v->number_of_graph_nodes + g0, cnt * sizeof(u32), cudaMemcpyHostToDevice, in));
+            GTM_TRY(up(ds->dg.node_index, v->node_index, (size_t)g0, cnt + (g1 < n ? 1 : 0)));
+            GTM_TRY(up(ds->dg.n_nodes, v->number_of_graph_nodes, (size_t)g0, cnt));
             cudaEvent_t landed, scored;
             GTM_TRY(event(in, &landed));
             GTM_CU(cudaStreamWaitEvent(m->stream, landed, 0));
-            GTM_TRY(stream_score(m->sm, ds->sd, d, ds->dg, n_types, g0, (int64_t)cnt, dev + (size_t)g0 * d.K, m->stream));
+            if (by_stream) GTM_TRY(stream_score(m->sm, ds->sd, d, ds->dg, n_types, g0, (int64_t)cnt, dev + (size_t)g0 * d.K, m->stream));
+            else GTM_TRY(tile_score(m->tm, ds->td, d, ds->dg, n_types, g0, (int64_t)cnt, dev + (size_t)g0 * d.K, m->score_error, m->stream));
             GTM_TRY(event(m->stream, &scored));
             GTM_CU(cudaStreamWaitEvent(back, scored, 0));
             GTM_CU(cudaMemcpyAsync(out + (size_t)g0 * d.K, dev + (size_t)g0 * d.K, cnt * d.K * sizeof(int), cudaMemcpyDeviceToHost, back));
         }
+        GTM_TRY(derive_edge_ranges(ds, v->number_of_graphs));       // every array has been queued before this point of the stream
+        GTM_CU(cudaMemcpyAsync(m->flag_host, m->score_error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
         GTM_CU(cudaStreamSynchronize(in));
         GTM_CU(cudaStreamSynchronize(back));
         GTM_CU(cudaStreamSynchronize(m->stream));
-        return GTM_OK;
+        return score_flag_status(m, *m->flag_host);
     };
     st = body();
     if (st != GTM_OK) {                                    // nothing may still be reading the host arrays when the call returns

@@ -29,6 +29,7 @@ struct FitArgs {
     int timers;             // CTA 0 accumulates phase cycle counts (gtm_debug_fit_phase_cycles); off by default: the reads sit on the critical path
     int stage;              // the state-resident kernel has its two graph staging buffers (0: every graph is read in place)
     int part_words;         // > 0: shared-memory words per CTA that accumulate one layer's messages before they are merged
+    int gstage_words;       // global-state kernel: shared-memory words for a copy of the current (small) graph, 0 = none
     int solo;               // one CTA learns the whole model: CTA barriers replace the grid barrier and the vote exchange
     int p_smem_words;       // solo and depth > 1: message buffers (words per parity) live in that CTA's shared memory
     // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits
@@ -183,6 +184,9 @@ __device__ __forceinline__ void bernoulli_round(const DevModel &m, int clause, u
 #pragma unroll
     for (int i = 0; i < 4; ++i) words[i] = __shfl_sync(kFull, mine, 8 * i);
 }
+
+// Graph copy of the global-state learning kernel: literal rows, per-node arrays of up to 32 nodes, edge rows.
+constexpr int kFitStageRowWords = 2560, kFitStageEdges = 384;
 
 constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of up to 8 positive classes x 32 words + 1
 

@@ -532,7 +532,9 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         // one layer's messages are accumulated per CTA in shared memory when a layer takes at most 64 KB
         const size_t layer_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);
         a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 72 * 1024) ? (int)(layer_bytes / sizeof(u32)) : 0;
-        smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + (size_t)a.part_words * sizeof(u32);
+        // graph sets of at most 32 nodes per graph: the current graph (and the message rows a layer reads) in shared memory
+        a.gstage_words = (!eval_only && ds->max_nodes <= 32) ? kFitStageRowWords + 3 * 32 + 2 * kFitStageEdges + 32 * d.MW : 0;
+        smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + ((size_t)a.part_words + a.gstage_words) * sizeof(u32);
         if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &sc, &a, &eval_only};
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));

@@ -236,8 +236,10 @@ int gtm_debug_evaluate(gtm_model *model, gtm_dataset *dataset, int number_of_nod
 int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t *class_clause_update_out);
 
 /* Profiling tap (no counterpart in the reference): SM clock cycles that CTA 0 of the last gtm_fit launch spent in
- * its phases, uint64[8] = {clause evaluation, waiting at grid barriers, summing vote partials, end of step, and for the
- * state-resident kernel: decisions, work-item table, mask generation, automaton updates}.  Filled only by launches made
+ * its phases, uint64[8] = {clause evaluation, waiting at grid barriers, summing vote partials, end of step (feedback), and
+ * then for the state-resident kernel: decisions, work-item table, mask generation, automaton updates; for the
+ * global-state kernel: clause loops, message merge, graph / message-row copies (these three are then not part of the
+ * first figure), 0}.  Filled only by launches made
  * after gtm_set_option(model, "fit_timers", 1): the clock reads sit on the per-graph critical path. */
 int gtm_debug_fit_phase_cycles(gtm_model *model, uint64_t *cycles_out);
 
