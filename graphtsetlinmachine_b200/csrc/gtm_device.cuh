@@ -180,6 +180,7 @@ constexpr int kMaxRanks = 8;
 constexpr int kTransposedTypes = 8;   // node types a transposed graph keeps masks for
 struct ScatterTargets {
     int world;
+    int rank;              // own index in base[] (clause-sharded fit); bits are sent to the peers only when they are new here
     u32 *local;            // CTA-local accumulation in shared memory of SOURCE-node bits (see flush_messages), or null:
                            // node v's MW words start at local_row(v) * (MW | 1) - odd row stride, and for the transposed
                            // evaluation (lane = node word) the rows of the nodes of one word are `local_words` apart, so
@@ -280,16 +281,27 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
                 if (pairs) {
                     const u32 hi = rotated_word(row, w[q] + 1, tq, MS, MW);
                     if ((lo | hi) == 0) continue;
-                    const unsigned long long v = ((unsigned long long)hi << 32) | lo;
+                    unsigned long long v = ((unsigned long long)hi << 32) | lo;
+                    const size_t at = (size_t)dst[q] * MW + w[q];
+                    // own buffer first: what was set there already has been sent to the peers by whoever set it
 #pragma unroll
                     for (int r = 0; r < kMaxRanks; ++r)
-                        if (r < t.world)
-                            atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + (size_t)dst[q] * MW + w[q]), v);
+                        if (r == t.rank) v &= ~atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
+                    if (v == 0 || t.world == 1) continue;
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                        if (r < t.world && r != t.rank) atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
                 } else {
                     if (lo == 0) continue;
+                    u32 v = lo;
+                    const size_t at = (size_t)dst[q] * MW + w[q];
 #pragma unroll
                     for (int r = 0; r < kMaxRanks; ++r)
-                        if (r < t.world) atomicOr(t.base[r] + (size_t)dst[q] * MW + w[q], lo);
+                        if (r == t.rank) v &= ~atomicOr(t.base[r] + at, v);
+                    if (v == 0 || t.world == 1) continue;
+#pragma unroll
+                    for (int r = 0; r < kMaxRanks; ++r)
+                        if (r < t.world && r != t.rank) atomicOr(t.base[r] + at, v);
                 }
             }
         }

@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 GTM_LAP(t_stage);
                 ScatterTargets targets;
                 targets.world = a.world;
+                targets.rank = a.rank;
                 targets.local_words = 0;
                 targets.all = nullptr;
                 targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) <= a.part_words) ? s_part : nullptr;

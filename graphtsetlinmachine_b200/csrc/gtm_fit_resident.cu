@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
             }
             ScatterTargets targets;
             targets.world = a.world;
+                targets.rank = a.rank;
             targets.local_words = transposed ? tg.words : 0;
             // the last kTransposedTypes rows of the buffer hold the marks of clauses that are true on every node of their type
             const int all_words = kTransposedTypes * (m.MW | 1);

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(kBatchNodes ? 512 : 256, kBatchNodes ? 1 : 5) 
             const bool last = d == m.D - 1;
             ScatterTargets targets;
             targets.world = 1;
+            targets.rank = 0;
             targets.local = part && !last ? s_part : nullptr;
             targets.local_words = transposed ? tg.words : 0;
             targets.all = (targets.local != nullptr && transposed) ? s_part + a.part_words - all_words : nullptr;
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(256, 5) score_small_graphs_kernel(DevModel m, 
             const bool last = d == m.D - 1;
             ScatterTargets targets;
             targets.world = 1;
+            targets.rank = 0;
             targets.local = part && !last ? s_part : nullptr;
             targets.local_words = 0;
             targets.all = nullptr;

@@ -194,3 +194,53 @@ def test_benchmark_shapes_match_reference_kernels_on_the_gpu(name):
         tile.close()
     engine.close()
     ref.close()
+
+
+def _accuracy_runs(kw, train, Y, test, y_test, seeds, epochs):
+    """Test accuracy after `epochs` passes for every seed, engine and reference kernels (same data, same hypervectors)."""
+    acc = {"engine": [], "reference": []}
+    for seed in seeds:
+        for name, tm in (("engine", EngineTM(seed=seed, **kw)), ("reference", _reference(dict(kw, seed=seed)))):
+            tm.set_graphs(train)
+            tm.prepare()
+            for _ in range(epochs):
+                tm.fit(Y)
+            tm.set_graphs(test)
+            acc[name].append(float((tm.score().argmax(axis=1) == y_test).mean()))
+            tm.close()
+    return np.array(acc["engine"]), np.array(acc["reference"])
+
+
+def _assert_same_accuracy(a, b, what):
+    """|difference of the mean accuracies| <= 0.5 percentage points, or within two standard errors of the difference
+    when the seed-to-seed spread is larger than that."""
+    diff = abs(a.mean() - b.mean())
+    se = float(np.sqrt(a.var(ddof=1) / len(a) + b.var(ddof=1) / len(b)))
+    print("%s: engine %.4f +- %.4f, reference kernels %.4f +- %.4f (n = %d each), |diff| %.4f, s.e. %.4f"
+          % (what, a.mean(), a.std(ddof=1), b.mean(), b.std(ddof=1), len(a), diff, se))
+    assert diff <= max(0.005, 2.0 * se), what
+
+
+def test_accuracy_after_training_matches_reference_kernels():
+    """End-to-end accuracy, engine (Philox streams) against the reference's kernels on the same GPU (XORWOW states),
+    eight seeds per learner: the MNIST-shaped configuration after five passes over 10,000 graphs, and Noisy XOR at
+    s = 2.0 (where the task is learned reliably) after ten passes."""
+    from graphtsetlinmachine_b200 import datasets
+
+    protos = datasets.image_prototypes(1)
+    np.random.seed(2)
+    train, y = datasets.vanilla_images(10000, 2, protos)
+    test, y_test = datasets.vanilla_images(4000, 3, protos, init_with=train)
+    kw = dict(clauses=2500, classes=10, literals=256, threshold=3125, s=10.0, depth=1, max_nodes=1)
+    a, b = _accuracy_runs(kw, train, encode_labels(y, 10, 3125), test, y_test, range(1, 9), 5)
+    _assert_same_accuracy(a, b, "vanilla images")
+
+    np.random.seed(3)
+    train, y = datasets.noisy_xor(4000, 11)
+    test, y_test = datasets.noisy_xor(2000, 12, noise=0.0, init_with=train)
+    rng = np.random.default_rng(4)
+    hv = np.stack([rng.choice(256, size=2, replace=False) for _ in range(10)]).astype(np.uint32)
+    kw = dict(clauses=10, classes=2, literals=64, threshold=100, s=2.0, depth=2, message_size=256, message_bits=2,
+              max_included=4, max_nodes=2, hypervectors=hv)
+    a, b = _accuracy_runs(kw, train, encode_labels(y, 2, 100), test, y_test, range(1, 9), 10)
+    _assert_same_accuracy(a, b, "noisy XOR, s = 2.0")
