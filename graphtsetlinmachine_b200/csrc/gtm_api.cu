@@ -161,7 +161,7 @@ extern "C" int gtm_set_option(gtm_model *m, const char *name, int value)
     if (!name) return fail(GTM_ERR_ARG, "option name is null");
     if (!strcmp(name, "fit_kernel") && value >= 0 && value <= 2) { m->opt_fit_kernel = value; return GTM_OK; }
     if (!strcmp(name, "score_kernel") && value >= 0 && value <= 3) { m->opt_score_kernel = value; return GTM_OK; }
-    if (!strcmp(name, "fit_timers") && value >= 0 && value <= 1) { m->opt_fit_timers = value; return GTM_OK; }
+    if (!strcmp(name, "fit_timers") && value >= 0 && value <= 3) { m->opt_fit_timers = value; return GTM_OK; }
     if (!strcmp(name, "fit_wait_ms") && value >= 1 && value <= 600000) { m->opt_fit_wait_ms = value; return GTM_OK; }
     if (!strcmp(name, "fit_missing_cta") && value >= 0 && value <= 1) { m->opt_fit_missing_cta = value; return GTM_OK; }
     return fail(GTM_ERR_ARG, "unknown option '%s' or value %d out of range", name, value);

@@ -116,14 +116,33 @@ __device__ __forceinline__ void philox4x32_10(u32 c0, u32 c1, u32 c2, u32 c3, u3
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
-// Draw i of the stream of clause c: component (i & 3) of Philox(counter = (i>>2, i>>34, c, 0)), or the recorded word.
+// Four consecutive draws (stream positions 4*block .. 4*block+3) of the stream of clause c: Philox(counter = (block, c, 0)),
+// or the recorded words at those positions.  Deliberately NOT inlined: the learning kernels draw at some thirty places,
+// their loop body runs once per graph, and one shared copy of these ~120 instructions stays in the instruction cache
+// where thirty copies evict each other.  Scalars instead of the model struct, so that the call passes registers only.
+static __device__ __noinline__ uint4 draw_block(const u32 *recorded, u64 recorded_len, u32 seed_lo, u32 seed_hi, u32 clause, u64 block)
+{
+    if (recorded) {
+        const u32 *rec = recorded + (u64)clause * recorded_len;
+        const u64 at = (4 * block) % recorded_len;
+        uint4 r;
+        r.x = rec[at];
+        r.y = rec[(at + 1) % recorded_len];
+        r.z = rec[(at + 2) % recorded_len];
+        r.w = rec[(at + 3) % recorded_len];
+        return r;
+    }
+    u32 o[4];
+    philox4x32_10((u32)block, (u32)(block >> 32), clause, 0u, seed_lo, seed_hi, o);
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Draw i of the stream of clause c: component (i & 3) of draw_block(i >> 2).
 __device__ __forceinline__ u32 draw_at(const DevModel &m, int clause, u64 i)
 {
-    if (m.recorded) return m.recorded[(u64)clause * m.recorded_len + i % m.recorded_len];
-    u32 o[4];
-    philox4x32_10((u32)(i >> 2), (u32)(i >> 34), (u32)clause, 0u, m.seed_lo, m.seed_hi, o);
+    const uint4 o = draw_block(m.recorded, m.recorded_len, m.seed_lo, m.seed_hi, (u32)clause, i >> 2);
     const u32 sel = (u32)i & 3u;
-    return sel == 0 ? o[0] : sel == 1 ? o[1] : sel == 2 ? o[2] : o[3];
+    return sel == 0 ? o.x : sel == 1 ? o.y : sel == 2 ? o.z : o.w;
 }
 
 // (0, 1] mapping of curand_uniform: x * 2^-32 + 2^-33 in float (the product is exact, so one rounding either way).

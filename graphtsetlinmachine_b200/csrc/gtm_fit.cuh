@@ -91,58 +91,72 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
     return *(volatile int *)a.error == 0;
 }
 
-// Class sums of one graph from per-CTA vote partials, in two levels.
-//   Inside a rank: every CTA adds its K partials to the rank's accumulator of the step's parity (device-scope atomics) and
-//   then arrives on a counter; the CTA whose arrival completes the count takes the sums out of the accumulator (leaving
-//   zeros for the step after next) and
-//   between ranks: publishes them as K 64-bit words that carry the step tag next to the value (an aligned 8-byte store is
-//   single-copy atomic, also through a peer pointer, so a reader that sees the tag sees the value) into slot
-//   [parity][own rank] of EVERY rank.  All CTAs then poll the world*K words of their own rank's slots.
-// A CTA thus sends K atomics and one arrival and reads world*K words per graph, whatever the grid size.
-// Parities alternate by step: a slot or accumulator is touched again two steps later, which any CTA can only reach after
-// every CTA of every rank has read the current step.  Layout of `exchange` (8-byte units): slots [2][world][K], then the
-// accumulators int[2][K] and the arrival counters unsigned[2] (both zeroed by the host before every launch).
+// Class sums of one graph from per-CTA vote partials.
+//   Inside a rank, one atomic and one poll: every CTA adds, per class, ONE 64-bit word to the rank's accumulator of the
+//   step - arrival count in bits 48..63, its partial plus 2^31 (never negative) in bits 0..47 - and then polls the K
+//   accumulators until the count field says that every CTA has added; the class sum is the low field minus count * 2^31.
+//   No arrival counter, no second round trip: the wait ends one atomic and one load after the last CTA's votes.
+//   There are four accumulator sets, used by step mod 4.  CTA 0 clears the set of step+2 before it adds at `step`: that
+//   set was last read at step-2, and every CTA finished reading step-2 before it added at step-1, which CTA 0 has seen
+//   complete; the next add to it comes from a CTA that has seen step+1 complete, i.e. CTA 0's add of step+1, a release
+//   that follows the clearing store in the same thread.  The host zeroes all sets before every launch.
+//   Between ranks (clause-sharded fit): CTA 0 of every rank publishes its rank's sums as K 64-bit words that carry the
+//   step tag next to the value (an aligned 8-byte store is single-copy atomic, also through a peer pointer, so a reader
+//   that sees the tag sees the value) into slot [parity][own rank] of EVERY rank, and all CTAs poll the slots of the
+//   other ranks.  Parities alternate by step: a slot is written again two steps later, which its writer can only reach
+//   after every CTA of every rank has read the current step.
+// Layout of `exchange` (8-byte units): slots [2][world][K], then the accumulators [4][K].
 // Call with s_sum complete (after a __syncthreads); leaves totals in s_total, clears s_sum.  Bounded polls.
-__device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_sum,
-                                                    int *s_total, int K)
+// First half: this CTA's votes go out (and CTA 0 clears the accumulators of the step after next).  Whatever the CTA
+// does between the two halves runs in the shadow of the exchange.
+__device__ __forceinline__ void publish_votes(const FitArgs &a, unsigned long long step, int *s_sum, int K)
 {
-    __shared__ int s_completes;
-    int *acc_base = reinterpret_cast<int *>(a.exchange + (size_t)2 * a.world * K);
-    int *acc = acc_base + par * K;
-    unsigned *arrive = reinterpret_cast<unsigned *>(acc_base + 2 * K) + par;
+    unsigned long long *acc_base = a.exchange + (size_t)2 * a.world * K;
+    unsigned long long *acc = acc_base + (size_t)(step & 3) * K;
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        const int v = s_sum[k];
-        if (v != 0) atomicAdd(acc + k, v);
+        if (blockIdx.x == 0) acc_base[(size_t)((step + 2) & 3) * K + k] = 0;
+        const unsigned long long word = (1ull << 48) + (1ull << 31) + (unsigned long long)(long long)s_sum[k];
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(acc + k), "l"(word) : "memory");
         s_sum[k] = 0;
-        s_total[k] = 0;
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned target = (gridDim.x + (unsigned)a.missing) * (unsigned)(step / 2 + 1);     // arrivals of this parity so far, this launch
-        s_completes = atomicAdd(arrive, 1u) + 1u == target;
-    }
-    __syncthreads();
-    if (s_completes) {
-        __threadfence();
-        for (int k = threadIdx.x; k < K; k += blockDim.x) {
-            const int v = atomicExch(acc + k, 0);
-            const unsigned long long word = ((unsigned long long)(u32)v << 32) | tag;
+}
+
+// Second half: wait for all votes of the step; totals in s_total (valid after the closing CTA barrier).
+__device__ __forceinline__ bool collect_votes(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_total, int K)
+{
+    unsigned long long *acc = a.exchange + (size_t)2 * a.world * K + (size_t)(step & 3) * K;
+    const unsigned long long want = (unsigned long long)gridDim.x + (unsigned long long)a.missing;   // test hook: a CTA that never adds
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        unsigned long long v;
+        WaitClock clock;
+        while (true) {
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(acc + k) : "memory");
+            if ((v >> 48) >= want) break;
+            if (clock.expired(a.wait_ns) || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
+        }
+        const int mine = (int)(long long)((v & 0xffffffffffffull) - ((v >> 48) << 31));
+        s_total[k] = mine;
+        if (a.world > 1 && blockIdx.x == 0) {
+            const unsigned long long out = ((unsigned long long)(u32)mine << 32) | tag;
             const size_t slot = ((size_t)par * a.world + a.rank) * K + k;
 #pragma unroll
             for (int r = 0; r < kMaxRanks; ++r)
-                if (r < a.world) *(volatile unsigned long long *)(a.exchange_peer[r] + slot) = word;
+                if (r < a.world && r != a.rank) *(volatile unsigned long long *)(a.exchange_peer[r] + slot) = out;
         }
     }
-    volatile unsigned long long *mine = a.exchange + (size_t)par * a.world * K;
-    for (int t = threadIdx.x; t < a.world * K; t += blockDim.x) {
-        unsigned long long v = mine[t];
-        WaitClock clock;
-        while ((u32)v != tag) {
-            if (clock.expired(a.wait_ns) || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
-            v = mine[t];
+    if (a.world > 1) {
+        __syncthreads();
+        volatile unsigned long long *slots = a.exchange + (size_t)par * a.world * K;
+        for (int t = threadIdx.x; t < a.world * K; t += blockDim.x) {
+            if (t / K == a.rank) continue;
+            unsigned long long v = slots[t];
+            WaitClock clock;
+            while ((u32)v != tag) {
+                if (clock.expired(a.wait_ns) || *(volatile int *)a.error) { atomicExch(a.error, 1); break; }
+                v = slots[t];
+            }
+            atomicAdd(&s_total[t % K], (int)(u32)(v >> 32));
         }
-        atomicAdd(&s_total[t % K], (int)(u32)(v >> 32));
     }
     __syncthreads();
     if (blockIdx.x == 0)
@@ -150,17 +164,19 @@ __device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, unsigned l
     return *(volatile int *)a.error == 0;
 }
 
+__device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_sum,
+                                                    int *s_total, int K)
+{
+    publish_votes(a, step, s_sum, K);
+    return collect_votes(a, step, par, tag, s_total, K);
+}
+
 // Four consecutive draws of a clause stream: Philox block `block` (draws 4*block .. 4*block+3), or the
 // recorded words at those positions.
 __device__ __forceinline__ void draw4_at(const DevModel &m, int clause, u64 block, u32 out[4])
 {
-    if (m.recorded) {
-        const u32 *rec = m.recorded + (u64)clause * m.recorded_len;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[i] = rec[(4 * block + i) % m.recorded_len];
-        return;
-    }
-    philox4x32_10((u32)block, (u32)(block >> 32), (u32)clause, 0u, m.seed_lo, m.seed_hi, out);
+    const uint4 o = draw_block(m.recorded, m.recorded_len, m.seed_lo, m.seed_hi, (u32)clause, block);
+    out[0] = o.x; out[1] = o.y; out[2] = o.z; out[3] = o.w;
 }
 
 // One round of Bernoulli bits for Type I masks.  Lane l takes Philox block `first_block + 32*round + l`, i.e.
@@ -193,13 +209,14 @@ constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of
 // Type I / II feedback of one clause on one layer (kernels.py:98-183), all classes in order.  The warp owns
 // the clause; lanes hold one automaton word each (planes in registers).  `upd_lo` holds the feedback type of
 // class `lane` (classes 0..31); further classes are read back from `update`.  Masks come from `pre` when the CTA
-// generated the layer's packed Bernoulli words beforehand (generate_masks); otherwise layers of at most 32 words take
+// generated the layer's packed Bernoulli words beforehand (generate_mask_round; the layer's first draw is bit `pre_off`
+// of that stream); otherwise layers of at most 32 words take
 // the words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds in flight per
 // step, and wider layers generate them class by class.  Returns the draws consumed.
 template <int MAXSB>
 __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
                                               bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
-                                              u64 pos0, int lane, u32 *pack, const u32 *pre, float p)
+                                              u64 pos0, int lane, u32 *pack, const u32 *pre, int pre_off, float p)
 {
     const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
     const bool all_ones = p >= 1.0f;         // every uniform is <= 1
@@ -252,10 +269,12 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
                     if (u > 0) {
                         u32 mask = kFull;
                         if (pre != nullptr && !all_ones) {
-                            // words generated beforehand by the whole CTA (generate_masks): pre[rank*W + w], stream-aligned
-                            const u32 lo = mine ? pre[rank * W + lane] : 0u;
-                            const u32 hi = (mine && shift) ? pre[rank * W + lane + 1] : 0u;
-                            mask = __funnelshift_r(lo, hi, shift);
+                            // words generated beforehand (generate_mask_round): the layer's first draw sits pre_off bits
+                            // into `pre`, rank r's word w follows 32 * (r * W + w) bits later
+                            const int at = (pre_off >> 5) + rank * W + lane, sh = pre_off & 31;
+                            const u32 lo = mine ? pre[at] : 0u;
+                            const u32 hi = (mine && sh) ? pre[at + 1] : 0u;
+                            mask = __funnelshift_r(lo, hi, sh);
                         } else if (packed) {
                             const u32 lo = mine ? pack[local * W + lane] : 0u;
                             const u32 hi = (mine && shift) ? pack[local * W + lane + 1] : 0u;
@@ -329,9 +348,16 @@ struct Decision {
     u64 pos;      // stream position after node choice and decisions = first mask draw of layer 0
 };
 
-__device__ __forceinline__ Decision clause_decide(const DevModel &m, const GraphView &gv, const ClauseView &cv,
-                                                  const FitArgs &a, const u32 *bits, const int *s_target,
-                                                  const float *s_thr, int c, int lane)
+// The part of the decision that does not depend on the class sums: the node choice and the uniforms of the first 16
+// classes.  A kernel runs it while the vote exchange is under way.
+struct PreDecision {
+    int chosen;   // selected true node or -1
+    u64 pos;      // stream position after the node choice
+    float uni;    // uniform of draw pos + lane
+};
+
+__device__ __forceinline__ PreDecision clause_predecide(const DevModel &m, const GraphView &gv, const ClauseView &cv,
+                                                        const u32 *bits, int c, int lane)
 {
     const int words = (gv.n + 31) >> 5;
     u64 pos = *cv.pos;
@@ -365,6 +391,19 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
             rank -= total;
         }
     }
+    PreDecision pd;
+    pd.chosen = chosen;
+    pd.pos = pos;
+    pd.uni = to_uniform(draw_at(m, c, pos + lane));     // only the first (at most 2 * min(K, 16)) are consumed
+    return pd;
+}
+
+__device__ __forceinline__ Decision clause_decide_finish(const DevModel &m, const ClauseView &cv, const FitArgs &a,
+                                                         const PreDecision &pd, const int *s_target, const float *s_thr,
+                                                         int c, int lane)
+{
+    const int chosen = pd.chosen;
+    u64 pos = pd.pos;
     const bool clause_true = chosen != -1;
 
     // 2. feedback type per class + weight move, 16 classes per pass, one class per lane.
@@ -375,7 +414,7 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
     int upd_lo = 0;
     for (int kb = 0; kb < m.K; kb += 16) {
         const int kn = min(16, m.K - kb);
-        const float uni = to_uniform(draw_at(m, c, pos + lane));     // only the first (at most 2*kn) are consumed
+        const float uni = kb == 0 ? pd.uni : to_uniform(draw_at(m, c, pos + lane));     // only the first (at most 2*kn) are consumed
         const bool mine = lane < kn;
         int wgt = 0, sign = 1, t = 1;
         float thr = 0.0f;
@@ -417,12 +456,22 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
     return dec;
 }
 
-// 3./4. automata of every layer.  `pre`, when given, holds the pre-generated packed words of all layers back to back
-// (layer l: npos*W_l + 1 words).
+__device__ __forceinline__ Decision clause_decide(const DevModel &m, const GraphView &gv, const ClauseView &cv,
+                                                  const FitArgs &a, const u32 *bits, const int *s_target,
+                                                  const float *s_thr, int c, int lane)
+{
+    const PreDecision pd = clause_predecide(m, gv, cv, bits, c, lane);
+    return clause_decide_finish(m, cv, a, pd, s_target, s_thr, c, lane);
+}
+
+// 3./4. automata of every layer.  `pre`, when given, holds the pre-generated packed words of all layers back to back:
+// layer 0 in the first pre0_words words, its first draw at bit pre0_off (the stream may have been started before the
+// decisions were known, see PreDecision); layer l >= 1 in npos*W_l + 1 words that start at the Philox block of its
+// first draw.
 template <int MAXSB>
 __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView &gv, const ClauseView &cv, const FitArgs &a,
                                              const u32 *P, const Decision &dec, int npos, int c, int lane, u32 *pack,
-                                             const u32 *pre, const float *p_mask)
+                                             const u32 *pre, int pre0_off, int pre0_words, const float *p_mask)
 {
     const bool clause_true = dec.chosen != -1;
     if (m.K <= 32 && __ballot_sync(kFull, dec.upd_lo != 0) == 0) {      // no feedback for this clause: nothing drawn, nothing changes
@@ -435,9 +484,10 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
 #pragma unroll 1
     for (int d = 0; d < m.D; ++d) {
         const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * a.max_nodes + node) * m.MW;
+        const int off = d == 0 ? pre0_off : (int)(pos & 3);
         pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), dec.upd_lo, a.update, clause_true, within, row, d > 0, pos, lane,
-                                     pack, pre, p_mask[d]);
-        if (pre) pre += npos * (d == 0 ? m.L0 : m.M) + 1;
+                                     pack, pre, off, p_mask[d]);
+        if (pre) pre += d == 0 ? pre0_words : npos * m.M + 1;
     }
     if (lane == 0) *cv.pos = pos;
 }
@@ -448,18 +498,16 @@ __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphVi
                                                 const float *s_thr, int c, int lane, u32 *pack, const float *p_mask)
 {
     const Decision dec = clause_decide(m, gv, cv, a, bits, s_target, s_thr, c, lane);
-    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr, p_mask);
+    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr, 0, 0, p_mask);
 }
 
-// Packed Bernoulli words of one (clause, layer, round) work item, written to the clause's pre-generated area.
-// Layer l of a clause with `npos` Type-I classes needs words [0, npos*W_l + (shift ? 1 : 0)) of the stream that starts
-// at Philox block pos_l >> 2; round q yields words 4q .. 4q+3.
-__device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, int layer, u64 pos_l, int npos, int q,
-                                                    u32 *dst, int lane, float p)
+// Round q of a packed Bernoulli stream that starts at Philox block `first_block`: the warp's 32 blocks
+// first_block + 32q .. + 31 give 128 outcomes [uniform <= p], in draw order, = words 4q .. 4q+3 of the stream; words
+// below `need` are written to dst.
+__device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, u64 first_block, int need, int q, u32 *dst,
+                                                    int lane, float p)
 {
-    const int W = layer == 0 ? m.L0 : m.M;
-    const int need = npos * W + ((pos_l & 3) ? 1 : 0);
-    const u32 nib = bernoulli_nibbles(m, c, (pos_l >> 2) + (u64)q * 32 + lane, p, lane);
+    const u32 nib = bernoulli_nibbles(m, c, first_block + (u64)q * 32 + lane, p, lane);
     const u32 word = __reduce_or_sync(0xffu << (lane & 24), nib);
     const int j = 4 * q + (lane >> 3);
     if ((lane & 7) == 0 && j < need) dst[j] = word;

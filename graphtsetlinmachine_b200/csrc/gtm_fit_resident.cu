@@ -17,7 +17,7 @@ namespace gtm {
 // most kStageNodes nodes, kStageRowWords literal words and kStageEdges edge rows; larger graphs are read in place.
 constexpr int kStageNodes = 256, kStageRowWords = 1536, kStageEdges = 512;
 constexpr int kStageWords = kStageRowWords + 3 * kStageNodes + 2 * kStageEdges;
-constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I classes, draw position (2), work items, pad, feedback type of 32 classes
+constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I classes, draw position (2), work items, feedback type (before the decisions: uniform) of 32 classes, bit offset of layer 0's first draw in its mask stream
 
 __device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global_src)
 {
@@ -36,9 +36,14 @@ __device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global
 //                  [12] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
 //                  per owned clause: clause_words words =
 //                  draw counter (2) | include count (1) | pad (1) | weights [K] | hypervector [MB] | node words [2][NC] | planes
-template <int MAXSB, bool kBatchNodes>
-__global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGraphs g, FitArgs a)
+template <int MAXSB, bool kBatchNodes, bool kOneLayer>
+__global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, DevGraphs g, FitArgs a)
 {
+    // kOneLayer: the depth is the compile-time constant 1, which removes the message passing, the grid barriers and the
+    // message-layer feedback from the code.  The kernel's loop body is executed once per graph: what it does not contain
+    // does not compete for the instruction cache.
+    DevModel m = m_in;
+    if (kOneLayer) m.D = 1;
     extern __shared__ __align__(16) int s_mem[];
     __shared__ FitShared s_fs;
     fill_fit_shared(&s_fs, m, a);
@@ -156,6 +161,9 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         if (!grid_barrier(a, arrivals)) return;
     }
     const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+    const bool fine = timer && a.timers >= 2;     // timers == 2: slots 4..7 split the evaluation instead of the feedback
+#define GTM_LAPE(acc) do { if (fine) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)
+#define GTM_LAPB(acc) do { if (timer && !fine) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t_x0 = 0, t_x1 = 0, t_x2 = 0, t_x3 = 0, t0 = clock64(), t1;
 
     int slot3 = 0;   // step % 3
@@ -180,8 +188,11 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
         TransposedGraph tg;
         tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (gv.n + 31) >> 5;
         const bool transposed = kBatchNodes && a.t_stride > 0 && gv.n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
+        if (a.timers == 3) GTM_LAPE(t_x0);
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
+        if (a.timers == 3) GTM_LAPE(t_x1);
         fetch_sizes(step + 2, e_nxt2);
+        if (a.timers == 3) GTM_LAPE(t_x2); else GTM_LAPE(t_x0);
 
         for (int d = 0; d < m.D; ++d) {
             const bool last = d == m.D - 1;
@@ -227,14 +238,17 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 if (last && any)
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
             }
+            if (a.timers != 3) GTM_LAPE(t_x1);
             if (targets.local) {            // this CTA's share of the layer's messages, merged before the grid barrier
                 __syncthreads();
                 flush_messages(targets, gv, m.MS, m.MW);
                 __syncthreads();
                 for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) targets.local[t] = 0;
+                if (a.timers != 3) GTM_LAPE(t_x3);
             }
         }
         __syncthreads();
+        if (a.timers == 3) GTM_LAPE(t_x3); else GTM_LAPE(t_x2);
         GTM_LAP(t_eval);
         if (solo) {
             for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
@@ -242,32 +256,62 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 a.class_sum_tap[k] = s_sum[k];
                 s_sum[k] = 0;
             }
-            __syncthreads();
-        } else if (!exchange_class_sums(a, step, par, a.tag_base + (u32)step + 1u, s_sum, s_total, m.K)) return;
+        } else {
+            publish_votes(a, step, s_sum, m.K);
+        }
+        // Layer 0's masks come from a Bernoulli stream that starts at Philox block B0 = (position after the node choice + K)
+        // >> 2: at or before the first mask draw whatever the decisions turn out to be, so that its first rounds - enough
+        // for one Type-I class - can be generated before the class sums are known.
+        const float p0 = s_fs.p_mask[0];
+        auto words0_of = [&](int npos, int off0) { return (npos > 0 && p0 < 1.0f) ? ((off0 + npos * m.L0 * 32 - 1) >> 5) + 1 : 0; };
+        const int spec_rounds = (a.pre_words > 0 && p0 < 1.0f) ? (words0_of(1, m.K + 3) + 3) >> 2 : 0;
+        if (a.pre_words > 0) {
+            // in the shadow of the vote exchange: what the decisions need besides the class sums, and the speculative rounds
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                const PreDecision pd = clause_predecide(m, gv, cv, node_words(c, m.D - 1), c, lane);
+                int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
+                if (lane == 0) { rec[0] = pd.chosen; rec[2] = (int)(u32)pd.pos; rec[3] = (int)(u32)(pd.pos >> 32); }
+                rec[5 + lane] = __float_as_int(pd.uni);
+                const u64 B0 = (pd.pos + (u64)m.K) >> 2;
+                for (int q = 0; q < spec_rounds; ++q)
+                    generate_mask_round(m, c, B0, 4 * spec_rounds, q, s_pre + (size_t)(c - c_lo) * a.pre_words, lane, p0);
+            }
+        }
+        if (solo) __syncthreads();
+        else if (!collect_votes(a, step, par, a.tag_base + (u32)step + 1u, s_total, m.K)) return;
         GTM_LAP(t_tot);
         class_decision_inputs(m, s_total, y, s_target, s_thr);
         __syncthreads();
         if (a.pre_words > 0) {
-            // cooperative feedback: decisions per clause, then every (clause, layer, round) of mask generation is a work
-            // item shared by all warps of the CTA, then the automaton updates per clause
+            // cooperative feedback: decisions per clause, then every (clause, layer, round) of mask generation that is still
+            // missing is a work item shared by all warps of the CTA, then the automaton updates per clause
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
-                const Decision dec = clause_decide(m, gv, cv, a, node_words(c, m.D - 1), s_target, s_thr, c, lane);
-                const int npos = __popc(__ballot_sync(kFull, dec.upd_lo > 0));
-                int need = 0, items = 0;
-                u64 pos_l = dec.pos;
-                for (int l = 0; l < m.D; ++l) {
-                    const int W = l == 0 ? m.L0 : m.M;
-                    need += npos * W + 1;
-                    if (npos > 0 && s_fs.p_mask[l] < 1.0f) items += (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
-                    pos_l += (u64)npos * W * 32;
-                }
                 int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
+                PreDecision pd;
+                pd.chosen = rec[0];
+                pd.pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                pd.uni = __int_as_float(rec[5 + lane]);
+                const u64 B0 = (pd.pos + (u64)m.K) >> 2;
+                const Decision dec = clause_decide_finish(m, cv, a, pd, s_target, s_thr, c, lane);
+                const int npos = __popc(__ballot_sync(kFull, dec.upd_lo > 0));
+                const int off0 = (int)(dec.pos - 4 * B0);
+                const int rounds0 = (words0_of(npos, off0) + 3) >> 2;
+                int need = 4 * max(rounds0, spec_rounds), items = max(0, rounds0 - spec_rounds);
+                u64 pos_l = dec.pos + (u64)npos * m.L0 * 32;
+                for (int l = 1; l < m.D; ++l) {
+                    need += npos * m.M + 1;
+                    if (npos > 0 && s_fs.p_mask[l] < 1.0f) items += (npos * m.M + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
+                    pos_l += (u64)npos * m.M * 32;
+                }
+                __syncwarp();
                 if (lane == 0) {
-                    rec[0] = dec.chosen; rec[1] = npos;
+                    rec[1] = npos;
                     rec[2] = (int)(u32)dec.pos; rec[3] = (int)(u32)(dec.pos >> 32);
                     const bool fits_pre = need <= a.pre_words;
                     rec[4] = fits_pre ? items : -1;                      // -1: does not fit, the clause generates on its own
+                    rec[37] = off0;
                     // this clause's work items take the next `items` numbers; (clause, first number) goes to the item table
                     if (fits_pre && items > 0) {
                         const int slot = atomicAdd(&s_item_off[0], 1);
@@ -279,8 +323,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 rec[5 + lane] = dec.upd_lo;
             }
             __syncthreads();
-            GTM_LAP(t_x0);
-            GTM_LAP(t_x1);
+            GTM_LAPB(t_x0);
+            GTM_LAPB(t_x1);
             {
                 const int entries = s_item_off[0], total = s_item_off[1];
                 for (int i = warp; i < total; i += nwarps) {
@@ -290,23 +334,31 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                         if (f <= i && f >= firsti) { firsti = f; ci = s_item_off[2 + 2 * t]; }
                     }
                     const int *rec = s_rec + (size_t)ci * kRecWords;
-                    const int npos = rec[1];
-                    u64 pos_l = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                    const int npos = rec[1], off0 = rec[37];
+                    const u64 pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                    const int rounds0 = (words0_of(npos, off0) + 3) >> 2;
                     int r = i - firsti;
                     u32 *dst = s_pre + (size_t)ci * a.pre_words;
-                    for (int l = 0; l < m.D; ++l) {
-                        const int W = l == 0 ? m.L0 : m.M;
-                        const int rounds = s_fs.p_mask[l] < 1.0f ? (npos * W + ((pos_l & 3) ? 1 : 0) + 3) >> 2 : 0;
-                        if (r < rounds) { generate_mask_round(m, c_lo + ci, l, pos_l, npos, r, dst, lane, s_fs.p_mask[l]); break; }
+                    if (r < rounds0 - spec_rounds) {
+                        generate_mask_round(m, c_lo + ci, (pos - (u64)off0) >> 2, 4 * rounds0, spec_rounds + r, dst, lane, p0);
+                        continue;
+                    }
+                    r -= max(0, rounds0 - spec_rounds);
+                    dst += 4 * max(rounds0, spec_rounds);
+                    u64 pos_l = pos + (u64)npos * m.L0 * 32;
+                    for (int l = 1; l < m.D; ++l) {
+                        const int wneed = npos * m.M + ((pos_l & 3) ? 1 : 0);
+                        const int rounds = s_fs.p_mask[l] < 1.0f ? (wneed + 3) >> 2 : 0;
+                        if (r < rounds) { generate_mask_round(m, c_lo + ci, pos_l >> 2, wneed, r, dst, lane, s_fs.p_mask[l]); break; }
                         r -= rounds;
-                        dst += npos * W + 1;
-                        pos_l += (u64)npos * W * 32;
+                        dst += npos * m.M + 1;
+                        pos_l += (u64)npos * m.M * 32;
                     }
                 }
             }
             __syncthreads();
             if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }     // next step's item table starts empty
-            GTM_LAP(t_x2);
+            GTM_LAPB(t_x2);
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 const int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
@@ -314,8 +366,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 dec.chosen = rec[0];
                 dec.pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
                 dec.upd_lo = rec[5 + lane];
+                const int rounds0 = (words0_of(rec[1], rec[37]) + 3) >> 2;
                 clause_apply<MAXSB>(m, gv, cv, a, P, dec, rec[1], c, lane, s_pack + warp * kPackWords,
-                                    rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr, s_fs.p_mask);
+                                    rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr, rec[37],
+                                    4 * max(rounds0, spec_rounds), s_fs.p_mask);
             }
         } else {
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
@@ -323,7 +377,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
                 clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords, s_fs.p_mask);
             }
         }
-        GTM_LAP(t_x3);
+        GTM_LAPB(t_x3);
         wait_copies();
         __syncthreads();   // next step's graph is complete; s_total and this step's stage buffer may be reused
         GTM_LAP(t_fb);
@@ -351,6 +405,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m, DevGra
     }
 }
 #undef GTM_LAP
+#undef GTM_LAPE
+#undef GTM_LAPB
 
 }  // namespace gtm
 
@@ -372,10 +428,14 @@ static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
 
 // The state-resident kernel for the automaton width, with four-at-a-time node words for graph sets of more than 32 nodes per graph.
-static const void *resident_kernel_for(int state_bits, int max_nodes)
+static const void *resident_kernel_for(int state_bits, int max_nodes, int depth)
 {
-    if (max_nodes > 32) return state_bits <= 8 ? (const void *)fit_resident_kernel<8, true> : (const void *)fit_resident_kernel<32, true>;
-    return state_bits <= 8 ? (const void *)fit_resident_kernel<8, false> : (const void *)fit_resident_kernel<32, false>;
+    if (depth == 1) {
+        if (max_nodes > 32) return state_bits <= 8 ? (const void *)fit_resident_kernel<8, true, true> : (const void *)fit_resident_kernel<32, true, true>;
+        return state_bits <= 8 ? (const void *)fit_resident_kernel<8, false, true> : (const void *)fit_resident_kernel<32, false, true>;
+    }
+    if (max_nodes > 32) return state_bits <= 8 ? (const void *)fit_resident_kernel<8, true, false> : (const void *)fit_resident_kernel<32, true, false>;
+    return state_bits <= 8 ? (const void *)fit_resident_kernel<8, false, false> : (const void *)fit_resident_kernel<32, false, false>;
 }
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
@@ -386,13 +446,13 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
     DevModel d = m->dm;
     d.C = n_clauses;   // clauses this rank learns
     ResidentPlan plan;
-    const void *fn = resident_kernel_for(d.SB, ds->max_nodes);
+    const void *fn = resident_kernel_for(d.SB, ds->max_nodes, d.D);
     const int warps = kResidentThreads / 32;
     int words = 4 + d.K + d.MB + 2 * ds->NC + d.SB * (d.L0 + (d.D - 1) * d.M);
     words = (words + 3) & ~3;
     // cooperative mask generation: layers of at most 32 words, at most 32 classes; room for 8 Type-I classes per clause
     int pre_words = 0;
-    if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 1) & ~1;
+    if (d.K <= 32 && d.L0 <= 32 && (d.D == 1 || d.M <= 32)) pre_words = (std::min(d.K, 8) * (d.L0 + (d.D - 1) * d.M) + d.D + 9) & ~1;
     const size_t p_words = (size_t)(d.D - 1) * ds->max_nodes * d.MW;
     const size_t layer_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);   // message bits of one layer: padded rows + per-type rows
     // transposed-graph buffer (graph sets of 33..1024 nodes per graph, few node types): rows of max(L0, MW) words plus type masks
@@ -441,11 +501,11 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
 
 static int shard_size(int C, int world) { return (C + world - 1) / world; }
 
-// Bytes of one rank's vote exchange area: tagged slots [2][world][K], accumulators int[2][K], arrival counters [2]
+// Bytes of one rank's vote exchange area: tagged slots [2][world][K], then the accumulators [4][K], all 64-bit
 // (exchange_class_sums).
 size_t exchange_bytes(int world, int K)
 {
-    return (size_t)2 * world * K * sizeof(unsigned long long) + (size_t)2 * K * sizeof(int) + 2 * sizeof(unsigned) + 8;
+    return ((size_t)2 * world * K + (size_t)4 * K) * sizeof(unsigned long long);
 }
 
 int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int64_t first, int64_t count,
@@ -489,10 +549,10 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             a.P_peer[r][0] = (u32 *)(base + cm.P_off[0]);
             a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
         }
-        // accumulators and arrival counters of the vote exchange start every launch at zero (they are this rank's own;
-        // the slots that peers write keep their tags)
+        // the accumulators of the vote exchange start every launch at zero (they are this rank's own; the slots that
+        // peers write keep their tags)
         GTM_CU(cudaMemsetAsync((char *)cm.block + cm.exchange_off + (size_t)2 * cm.world * d.K * sizeof(unsigned long long), 0,
-                               (size_t)2 * d.K * sizeof(int) + 2 * sizeof(unsigned), m->stream));
+                               (size_t)4 * d.K * sizeof(unsigned long long), m->stream));
         resident = cm.resident; grid = cm.grid;
         a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride;
         smem = cm.smem;
@@ -522,7 +582,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
 
     DevModel dm = d;
     if (resident) {
-        fn = resident_kernel_for(d.SB, ds->max_nodes);
+        fn = resident_kernel_for(d.SB, ds->max_nodes, d.D);
         block = kResidentThreads;
         if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &a};

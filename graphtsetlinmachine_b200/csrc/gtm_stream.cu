@@ -107,6 +107,7 @@ __device__ __forceinline__ uint4 lds128(unsigned addr)
     return v;
 }
 
+constexpr int kWarpVoteGraphs = 64;   // tiles of at most this many (multi-node) graphs vote warp-wise, see below
 constexpr int kRTStride = 33;   // RT[cw][b * 33 + j] holds node 32j+b: conflict-free both for the writer (lanes = j) and the reader (lanes = b)
 
 template <int KP>
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
     u32 *RT = R + (size_t)kStreamCB * TNC;             // [CW][32*33]      clause bits per node
     int *Wb = (int *)(RT + (size_t)CW * 32 * kRTStride);   // [CB][KROW]
     __shared__ int s_tile;
+    __shared__ int s_vsum[kWarpVoteGraphs * KP];      // class sums of the tile's graphs when they are voted warp-wise
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kStreamThreads / 32;
     const int KROW = a.KROW;
     const unsigned xt32 = (unsigned)__cvta_generic_to_shared(XT);
@@ -156,6 +158,13 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
             if (lane == 0) TMV[tj] = col;
         }
 
+        // Tiles of a few large graphs (e.g. 361-node images, two per tile) would leave the one-thread-per-graph votes to a
+        // couple of threads: they vote warp-wise instead - lane = clause, OR of the clause's node words over the graph's
+        // slots, the weights of the lanes that fired summed over the warp (redux.sync), one shared-memory add per warp.
+        const int ng = g1 - g0;
+        const bool warp_votes = ng <= kWarpVoteGraphs && nn >= 8 * ng;
+        if (warp_votes)
+            for (int i = tid; i < ng * KP; i += kStreamThreads) s_vsum[i] = 0;
         // ---- per-graph state: graphs tid and tid+512 of the tile ----
         int acc[2][KP];
         int seg_lo[2], seg_hi[2];
@@ -201,6 +210,32 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
             }
             for (int i = tid; i < cbn * KROW; i += kStreamThreads) Wb[i] = a.Wt[(size_t)cb0 * KROW + i];
             __syncthreads();
+            if (warp_votes) {
+                for (int task = warp; task < CW * ng; task += nwarps) {
+                    const int cw = task % CW, gl = task / CW;
+                    const int cb = 32 * cw + lane;
+                    const int lo = (int)g.node_index[g0 + gl] - node0, hi = lo + (int)g.n_nodes[g0 + gl];     // slots [lo, hi)
+                    u32 any = 0;
+                    if (cb < cbn)
+                        for (int j = lo >> 5; j <= (hi - 1) >> 5; ++j) {
+                            u32 mask = kFull;
+                            if (j == lo >> 5) mask &= kFull << (lo & 31);
+                            if (j == (hi - 1) >> 5) mask &= kFull >> (31 - ((hi - 1) & 31));
+                            any |= R[(size_t)cb * TNC + j] & mask;
+                        }
+                    const bool fired = any != 0;
+                    if (!__any_sync(kFull, fired)) continue;
+                    int mine = 0;
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) {
+                        const int sk = __reduce_add_sync(kFull, fired && k < KROW ? Wb[(size_t)cb * KROW + k] : 0);
+                        if (lane == k) mine = sk;
+                    }
+                    if (lane < m.K) atomicAdd(&s_vsum[gl * KP + lane], mine);
+                }
+                __syncthreads();
+                continue;
+            }
             // ---- 32 clauses x 32 nodes blocks of R, transposed in registers: warp = clause word, lane = node word ----
             for (int blk = tid; blk < CW * TNC; blk += kStreamThreads) {
                 const int cw = blk / TNC, j = blk - cw * TNC;
@@ -239,8 +274,14 @@ __global__ void __launch_bounds__(kStreamThreads, 2) stream_score_kernel(DevMode
         }
 
         // ---- class sums of the tile's graphs (only those inside the requested range) ----
+        if (warp_votes)
+            for (int i = tid; i < ng * m.K; i += kStreamThreads) {
+                const int gl = i / m.K, k = i - gl * m.K;
+                const int64_t gi = (int64_t)g0 + gl;
+                if (gi >= a.first && gi < a.first + a.count) a.class_sums[(size_t)(gi - a.first) * m.K + k] = s_vsum[gl * KP + k];
+            }
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < 2 && !warp_votes; ++s) {
             const int64_t gi = (int64_t)g0 + tid + s * kStreamThreads;
             if (gi < g1 && gi >= a.first && gi < a.first + a.count) {
                 int *out = a.class_sums + (size_t)(gi - a.first) * m.K;

@@ -12,7 +12,8 @@ reference text is the replacement of its ``#include <curand_kernel.h>`` line by 
 Because the reference specialises its kernels by preprocessor constants, one shared object is built per
 hyper-parameter set; ``config_key`` names it.  The intermediate translation unit is deleted after compiling.
 
-The reference checkout is looked up in ``$GTM_REFERENCE``, ``baseline/_ref`` and ``DEFAULT_REFERENCE``; when none
+The reference checkout is looked up in ``$GTM_REFERENCE``, ``baseline/_ref`` and a directory ``reference`` beside the
+repository; when none
 is present (e.g. on a GPU box) only shared objects built earlier can be used.
 """
 
@@ -32,12 +33,13 @@ PARAM_ORDER = (
 )
 
 
-DEFAULT_REFERENCE = "/root/reference"   # where the build machine keeps the read-only checkout
+# a checkout named `reference` beside the repository directory (where the build machine keeps its read-only copy)
+SIBLING_REFERENCE = os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 
 def find_reference():
     """Path of the reference's kernels.py, or None."""
-    roots = [os.environ.get("GTM_REFERENCE"), os.path.join(HERE, "..", "baseline", "_ref"), DEFAULT_REFERENCE]
+    roots = [os.environ.get("GTM_REFERENCE"), os.path.join(HERE, "..", "baseline", "_ref"), SIBLING_REFERENCE]
     for root in roots:
         if not root:
             continue

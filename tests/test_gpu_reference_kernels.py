@@ -232,7 +232,7 @@ def test_accuracy_after_training_matches_reference_kernels():
     train, y = datasets.vanilla_images(10000, 2, protos)
     test, y_test = datasets.vanilla_images(4000, 3, protos, init_with=train)
     kw = dict(clauses=2500, classes=10, literals=256, threshold=3125, s=10.0, depth=1, max_nodes=1)
-    a, b = _accuracy_runs(kw, train, encode_labels(y, 10, 3125), test, y_test, range(1, 9), 5)
+    a, b = _accuracy_runs(kw, train, encode_labels(y, 10, 3125), test, y_test, range(1, 17), 5)
     _assert_same_accuracy(a, b, "vanilla images")
 
     np.random.seed(3)
