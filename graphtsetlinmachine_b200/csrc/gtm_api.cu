@@ -159,6 +159,7 @@ extern "C" int gtm_set_option(gtm_model *m, const char *name, int value)
 {
     GTM_TRY(bind(m));
     if (!name) return fail(GTM_ERR_ARG, "option name is null");
+    if (!strcmp(name, "fit_block_clauses") && value >= 0 && value <= 4096) { m->opt_fit_block_clauses = value; return GTM_OK; }
     if (!strcmp(name, "fit_kernel") && value >= 0 && value <= 2) { m->opt_fit_kernel = value; return GTM_OK; }
     if (!strcmp(name, "score_kernel") && value >= 0 && value <= 3) { m->opt_score_kernel = value; return GTM_OK; }
     if (!strcmp(name, "fit_timers") && value >= 0 && value <= 3) { m->opt_fit_timers = value; return GTM_OK; }

@@ -117,10 +117,8 @@ __device__ __forceinline__ void philox4x32_10(u32 c0, u32 c1, u32 c2, u32 c3, u3
 }
 
 // Four consecutive draws (stream positions 4*block .. 4*block+3) of the stream of clause c: Philox(counter = (block, c, 0)),
-// or the recorded words at those positions.  Deliberately NOT inlined: the learning kernels draw at some thirty places,
-// their loop body runs once per graph, and one shared copy of these ~120 instructions stays in the instruction cache
-// where thirty copies evict each other.  Scalars instead of the model struct, so that the call passes registers only.
-static __device__ __noinline__ uint4 draw_block(const u32 *recorded, u64 recorded_len, u32 seed_lo, u32 seed_hi, u32 clause, u64 block)
+// or the recorded words at those positions.
+__device__ __forceinline__ uint4 draw_block(const u32 *recorded, u64 recorded_len, u32 seed_lo, u32 seed_hi, u32 clause, u64 block)
 {
     if (recorded) {
         const u32 *rec = recorded + (u64)clause * recorded_len;
@@ -330,6 +328,82 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
 __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const GraphView &gv, int MS, int MW)
 {
     flush_messages(t, gv, MS, MW, (int)threadIdx.x, (int)blockDim.x);
+}
+
+// Small graphs (at most 32 nodes), learning kernels: instead of walking the edges in every CTA and sending every rotated
+// row to the shared destination rows with atomics (flush_messages), a CTA sends only its SOURCE-node marks - one atomic
+// per non-empty word (pair) of a node, no edge walk, no answer needed on a single GPU - into the layer's merged-marks
+// buffer (the same global rows, node-major, on every rank; a clause-sharded fit sends a peer only the bits that were new
+// in its own buffer).  After the grid barrier every CTA reads the merged marks once (n * MW words) and builds the
+// destination rows itself, in shared memory (build_message_rows).  All threads of the CTA, between two CTA barriers.
+__device__ __forceinline__ void flush_marks(const ScatterTargets &t, int n, int MW)
+{
+    const bool pairs = (MW & 1) == 0;
+    const int per_row = pairs ? MW >> 1 : MW;
+    for (int i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+        const int u = i / per_row, w = (i - u * per_row) << (pairs ? 1 : 0);
+        const u32 *row = local_row(t, u, MW);
+        const u32 lo = row[w], hi = pairs ? row[w + 1] : 0u;
+        if ((lo | hi) == 0) continue;
+        const size_t at = (size_t)u * MW + w;
+        if (pairs) {
+            unsigned long long v = ((unsigned long long)hi << 32) | lo;
+            if (t.world == 1) { atomicOr(reinterpret_cast<unsigned long long *>(t.base[0] + at), v); continue; }
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r == t.rank) v &= ~atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
+            if (v == 0) continue;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < t.world && r != t.rank) atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
+        } else {
+            u32 v = lo;
+            if (t.world == 1) { atomicOr(t.base[0] + at, v); continue; }
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r == t.rank) v &= ~atomicOr(t.base[r] + at, v);
+            if (v == 0) continue;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < t.world && r != t.rank) atomicOr(t.base[r] + at, v);
+        }
+    }
+}
+
+// Destination rows of one layer from its merged source marks: rows[v] = OR over the edges (u -> v, type t) of marks[u]
+// rotated up by t ((hv + t) mod MS, kernels.py:581).  `marks` = the layer's merged-marks rows in global memory (complete:
+// call after the grid barrier), `tmp` = a CTA buffer of n rows with stride MW | 1 (the local marks buffer, which is left
+// cleared for the next layer), `rows` = [32][MW] in shared memory.  All threads of the CTA; ends with a CTA barrier.
+__device__ __forceinline__ void build_message_rows(const u32 *marks, u32 *tmp, u32 *rows, const GraphView &gv, int MS, int MW)
+{
+    const int n = gv.n, stride = MW | 1;
+    for (int i = threadIdx.x; i < n * MW; i += blockDim.x) {
+        const int u = i / MW, w = i - u * MW;
+        tmp[u * stride + w] = __ldcg(marks + i);
+        rows[i] = 0;
+    }
+    __syncthreads();
+    const bool pairs = (MW & 1) == 0;
+    const int per_row = pairs ? MW >> 1 : MW;
+    for (int i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+        const int u = i / per_row, w = (i - u * per_row) << (pairs ? 1 : 0);
+        const u32 *row = tmp + u * stride;
+        const u32 e0 = gv.eidx[u] - gv.e_off, deg = gv.degree[u];
+        for (u32 k = 0; k < deg && e0 + k < gv.e_cnt; ++k) {
+            const u32 dst = gv.edge[2 * (size_t)(e0 + k)], ty = gv.edge[2 * (size_t)(e0 + k) + 1];
+            if (dst >= (u32)n) continue;                               // malformed edge: ignore, never fault
+            const u32 tq = ty >= (u32)MS ? ty % (u32)MS : ty;
+            const u32 lo = rotated_word(row, w, tq, MS, MW);
+            if (lo) atomicOr(rows + (size_t)dst * MW + w, lo);
+            if (pairs) {
+                const u32 hi = rotated_word(row, w + 1, tq, MS, MW);
+                if (hi) atomicOr(rows + (size_t)dst * MW + w + 1, hi);
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * MW; i += blockDim.x) tmp[(i / MW) * stride + (i % MW)] = 0;
+    __syncthreads();
 }
 
 // In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.

@@ -30,6 +30,8 @@ struct FitArgs {
     int stage;              // the state-resident kernel has its two graph staging buffers (0: every graph is read in place)
     int part_words;         // > 0: shared-memory words per CTA that accumulate one layer's messages before they are merged
     int gstage_words;       // global-state kernel: shared-memory words for a copy of the current (small) graph, 0 = none
+    int rows_words;         // state-resident kernel, graph sets of at most 32 nodes: shared-memory words for the message rows
+                            // [D-1][32][MW] that the CTA builds from the merged marks (build_message_rows), 0 = none
     int solo;               // one CTA learns the whole model: CTA barriers replace the grid barrier and the vote exchange
     int p_smem_words;       // solo and depth > 1: message buffers (words per parity) live in that CTA's shared memory
     // clause sharding over GPUs (one process per GPU): this rank learns clauses [c_begin, c_end); votes, message bits
@@ -91,6 +93,24 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
     return *(volatile int *)a.error == 0;
 }
 
+// Per-class quantities of the feedback decision that do not depend on the clause (kernels.py:373-384):
+// target = +1 / -1; thr = rd(1.0 * |y - clamp(sum)| / (2T)) as a float (see DevModel).
+__device__ __forceinline__ void class_decision_input(int T, int sum, int yk, int *target, float *thr)
+{
+    sum = sum > T ? T : (sum < -T ? -T : sum);
+    *target = 1 - 2 * (sum > yk);
+    *thr = __double2float_rd(1.0 * abs(yk - sum) / (double)(2 * T));
+}
+
+// Where collect_votes leaves the per-class decision inputs of a single-GPU fit (the thread that reads a class sum
+// computes them on the spot, which saves the CTA a pass and a barrier); y == nullptr: not wanted.
+struct DecisionInputs {
+    const int *y;
+    int *target;
+    float *thr;
+    int T;
+};
+
 // Class sums of one graph from per-CTA vote partials.
 //   Inside a rank, one atomic and one poll: every CTA adds, per class, ONE 64-bit word to the rank's accumulator of the
 //   step - arrival count in bits 48..63, its partial plus 2^31 (never negative) in bits 0..47 - and then polls the K
@@ -121,9 +141,12 @@ __device__ __forceinline__ void publish_votes(const FitArgs &a, unsigned long lo
     }
 }
 
-// Second half: wait for all votes of the step; totals in s_total (valid after the closing CTA barrier).
-__device__ __forceinline__ bool collect_votes(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_total, int K)
+// Second half: wait for all votes of the step; totals in s_total (valid after the closing CTA barrier), and with them the
+// decision inputs when `di` asks for them and there is one GPU (returns with *di_done set then).
+__device__ __forceinline__ bool collect_votes(const FitArgs &a, unsigned long long step, int par, u32 tag, int *s_total, int K,
+                                              const DecisionInputs &di, bool *di_done)
 {
+    *di_done = di.y != nullptr && a.world == 1;
     unsigned long long *acc = a.exchange + (size_t)2 * a.world * K + (size_t)(step & 3) * K;
     const unsigned long long want = (unsigned long long)gridDim.x + (unsigned long long)a.missing;   // test hook: a CTA that never adds
     for (int k = threadIdx.x; k < K; k += blockDim.x) {
@@ -136,6 +159,7 @@ __device__ __forceinline__ bool collect_votes(const FitArgs &a, unsigned long lo
         }
         const int mine = (int)(long long)((v & 0xffffffffffffull) - ((v >> 48) << 31));
         s_total[k] = mine;
+        if (*di_done) class_decision_input(di.T, mine, di.y[k], di.target + k, di.thr + k);
         if (a.world > 1 && blockIdx.x == 0) {
             const unsigned long long out = ((unsigned long long)(u32)mine << 32) | tag;
             const size_t slot = ((size_t)par * a.world + a.rank) * K + k;
@@ -168,7 +192,10 @@ __device__ __forceinline__ bool exchange_class_sums(const FitArgs &a, unsigned l
                                                     int *s_total, int K)
 {
     publish_votes(a, step, s_sum, K);
-    return collect_votes(a, step, par, tag, s_total, K);
+    DecisionInputs none;
+    none.y = nullptr; none.target = nullptr; none.thr = nullptr; none.T = 0;
+    bool done;
+    return collect_votes(a, step, par, tag, s_total, K, none, &done);
 }
 
 // Four consecutive draws of a clause stream: Philox block `block` (draws 4*block .. 4*block+3), or the
@@ -203,6 +230,14 @@ __device__ __forceinline__ void bernoulli_round(const DevModel &m, int clause, u
 
 // Graph copy of the global-state learning kernel: literal rows, per-node arrays of up to 32 nodes, edge rows.
 constexpr int kFitStageRowWords = 2560, kFitStageEdges = 384;
+constexpr int kFitStageGraphWords = kFitStageRowWords + 3 * 32 + 2 * kFitStageEdges;
+
+// One word, global -> shared, asynchronously (completion: cp.async.wait_all).
+__device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global_src)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global_src) : "memory");
+}
 
 constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of up to 8 positive classes x 32 words + 1
 
@@ -212,11 +247,14 @@ constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of
 // generated the layer's packed Bernoulli words beforehand (generate_mask_round; the layer's first draw is bit `pre_off`
 // of that stream); otherwise layers of at most 32 words take
 // the words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds in flight per
-// step, and wider layers generate them class by class.  Returns the draws consumed.
+// step, and wider layers generate them class by class.  Words [g_begin, g_end) of the layer are updated (a multiple of 32
+// apart: a wide layer can be split over several warps, every word's masks depend on the layer's first draw only).
+// Returns the draws the whole layer consumes.
 template <int MAXSB>
 __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
                                               bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
-                                              u64 pos0, int lane, u32 *pack, const u32 *pre, int pre_off, float p)
+                                              u64 pos0, int g_begin, int g_end, int lane, u32 *pack, const u32 *pre, int pre_off,
+                                              float p)
 {
     const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
     const bool all_ones = p >= 1.0f;         // every uniform is <= 1
@@ -224,7 +262,7 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
     const int shift = (int)(pos0 & 3);       // the layer's first draw sits `shift` bits into the packed stream
     int positives = 0;
 
-    for (int g0 = 0; g0 < W; g0 += 32) {
+    for (int g0 = g_begin; g0 < g_end; g0 += 32) {
         const int w = g0 + lane;
         const bool mine = w < W;
         const int wend = min(W, g0 + 32);
@@ -327,13 +365,7 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
 __device__ __forceinline__ void class_decision_inputs(const DevModel &m, const int *s_total, const int *y, int *s_target,
                                                       float *s_thr)
 {
-    for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
-        int sum = s_total[k];
-        sum = sum > m.T ? m.T : (sum < -m.T ? -m.T : sum);
-        const int yk = y[k];
-        s_target[k] = 1 - 2 * (sum > yk);
-        s_thr[k] = __double2float_rd(1.0 * abs(yk - sum) / (double)(2 * m.T));
-    }
+    for (int k = threadIdx.x; k < m.K; k += blockDim.x) class_decision_input(m.T, s_total[k], y[k], s_target + k, s_thr + k);
 }
 
 // Everything after the class sums for one clause (kernels.py:319-405 then :185-242), in the draw order of the
@@ -341,7 +373,7 @@ __device__ __forceinline__ void class_decision_inputs(const DevModel &m, const i
 // Lane-parallel throughout: node words, classes (16 per pass: both possible uniforms of every class are drawn at
 // once, lanes 0..31 = the pass's next 32 draws, and a short uniform scan replays the reference's short-circuit
 // order on them) and automaton words are spread over lanes; nothing per class goes through global memory.
-// `bits` = the clause's node-output words of the last layer; `P` = message rows [D-1][max_nodes][MW].
+// `bits` = the clause's node-output words of the last layer; `P` = message rows [D-1][p_nodes][MW].
 struct Decision {
     int chosen;   // selected true node or -1
     int upd_lo;   // feedback type of class `lane` (classes 0..31)
@@ -470,8 +502,8 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
 // first draw.
 template <int MAXSB>
 __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView &gv, const ClauseView &cv, const FitArgs &a,
-                                             const u32 *P, const Decision &dec, int npos, int c, int lane, u32 *pack,
-                                             const u32 *pre, int pre0_off, int pre0_words, const float *p_mask)
+                                             const u32 *P, int p_nodes, const Decision &dec, int npos, int c, int lane,
+                                             u32 *pack, const u32 *pre, int pre0_off, int pre0_words, const float *p_mask)
 {
     const bool clause_true = dec.chosen != -1;
     if (m.K <= 32 && __ballot_sync(kFull, dec.upd_lo != 0) == 0) {      // no feedback for this clause: nothing drawn, nothing changes
@@ -483,10 +515,10 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
     u64 pos = dec.pos;
 #pragma unroll 1
     for (int d = 0; d < m.D; ++d) {
-        const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * a.max_nodes + node) * m.MW;
+        const u32 *row = d == 0 ? gv.X + (size_t)node * m.L0 : P + ((size_t)(d - 1) * p_nodes + node) * m.MW;
         const int off = d == 0 ? pre0_off : (int)(pos & 3);
-        pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), dec.upd_lo, a.update, clause_true, within, row, d > 0, pos, lane,
-                                     pack, pre, off, p_mask[d]);
+        pos += layer_feedback<MAXSB>(m, c, d, cv.ta(d), dec.upd_lo, a.update, clause_true, within, row, d > 0, pos, 0,
+                                     d == 0 ? m.L0 : m.M, lane, pack, pre, off, p_mask[d]);
         if (pre) pre += d == 0 ? pre0_words : npos * m.M + 1;
     }
     if (lane == 0) *cv.pos = pos;
@@ -494,11 +526,12 @@ __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView 
 
 template <int MAXSB>
 __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
-                                                const FitArgs &a, const u32 *bits, const u32 *P, const int *s_target,
-                                                const float *s_thr, int c, int lane, u32 *pack, const float *p_mask)
+                                                const FitArgs &a, const u32 *bits, const u32 *P, int p_nodes,
+                                                const int *s_target, const float *s_thr, int c, int lane, u32 *pack,
+                                                const float *p_mask)
 {
     const Decision dec = clause_decide(m, gv, cv, a, bits, s_target, s_thr, c, lane);
-    clause_apply<MAXSB>(m, gv, cv, a, P, dec, 0, c, lane, pack, nullptr, 0, 0, p_mask);
+    clause_apply<MAXSB>(m, gv, cv, a, P, p_nodes, dec, 0, c, lane, pack, nullptr, 0, 0, p_mask);
 }
 
 // Round q of a packed Bernoulli stream that starts at Philox block `first_block`: the warp's 32 blocks

@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     // reads: a clause evaluation then waits for shared memory instead of for L2
     u32 *s_graph = a.gstage_words > 0 ? reinterpret_cast<u32 *>(s_mem + ((4 * m.K + 3) & ~3)) + max(a.part_words, 0) : nullptr;
     __shared__ u32 s_pack[16][kPackWords];
+    __shared__ int s_next;                        // next clause of the CTA that gets its feedback
     __shared__ FitShared s_fs;
     fill_fit_shared(&s_fs, m, a);
     const int lane = threadIdx.x & 31;
@@ -48,30 +49,75 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
         arrivals += gridDim.x * a.world;
         if (!grid_barrier(a, arrivals)) return;
     }
-    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+    // the whole first warp of CTA 0 reads the clock (a warp-uniform branch: one timing lane would serialise against the
+    // other 31 and count their instructions as its own); lane 0 reports
+    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x < 32;
     long long t_eval = 0, t_bar = 0, t_tot = 0, t_fb = 0, t_clauses = 0, t_merge = 0, t_stage = 0, t0 = clock64(), t1;
 
-    u64 step = 0;
-    for (int ep = 0; ep < a.epochs; ++ep) {
-        for (int64_t i = 0; i < a.count; ++i, ++step) {
-            const int64_t e = a.first + i;
+    // Small graphs are staged one step ahead (two buffers), their sizes two steps ahead (a ring of three): the copies are
+    // issued at the start of a step and have the whole step to land.  Fetched at the start of its own step instead, a
+    // graph's dependent loads (index arrays, then rows) would queue behind the automaton write-back of the step before.
+    __shared__ int s_size[3][4];                  // n, first node, first edge row, edge rows
+    const u64 steps = (u64)a.epochs * (u64)a.count;
+    int64_t e_cur = a.first, e_nxt = a.count > 1 ? a.first + 1 : a.first, e_nxt2 = a.count > 2 ? a.first + 2 : a.first;
+    auto advance = [&](int64_t e) { return e + 1 < a.first + a.count ? e + 1 : a.first; };
+    auto stage_fits = [&](const int *sz) {
+        return s_graph != nullptr && sz[0] <= 32 && sz[0] * m.L0 <= kFitStageRowWords && (u32)sz[3] <= (u32)kFitStageEdges &&
+               (u64)(u32)sz[2] + (u32)sz[3] <= g.total_edges;
+    };
+    auto fetch_sizes = [&](u64 st, int64_t e) {
+        if (s_graph != nullptr && threadIdx.x < 4 && st < steps) {
+            const u32 *src = threadIdx.x == 0 ? g.n_nodes : threadIdx.x == 1 ? g.node_index : threadIdx.x == 2 ? g.graph_edge0 : g.graph_edges;
+            async_copy_word(reinterpret_cast<u32 *>(&s_size[(u32)st % 3u][threadIdx.x]), src + e);
+        }
+    };
+    auto fetch_graph = [&](u64 st) {                // sizes of step st are in s_size[st % 3]
+        if (s_graph == nullptr || st >= steps) return;
+        const int *sz = s_size[(u32)st % 3u];
+        if (!stage_fits(sz)) return;
+        const int n = sz[0], base = sz[1], e0 = sz[2], ne = sz[3];
+        u32 *st_x = s_graph + (st & 1) * kFitStageGraphWords, *st_t = st_x + kFitStageRowWords, *st_d = st_t + 32, *st_i = st_d + 32, *st_e = st_i + 32;
+        for (int t = threadIdx.x; t < n * m.L0; t += blockDim.x) async_copy_word(st_x + t, g.X + (size_t)base * m.L0 + t);
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            async_copy_word(st_t + t, g.node_type + base + t);
+            async_copy_word(st_d + t, g.degree + base + t);
+            async_copy_word(st_i + t, g.edge_index + base + t);
+        }
+        for (int t = threadIdx.x; t < 2 * ne; t += blockDim.x) async_copy_word(st_e + t, g.edge + 2 * (size_t)e0 + t);
+    };
+    auto wait_copies = [&]() { asm volatile("cp.async.wait_all;" ::: "memory"); };
+    fetch_sizes(0, e_cur);
+    fetch_sizes(1, e_nxt);
+    wait_copies();
+    __syncthreads();
+    fetch_graph(0);
+    wait_copies();
+    __syncthreads();
+
+    int slot3 = 0;   // step % 3
+    for (u64 step = 0; step < steps; ++step) {
+        {
+            const int64_t e = e_cur;
             const int par = (int)(step & 1);
-            GraphView gv = global_graph(g, e, m.L0);
+            GraphView gv;
             u32 *P = par ? a.P_pair[1] : a.P_pair[0];
             const u32 *s_rows = nullptr;              // shared-memory copy of the message rows the current layer reads
-            if (s_graph != nullptr) {
-                // layout: literal rows [kFitStageRowWords] | type, degree, CSR start [3][32] | edge rows [2*kFitStageEdges] | message rows [32*MW]
-                const u32 ge0 = g.graph_edge0[e], gne = g.graph_edges[e];
-                if (gv.n <= 32 && gv.n * m.L0 <= kFitStageRowWords && gne <= (u32)kFitStageEdges && ge0 + gne <= g.total_edges) {
-                    u32 *st_x = s_graph, *st_t = st_x + kFitStageRowWords, *st_d = st_t + 32, *st_i = st_d + 32, *st_e = st_i + 32;
-                    for (int t = threadIdx.x; t < gv.n * m.L0; t += blockDim.x) st_x[t] = gv.X[t];
-                    for (int t = threadIdx.x; t < gv.n; t += blockDim.x) { st_t[t] = gv.type[t]; st_d[t] = gv.degree[t]; st_i[t] = gv.eidx[t]; }
-                    for (int t = threadIdx.x; t < 2 * (int)gne; t += blockDim.x) st_e[t] = g.edge[2 * (size_t)ge0 + t];
-                    gv.X = st_x; gv.type = st_t; gv.degree = st_d; gv.eidx = st_i; gv.edge = st_e; gv.e_off = ge0; gv.e_cnt = gne;
-                    s_rows = st_e + 2 * kFitStageEdges;
-                    __syncthreads();
-                }
+            if (s_graph == nullptr || !stage_fits(s_size[slot3])) {
+                gv = global_graph(g, e, m.L0);
+            } else {
+                // layout: [2] x (literal rows [kFitStageRowWords] | type, degree, CSR start [3][32] | edge rows [2*kFitStageEdges]) | message rows [D-1][32][MW]
+                u32 *st_x = s_graph + par * kFitStageGraphWords, *st_t = st_x + kFitStageRowWords, *st_d = st_t + 32, *st_i = st_d + 32, *st_e = st_i + 32;
+                gv.n = s_size[slot3][0];
+                gv.X = st_x; gv.type = st_t; gv.degree = st_d; gv.eidx = st_i; gv.edge = st_e;
+                gv.e_off = (u32)s_size[slot3][2]; gv.e_cnt = (u32)s_size[slot3][3];
+                s_rows = s_graph + 2 * kFitStageGraphWords;
             }
+            // staged (small) graphs: the CTAs merge their source-node marks and build the message rows themselves (flush_marks)
+            const bool merged_marks = s_rows != nullptr && s_part != nullptr && (32 + kTransposedTypes) * (m.MW | 1) <= a.part_words;
+            const u32 *rows_base = merged_marks ? s_rows : P;              // message rows [D-1][rows_nodes][MW] of this graph
+            const int rows_nodes = merged_marks ? 32 : a.max_nodes;
+            fetch_graph(step + 1);                    // lands in the other buffer while this step runs
+            fetch_sizes(step + 2, e_nxt2);
 
             for (int d = 0; d < m.D; ++d) {
                 const bool last = d == m.D - 1;
@@ -80,14 +126,9 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                     arrivals += gridDim.x * a.world;
                     if (!grid_barrier(a, arrivals)) return;
                     GTM_LAP(t_bar);
-                    if (d == 1) clear_next_messages(m, a, par ? a.P_pair[0] : a.P_pair[1], (int)g.n_nodes[i + 1 < a.count ? e + 1 : a.first]);
-                    if (s_rows != nullptr) {          // the messages of the layer below are complete: this CTA's copy of them
-                        u32 *dst = const_cast<u32 *>(s_rows);
-                        const u32 *src = P + (size_t)(d - 1) * layer_words;
-                        __syncthreads();              // the previous layer's readers are done
-                        for (int t = threadIdx.x; t < gv.n * m.MW; t += blockDim.x) dst[t] = __ldcg(src + t);
-                        __syncthreads();
-                    }
+                    if (d == 1) clear_next_messages(m, a, par ? a.P_pair[0] : a.P_pair[1], step + 1 < steps ? (int)g.n_nodes[e_nxt] : 0);
+                    // the marks of the layer below are complete: this CTA's message rows from them
+                    if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, const_cast<u32 *>(s_rows) + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
                 }
                 GTM_LAP(t_stage);
                 ScatterTargets targets;
@@ -108,13 +149,17 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                     }
                     const u32 any = eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? cno_row(sc, m.C, d - 1, c) : nullptr,
                                                       cno_row(sc, m.C, d, c),
-                                                      d > 0 ? (s_rows != nullptr ? s_rows : P + (size_t)(d - 1) * layer_words) : nullptr,
+                                                      d > 0 ? rows_base + (size_t)(d - 1) * rows_nodes * m.MW : nullptr,
                                                       last ? nullptr : &targets, lane);
                     if (last && any)
                         for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], m.weights[(size_t)k * m.C + c]);
                 }
                 GTM_LAP(t_clauses);
-                if (targets.local) {        // this CTA's share of the layer's messages, merged before the grid barrier
+                if (targets.local && merged_marks) {
+                    __syncthreads();
+                    flush_marks(targets, gv.n, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
+                    GTM_LAP(t_merge);
+                } else if (targets.local) { // this CTA's share of the layer's messages, merged before the grid barrier
                     __syncthreads();
                     flush_messages(targets, gv, m.MS, m.MW);
                     __syncthreads();
@@ -128,18 +173,34 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
             GTM_LAP(t_tot);
             if (!eval_only) {
                 class_decision_inputs(m, s_total, a.Y + (size_t)e * m.K, s_target, s_thr);
+                if (threadIdx.x == 0) s_next = 0;
                 __syncthreads();
-                for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
+                // The CTA's clauses (those its warps evaluated) are handed out one at a time to whichever warp is free:
+                // a clause with Type I feedback costs tens of Philox rounds, one without costs next to nothing, and a
+                // fixed assignment leaves most warps waiting for the unluckiest one.  Everything a clause owns is in
+                // global memory and was last written by this CTA before a CTA barrier.
+                const int warps_cta = (int)(blockDim.x >> 5);
+                const int rounds = (a.c_end - a.c_begin + nwarps - 1) / nwarps;
+                while (true) {
+                    int j = 0;
+                    if (lane == 0) j = atomicAdd(&s_next, 1);
+                    j = __shfl_sync(kFull, j, 0);
+                    if (j >= rounds * warps_cta) break;
+                    const int c = a.c_begin + (int)blockIdx.x * warps_cta + (j % warps_cta) + (j / warps_cta) * nwarps;
+                    if (c >= a.c_end) continue;
                     const ClauseView cv = global_view(m, sc.n_inc, c);
-                    clause_feedback<MAXSB>(m, gv, cv, a, cno_row(sc, m.C, m.D - 1, c), P, s_target, s_thr, c, lane,
+                    clause_feedback<MAXSB>(m, gv, cv, a, cno_row(sc, m.C, m.D - 1, c), rows_base, rows_nodes, s_target, s_thr, c, lane,
                                            s_pack[threadIdx.x >> 5], s_fs.p_mask);
                 }
             }
-            __syncthreads();   // s_total is rewritten by the next graph
+            wait_copies();
+            __syncthreads();   // s_total is rewritten by the next graph; the next graph's copy is complete
             GTM_LAP(t_fb);
+            e_cur = e_nxt; e_nxt = e_nxt2; e_nxt2 = advance(e_nxt2);
+            slot3 = slot3 == 2 ? 0 : slot3 + 1;
         }
     }
-    if (timer) {
+    if (timer && threadIdx.x == 0) {
         a.phase_cycles[0] = (unsigned long long)t_eval; a.phase_cycles[1] = (unsigned long long)t_bar;
         a.phase_cycles[2] = (unsigned long long)t_tot; a.phase_cycles[3] = (unsigned long long)t_fb;
         a.phase_cycles[4] = (unsigned long long)t_clauses; a.phase_cycles[5] = (unsigned long long)t_merge;

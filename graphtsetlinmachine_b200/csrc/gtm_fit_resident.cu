@@ -19,12 +19,6 @@ constexpr int kStageNodes = 256, kStageRowWords = 1536, kStageEdges = 512;
 constexpr int kStageWords = kStageRowWords + 3 * kStageNodes + 2 * kStageEdges;
 constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I classes, draw position (2), work items, feedback type (before the decisions: uniform) of 32 classes, bit offset of layer 0's first draw in its mask stream
 
-__device__ __forceinline__ void async_copy_word(u32 *smem_dst, const u32 *global_src)
-{
-    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(global_src) : "memory");
-}
-
 // State-resident learning kernel.  Same schedule as fit_kernel, but everything a clause owns lives in the shared
 // memory of the CTA that owns the clause for the whole launch: automaton planes of every layer, weights, message
 // hypervector, draw counter, include count and the node-output words.  The graph of the NEXT step (rows, node
@@ -75,6 +69,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
     // transposed copy of the current graph (graphs of 33..1024 nodes): literal rows, then node-type masks
     const int t_rows = 32 * max(m.L0, m.MW);
     u32 *s_T = s_clauses + (size_t)a.clauses_per_cta * a.clause_words + a.part_words + 2 * a.p_smem_words;
+    // message rows [D-1][32][MW] that the CTA builds from the merged marks (graph sets of at most 32 nodes)
+    u32 *s_rows = a.rows_words > 0 ? s_T + (a.t_stride > 0 ? (size_t)(t_rows + kTransposedTypes) * a.t_stride : 0) : nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int c_lo = min(a.c_end, a.c_begin + (int)blockIdx.x * a.clauses_per_cta), c_hi = min(a.c_end, c_lo + a.clauses_per_cta);
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
@@ -160,7 +156,9 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
         arrivals += gridDim.x * a.world;
         if (!grid_barrier(a, arrivals)) return;
     }
-    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+    // the whole first warp of CTA 0 reads the clock (a warp-uniform branch: one timing lane would serialise against the
+    // other 31 and count their instructions as its own); lane 0 reports
+    const bool timer = a.timers != 0 && blockIdx.x == 0 && threadIdx.x < 32;
     const bool fine = timer && a.timers >= 2;     // timers == 2: slots 4..7 split the evaluation instead of the feedback
 #define GTM_LAPE(acc) do { if (fine) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)
 #define GTM_LAPB(acc) do { if (timer && !fine) { t1 = clock64(); acc += t1 - t0; t0 = t1; } } while (0)
@@ -189,6 +187,11 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
         tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (gv.n + 31) >> 5;
         const bool transposed = kBatchNodes && a.t_stride > 0 && gv.n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         if (a.timers == 3) GTM_LAPE(t_x0);
+        // small graphs: the CTAs merge their source-node marks and build the message rows themselves (flush_marks)
+        const bool merged_marks = !kBatchNodes && !solo && s_rows != nullptr && s_part != nullptr && gv.n <= 32 &&
+                                  (32 + kTransposedTypes) * (m.MW | 1) <= a.part_words;
+        const u32 *rows_base = merged_marks ? s_rows : P;                  // message rows [D-1][rows_nodes][MW] of this graph
+        const int rows_nodes = merged_marks ? 32 : a.max_nodes;
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
         if (a.timers == 3) GTM_LAPE(t_x1);
         fetch_sizes(step + 2, e_nxt2);
@@ -206,6 +209,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 }
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
+                if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, s_rows + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
             }
             if (transposed) {
                 // this layer's literal rows, one bit per node: the graph's literals, or the messages of the layer below
@@ -233,13 +237,17 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     ? eval_clause_layer_transposed(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
                                                    tg, last ? nullptr : &targets, lane)
                     : eval_clause_layer<kBatchNodes>(m, gv, g.n_types, cv, c, d, d > 0 ? node_words(c, d - 1) : nullptr, node_words(c, d),
-                                                  d > 0 ? P + (size_t)(d - 1) * layer_words : nullptr,
+                                                  d > 0 ? rows_base + (size_t)(d - 1) * rows_nodes * m.MW : nullptr,
                                                   last ? nullptr : &targets, lane);
                 if (last && any)
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
             }
             if (a.timers != 3) GTM_LAPE(t_x1);
-            if (targets.local) {            // this CTA's share of the layer's messages, merged before the grid barrier
+            if (targets.local && merged_marks) {
+                __syncthreads();
+                flush_marks(targets, gv.n, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
+                if (a.timers != 3) GTM_LAPE(t_x3);
+            } else if (targets.local) {     // this CTA's share of the layer's messages, merged before the grid barrier
                 __syncthreads();
                 flush_messages(targets, gv, m.MS, m.MW);
                 __syncthreads();
@@ -254,6 +262,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
                 s_total[k] = s_sum[k];
                 a.class_sum_tap[k] = s_sum[k];
+                class_decision_input(m.T, s_sum[k], y[k], s_target + k, s_thr + k);
                 s_sum[k] = 0;
             }
         } else {
@@ -278,14 +287,23 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     generate_mask_round(m, c, B0, 4 * spec_rounds, q, s_pre + (size_t)(c - c_lo) * a.pre_words, lane, p0);
             }
         }
-        if (solo) __syncthreads();
-        else if (!collect_votes(a, step, par, a.tag_base + (u32)step + 1u, s_total, m.K)) return;
+        bool inputs_done = true;
+        if (solo) {
+            __syncthreads();
+        } else {
+            DecisionInputs di;
+            di.y = y; di.target = s_target; di.thr = s_thr; di.T = m.T;
+            if (!collect_votes(a, step, par, a.tag_base + (u32)step + 1u, s_total, m.K, di, &inputs_done)) return;
+        }
         GTM_LAP(t_tot);
-        class_decision_inputs(m, s_total, y, s_target, s_thr);
-        __syncthreads();
+        if (!inputs_done) {
+            class_decision_inputs(m, s_total, y, s_target, s_thr);
+            __syncthreads();
+        }
         if (a.pre_words > 0) {
             // cooperative feedback: decisions per clause, then every (clause, layer, round) of mask generation that is still
             // missing is a work item shared by all warps of the CTA, then the automaton updates per clause
+            int any_items = 0;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
@@ -321,11 +339,13 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     }
                 }
                 rec[5 + lane] = dec.upd_lo;
+                any_items |= items;
             }
-            __syncthreads();
+            // the work-item phase and its two CTA barriers only when some clause of the CTA has items
+            any_items = __syncthreads_or(any_items > 0);
             GTM_LAPB(t_x0);
             GTM_LAPB(t_x1);
-            {
+            if (any_items) {
                 const int entries = s_item_off[0], total = s_item_off[1];
                 for (int i = warp; i < total; i += nwarps) {
                     int ci = 0, firsti = 0;
@@ -356,8 +376,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     }
                 }
             }
-            __syncthreads();
-            if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }     // next step's item table starts empty
+            if (any_items) {
+                __syncthreads();
+                if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }     // next step's item table starts empty
+            }
             GTM_LAPB(t_x2);
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
@@ -367,14 +389,64 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 dec.pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
                 dec.upd_lo = rec[5 + lane];
                 const int rounds0 = (words0_of(rec[1], rec[37]) + 3) >> 2;
-                clause_apply<MAXSB>(m, gv, cv, a, P, dec, rec[1], c, lane, s_pack + warp * kPackWords,
+                clause_apply<MAXSB>(m, gv, cv, a, rows_base, rows_nodes, dec, rec[1], c, lane, s_pack + warp * kPackWords,
                                     rec[4] >= 0 ? s_pre + (size_t)(c - c_lo) * a.pre_words : nullptr, rec[37],
                                     4 * max(rounds0, spec_rounds), s_fs.p_mask);
             }
+        } else if (m.K <= 32) {
+            // wide layers: the clause's warp decides; the automaton updates are then work items of one (clause, layer,
+            // 32-word stretch) each, shared by all warps of the CTA - a clause with Type I feedback costs tens of Philox
+            // rounds per layer, one without costs nothing, and there are hardly more clauses than warps
+            const int chunks0 = (m.L0 + 31) >> 5, chunksM = (m.M + 31) >> 5;
+            for (int c = c_lo + warp; c < c_hi; c += nwarps) {
+                const ClauseView cv = view_of(c);
+                const Decision dec = clause_decide(m, gv, cv, a, node_words(c, m.D - 1), s_target, s_thr, c, lane);
+                const int npos = __popc(__ballot_sync(kFull, dec.upd_lo > 0));
+                const bool any_feedback = __ballot_sync(kFull, dec.upd_lo != 0) != 0;
+                int *rec = s_rec + (size_t)(c - c_lo) * kRecWords;
+                if (lane == 0) {
+                    rec[0] = dec.chosen; rec[1] = npos;
+                    rec[2] = (int)(u32)dec.pos; rec[3] = (int)(u32)(dec.pos >> 32);
+                    *cv.pos = dec.pos + (any_feedback ? (u64)npos * (u64)(m.L0 + (m.D - 1) * m.M) * 32u : 0u);
+                    if (any_feedback) {
+                        const int slot = atomicAdd(&s_item_off[0], 1);
+                        const int firsti = atomicAdd(&s_item_off[1], chunks0 + (m.D - 1) * chunksM);
+                        s_item_off[2 + 2 * slot] = c - c_lo;
+                        s_item_off[3 + 2 * slot] = firsti;
+                    }
+                }
+                rec[5 + lane] = dec.upd_lo;
+            }
+            __syncthreads();
+            const int entries = s_item_off[0], total = s_item_off[1];
+            for (int i = warp; i < total; i += nwarps) {
+                int ci = 0, firsti = 0;
+                for (int t = 0; t < entries; ++t) {                   // the entry whose range holds item i
+                    const int f = s_item_off[3 + 2 * t];
+                    if (f <= i && f >= firsti) { firsti = f; ci = s_item_off[2 + 2 * t]; }
+                }
+                const int c = c_lo + ci;
+                const ClauseView cv = view_of(c);
+                const int *rec = s_rec + (size_t)ci * kRecWords;
+                const int chosen = rec[0], npos = rec[1];
+                const u64 pos = (u64)(u32)rec[2] | ((u64)(u32)rec[3] << 32);
+                const int r = i - firsti;
+                const int l = r < chunks0 ? 0 : 1 + (r - chunks0) / chunksM;
+                const int g0 = 32 * (l == 0 ? r : (r - chunks0) % chunksM);
+                const int W = l == 0 ? m.L0 : m.M;
+                const u64 pos_l = pos + (l == 0 ? 0u : (u64)npos * (u64)(m.L0 + (l - 1) * m.M) * 32u);
+                const bool clause_true = chosen != -1;
+                const int node = clause_true ? chosen : 0;
+                const u32 *row = l == 0 ? gv.X + (size_t)node * m.L0 : rows_base + ((size_t)(l - 1) * rows_nodes + node) * m.MW;
+                layer_feedback<MAXSB>(m, c, l, cv.ta(l), rec[5 + lane], a.update, clause_true, *cv.n_inc <= m.max_included, row, l > 0,
+                                      pos_l, g0, min(W, g0 + 32), lane, s_pack + warp * kPackWords, nullptr, 0, s_fs.p_mask[l]);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) { s_item_off[0] = 0; s_item_off[1] = 0; }     // next step's item table starts empty
         } else {
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
-                clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), P, s_target, s_thr, c, lane, s_pack + warp * kPackWords, s_fs.p_mask);
+                clause_feedback<MAXSB>(m, gv, cv, a, node_words(c, m.D - 1), rows_base, rows_nodes, s_target, s_thr, c, lane, s_pack + warp * kPackWords, s_fs.p_mask);
             }
         }
         GTM_LAPB(t_x3);
@@ -397,7 +469,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             for (int t = lane; t < total; t += 32) dst[t] = src[t];
         }
     }
-    if (timer) {
+    if (timer && threadIdx.x == 0) {
         a.phase_cycles[0] = (unsigned long long)t_eval; a.phase_cycles[1] = (unsigned long long)t_bar;
         a.phase_cycles[2] = (unsigned long long)t_tot; a.phase_cycles[3] = (unsigned long long)t_fb;
         a.phase_cycles[4] = (unsigned long long)t_x0; a.phase_cycles[5] = (unsigned long long)t_x1;
@@ -439,7 +511,7 @@ static const void *resident_kernel_for(int state_bits, int max_nodes, int depth)
 }
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1, t_stride = 0; size_t smem = 0; };
+struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0; size_t smem = 0; };
 
 static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses, bool solo_allowed)
 {
@@ -467,15 +539,17 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
         for (int choice = part_possible ? 0 : 2; choice < 3; ++choice) {
             const int with_part = choice < 2, stage = choice != 1;
             int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
-            const int cpb = (d.C + grid - 1) / grid;
+            int cpb = (d.C + grid - 1) / grid;
+            if (m->opt_fit_block_clauses > 0) cpb = m->opt_fit_block_clauses;
             grid = (d.C + cpb - 1) / cpb;
+            if (grid > per_sm * m->sm_count) continue;
             size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + (stage ? 2 * (size_t)kStageWords : 0) + 12 * (size_t)kPackWords) * sizeof(int) +
                           ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
                           (size_t)cpb * words * sizeof(u32);
             // a model that one CTA learns alone needs no grid-wide step; its message buffers (two parities) then live in
             // shared memory, which they must fit (messages written with atomics to global memory would need a device-scope
             // acquire before they are read, i.e. the grid barrier)
-            int solo = 0, p_smem_words = 0, part_words = 0;
+            int solo = 0, p_smem_words = 0, part_words = 0, rows_words = 0;
             if (solo_allowed && grid == 1 && (d.D == 1 || smem + 2 * p_words * sizeof(u32) <= 96 * 1024)) {
                 solo = 1;
                 p_smem_words = (int)p_words;
@@ -483,6 +557,10 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
             } else if (with_part) {
                 part_words = (int)(layer_bytes / sizeof(u32));
                 smem += layer_bytes;
+                if (ds->max_nodes <= 32) {      // merged marks: the message rows of all layers below the last live in the CTA
+                    rows_words = (d.D - 1) * 32 * d.MW;
+                    smem += (size_t)rows_words * sizeof(u32);
+                }
             }
             if (with_t) smem += t_bytes;
             if (smem > 200 * 1024) continue;
@@ -491,7 +569,7 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
             if ((long long)occ * m->sm_count < grid) continue;
             plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
-            plan.solo = solo; plan.p_smem_words = p_smem_words; plan.part_words = part_words; plan.stage = stage;
+            plan.solo = solo; plan.p_smem_words = p_smem_words; plan.part_words = part_words; plan.stage = stage; plan.rows_words = rows_words;
             plan.t_stride = with_t ? t_stride : 0;
             return plan;
         }
@@ -554,7 +632,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         GTM_CU(cudaMemsetAsync((char *)cm.block + cm.exchange_off + (size_t)2 * cm.world * d.K * sizeof(unsigned long long), 0,
                                (size_t)4 * d.K * sizeof(unsigned long long), m->stream));
         resident = cm.resident; grid = cm.grid;
-        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride;
+        a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride; a.rows_words = cm.rows_words;
         smem = cm.smem;
     } else {
         a.world = 1; a.rank = 0; a.c_begin = 0; a.c_end = d.C;
@@ -574,7 +652,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         resident = plan.grid > 0;
         grid = resident ? plan.grid : m->fit_grid;
         a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
-        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage; a.t_stride = plan.t_stride;
+        a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage; a.t_stride = plan.t_stride; a.rows_words = plan.rows_words;
         smem = plan.smem;
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
@@ -584,7 +662,8 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     if (resident) {
         fn = resident_kernel_for(d.SB, ds->max_nodes, d.D);
         block = kResidentThreads;
-        if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // static and dynamic shared memory together may pass 48 KB well before the dynamic part alone does
+        if (smem > 16 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &a};
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
     } else {
@@ -594,9 +673,10 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         const size_t layer_bytes = (size_t)(((ds->max_nodes + 31) & ~31) + kTransposedTypes) * (d.MW | 1) * sizeof(u32);
         a.part_words = (!eval_only && d.D > 1 && layer_bytes <= 72 * 1024) ? (int)(layer_bytes / sizeof(u32)) : 0;
         // graph sets of at most 32 nodes per graph: the current graph (and the message rows a layer reads) in shared memory
-        a.gstage_words = (!eval_only && ds->max_nodes <= 32) ? kFitStageRowWords + 3 * 32 + 2 * kFitStageEdges + 32 * d.MW : 0;
+        a.gstage_words = (!eval_only && ds->max_nodes <= 32) ? 2 * kFitStageGraphWords + std::max(1, d.D - 1) * 32 * d.MW : 0;
         smem = (size_t)((4 * d.K + 3) & ~3) * sizeof(int) + ((size_t)a.part_words + a.gstage_words) * sizeof(u32);
-        if (smem > 48 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // static and dynamic shared memory together may pass 48 KB well before the dynamic part alone does
+        if (smem > 16 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &sc, &a, &eval_only};
         GTM_CU(cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(block), args, smem, m->stream));
     }
@@ -642,7 +722,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     cm.resident = plan.grid > 0;
     if (cm.resident) {
         cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
-        cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.t_stride = plan.t_stride; cm.smem = plan.smem;
+        cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.t_stride = plan.t_stride; cm.rows_words = plan.rows_words; cm.smem = plan.smem;
     } else {
         const int warps = m->fit_block / 32;
         cm.grid = std::max(1, std::min(m->fit_grid, (per + warps - 1) / warps));

@@ -23,6 +23,7 @@ struct gtm_model {
     int *score_error = nullptr;               // raised by scoring kernels that skipped a malformed graph (device-pointer inputs)
     int *error = nullptr, *clause_node = nullptr, *update = nullptr, *class_sum_tap = nullptr;
     unsigned long long *exchange = nullptr;   // vote exchange area of a single-GPU fit (exchange_bytes(1, K))
+    int opt_fit_block_clauses = 0;            // > 0: clauses per thread block of the state-resident kernel (0: automatic)
     int opt_fit_kernel = 0;                   // 0 auto, 1 state in global memory, 2 state resident in shared memory
     int opt_fit_wait_ms = 2000;               // budget of one device-side wait of the learning kernels
     int opt_fit_missing_cta = 0;              // test hook: waits expect one arrival that never comes (they must run out cleanly)
@@ -47,7 +48,7 @@ struct FitComm {
     size_t bytes = 0, exchange_off = 0, P_off[2] = {0, 0};
     int world = 1, rank = 0, grid = 0;
     bool resident = false;
-    int clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1, t_stride = 0;
+    int clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0;
     size_t smem = 0;
     bool connected = false, broken = false;
     u32 tag_base = 0;
