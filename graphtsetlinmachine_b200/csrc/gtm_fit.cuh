@@ -220,14 +220,6 @@ __device__ __forceinline__ u32 bernoulli_nibbles(const DevModel &m, int clause, 
     return nib << (4 * (lane & 7));
 }
 
-__device__ __forceinline__ void bernoulli_round(const DevModel &m, int clause, u64 first_block, int round, float p,
-                                                int lane, u32 (&words)[4])
-{
-    const u32 mine = __reduce_or_sync(0xffu << (lane & 24), bernoulli_nibbles(m, clause, first_block + (u64)round * 32 + lane, p, lane));
-#pragma unroll
-    for (int i = 0; i < 4; ++i) words[i] = __shfl_sync(kFull, mine, 8 * i);
-}
-
 // Graph copy of the global-state learning kernel: literal rows, per-node arrays of up to 32 nodes, edge rows.
 constexpr int kFitStageRowWords = 2560, kFitStageEdges = 384;
 constexpr int kFitStageGraphWords = kFitStageRowWords + 3 * 32 + 2 * kFitStageEdges;
@@ -245,9 +237,8 @@ constexpr int kPackWords = 264;   // per-warp scratch: packed Bernoulli words of
 // the clause; lanes hold one automaton word each (planes in registers).  `upd_lo` holds the feedback type of
 // class `lane` (classes 0..31); further classes are read back from `update`.  Masks come from `pre` when the CTA
 // generated the layer's packed Bernoulli words beforehand (generate_mask_round; the layer's first draw is bit `pre_off`
-// of that stream); otherwise layers of at most 32 words take
-// the words of up to 8 classes at a time through `pack` (per-warp shared scratch), two Philox rounds in flight per
-// step, and wider layers generate them class by class.  Words [g_begin, g_end) of the layer are updated (a multiple of 32
+// of that stream); otherwise the words of up to 8 classes at a time are generated into `pack` (per-warp shared scratch),
+// two Philox rounds in flight per step.  Words [g_begin, g_end) of the layer are updated (a multiple of 32
 // apart: a wide layer can be split over several warps, every word's masks depend on the layer's first draw only).
 // Returns the draws the whole layer consumes.
 template <int MAXSB>
@@ -271,29 +262,36 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
         for (int b = 0; b < plane_bound<MAXSB>(SB); ++b) pl[b] = (b < SB && mine) ? ta[(size_t)b * W + w] : 0u;
         u32 x = 0;
         if (mine && clause_true) x = row_is_msg ? msg_word(row, w, m.MS, m.MW) : row[w];
-        int rank = 0, cached = -1;
+        int rank = 0;
         bool dirty = false;
-        u32 sw[4] = {0, 0, 0, 0};
         for (int kb = 0; kb < m.K; kb += 32) {
             const int vals = kb == 0 ? upd_lo : (kb + lane < m.K ? update[(size_t)(kb + lane) * m.C + c] : 0);
             const int kn = min(32, m.K - kb);
             const u32 posmask = __ballot_sync(kFull, vals > 0 && lane < kn);
             for (int k8 = 0; k8 < kn; k8 += 8) {
                 const int npos8 = __popc((posmask >> k8) & 0xffu);
-                const bool packed = pre == nullptr && W <= 32 && npos8 > 0 && !all_ones;
+                const bool packed = pre == nullptr && npos8 > 0 && !all_ones;
                 if (packed) {
-                    // packed-stream words rank*W .. (rank+npos8)*W [+1 when the stream is not word-aligned]
-                    const int j0 = rank * W, j1 = (rank + npos8) * W - (shift ? 0 : 1);
+                    // The masks of these classes for words [g0, wend) go through `pack`, two Philox rounds in flight per
+                    // step.  A layer of at most 32 words: stream words rank*W .. (rank+npos8)*W [+1 when the stream is not
+                    // word-aligned] in one run.  A wider layer: class by class, 33 words apart in `pack`, stream words
+                    // r*W + g0 .. r*W + wend [+1].
                     __syncwarp();
-                    for (int q = j0 >> 2; q <= j1 >> 2; q += 2) {
-                        const u32 na = bernoulli_nibbles(m, c, first_block + (u64)q * 32 + lane, p, lane);
-                        const u32 nb = bernoulli_nibbles(m, c, first_block + (u64)(q + 1) * 32 + lane, p, lane);
-                        const u32 wa = __reduce_or_sync(0xffu << (lane & 24), na);
-                        const u32 wb = __reduce_or_sync(0xffu << (lane & 24), nb);
-                        if ((lane & 7) == 0) {
-                            const int ja = 4 * q + (lane >> 3) - j0, jb = ja + 4;
-                            if (ja >= 0 && ja <= j1 - j0) pack[ja] = wa;
-                            if (jb >= 0 && jb <= j1 - j0) pack[jb] = wb;
+                    const int runs = W <= 32 ? 1 : npos8;
+                    for (int cls = 0; cls < runs; ++cls) {
+                        const int j0 = (rank + cls) * W + g0;
+                        const int j1 = (W <= 32 ? (rank + npos8) * W : (rank + cls) * W + wend) - (shift ? 0 : 1);
+                        u32 *dst = pack + cls * 33;
+                        for (int q = j0 >> 2; q <= j1 >> 2; q += 2) {
+                            const u32 na = bernoulli_nibbles(m, c, first_block + (u64)q * 32 + lane, p, lane);
+                            const u32 nb = bernoulli_nibbles(m, c, first_block + (u64)(q + 1) * 32 + lane, p, lane);
+                            const u32 wa = __reduce_or_sync(0xffu << (lane & 24), na);
+                            const u32 wb = __reduce_or_sync(0xffu << (lane & 24), nb);
+                            if ((lane & 7) == 0) {
+                                const int ja = 4 * q + (lane >> 3) - j0, jb = ja + 4;
+                                if (ja >= 0 && ja <= j1 - j0) dst[ja] = wa;
+                                if (jb >= 0 && jb <= j1 - j0) dst[jb] = wb;
+                            }
                         }
                     }
                     __syncwarp();
@@ -314,24 +312,11 @@ __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int laye
                             const u32 hi = (mine && sh) ? pre[at + 1] : 0u;
                             mask = __funnelshift_r(lo, hi, sh);
                         } else if (packed) {
-                            const u32 lo = mine ? pack[local * W + lane] : 0u;
-                            const u32 hi = (mine && shift) ? pack[local * W + lane + 1] : 0u;
+                            const u32 *src = pack + (W <= 32 ? local * W : local * 33);
+                            const u32 lo = mine ? src[lane] : 0u;
+                            const u32 hi = (mine && shift) ? src[lane + 1] : 0u;
                             mask = __funnelshift_r(lo, hi, shift);
                             ++local;
-                        } else if (!all_ones) {
-                            const int j0 = rank * W + g0;                        // packed-stream word of lane 0's mask
-                            const int j1 = rank * W + wend - (shift ? 0 : 1);    // last packed word needed
-                            u32 lo = 0, hi = 0;
-                            for (int q = j0 >> 2; q <= j1 >> 2; ++q) {
-                                if (q != cached) { bernoulli_round(m, c, first_block, q, p, lane, sw); cached = q; }
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const int rel = 4 * q + i - j0;
-                                    if (rel == lane) lo = sw[i];
-                                    if (rel - 1 == lane) hi = sw[i];
-                                }
-                            }
-                            mask = __funnelshift_r(lo, hi, shift);
                         }
                         if (clause_true && within_budget) {
                             automata_inc<MAXSB>(pl, SB, m.boost == 1 ? x : (x & ~mask));
