@@ -118,7 +118,10 @@ def peaks():
 
 # DRAM bytes per graph of the dominant scoring kernel from ncu captures (profiles/): dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch divided by the graphs of that launch; None where no capture exists
-NCU_DRAM_BYTES_PER_GRAPH = {2: (186.750208e6 + 124.236288e6) / 4194304}
+NCU_DRAM_BYTES_PER_GRAPH = {1: (270.0e6 + 30.0e6) / 4194304,
+                            2: (186.750208e6 + 124.236288e6) / 4194304,
+                            4: (145.0e6 + 390.0e6) / 512,
+                            5: (8.885644e9 + 3.636144e9) / 32768}
 
 
 class ClockSampler:

@@ -336,8 +336,19 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
 // buffer (the same global rows, node-major, on every rank; a clause-sharded fit sends a peer only the bits that were new
 // in its own buffer).  After the grid barrier every CTA reads the merged marks once (n * MW words) and builds the
 // destination rows itself, in shared memory (build_message_rows).  All threads of the CTA, between two CTA barriers.
-__device__ __forceinline__ void flush_marks(const ScatterTargets &t, int n, int MW)
+__device__ __forceinline__ void flush_marks(const ScatterTargets &t, const GraphView &gv, int MW)
 {
+    const int n = gv.n;
+    if (t.all != nullptr) {         // marks of clauses that are true on every node of their type: into the nodes' rows first
+        for (int i = threadIdx.x; i < n * MW; i += blockDim.x) {
+            const int u = i / MW, w = i - u * MW;
+            const u32 ty = gv.type[u];
+            const u32 v = ty < (u32)kTransposedTypes ? t.all[ty * (MW | 1) + w] : 0u;
+            if (v) local_row(t, u, MW)[w] |= v;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < kTransposedTypes * (MW | 1); i += blockDim.x) t.all[i] = 0;
+    }
     const bool pairs = (MW & 1) == 0;
     const int per_row = pairs ? MW >> 1 : MW;
     for (int i = threadIdx.x; i < n * per_row; i += blockDim.x) {
@@ -404,6 +415,79 @@ __device__ __forceinline__ void build_message_rows(const u32 *marks, u32 *tmp, u
     __syncthreads();
     for (int i = threadIdx.x; i < n * MW; i += blockDim.x) tmp[(i / MW) * stride + (i % MW)] = 0;
     __syncthreads();
+}
+
+// build_message_rows for graphs of any size.  `src` = a CTA buffer of at least n * MW words that receives a copy of the
+// merged marks (node-major, stride MW), `rows` = the CTA's local marks buffer (n rows, stride MW | 1), which is left
+// holding the destination rows; `out` (global, node-major, stride MW), when given, receives them too, every CTA writing
+// the rows b, b + gridDim.x, ... - the feedback of the step reads single rows there.  All threads; ends with a barrier.
+__device__ __forceinline__ void build_message_rows_large(const u32 *marks, u32 *src, u32 *rows, u32 *out, const GraphView &gv,
+                                                         int MS, int MW)
+{
+    const int n = gv.n, stride = MW | 1;
+    constexpr int kInFlight = 4;      // loads per thread that are issued together (a larger graph's arrays are in global memory)
+    if ((reinterpret_cast<uintptr_t>(marks) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        // 16 bytes per asynchronous copy, all of a thread's copies in flight at once
+        const int quads = (n * MW) >> 2;
+        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(src + 4 * i);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(marks + 4 * i) : "memory");
+        }
+        for (int i = 4 * quads + threadIdx.x; i < n * MW; i += blockDim.x) src[i] = __ldcg(marks + i);
+    } else {
+        for (int i0 = threadIdx.x; i0 < n * MW; i0 += kInFlight * blockDim.x) {
+            u32 v[kInFlight];
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) v[q] = i0 + q * (int)blockDim.x < n * MW ? __ldcg(marks + i0 + q * blockDim.x) : 0u;
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) if (i0 + q * (int)blockDim.x < n * MW) src[i0 + q * blockDim.x] = v[q];
+        }
+    }
+    for (int i = threadIdx.x; i < ((n + 31) & ~31) * stride; i += blockDim.x) rows[i] = 0;     // the local marks, sent already
+    asm volatile("cp.async.wait_all;" ::: "memory");     // also completes the next graph's staging copies, harmlessly
+    __syncthreads();
+    const bool pairs = (MW & 1) == 0;
+    const int per_row = pairs ? MW >> 1 : MW;
+    const int items = n * per_row;                  // (source node, word or word pair)
+    for (int i0 = threadIdx.x; i0 < items; i0 += kInFlight * blockDim.x) {
+        int u[kInFlight], w[kInFlight];
+        u32 e0[kInFlight], deg[kInFlight], maxdeg = 0;
+#pragma unroll
+        for (int q = 0; q < kInFlight; ++q) {
+            const int i = i0 + q * (int)blockDim.x;
+            u[q] = i < items ? i / per_row : 0;
+            w[q] = (i - u[q] * per_row) << (pairs ? 1 : 0);
+            e0[q] = gv.eidx[u[q]] - gv.e_off;
+            deg[q] = i < items ? gv.degree[u[q]] : 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < kInFlight; ++q) maxdeg = max(maxdeg, deg[q]);
+        for (u32 k = 0; k < maxdeg; ++k) {
+            u32 dst[kInFlight], ty[kInFlight];
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) {
+                const bool row_ok = k < deg[q] && e0[q] + k < gv.e_cnt;
+                dst[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k)] : ~0u;
+                ty[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k) + 1] : 0u;
+            }
+#pragma unroll
+            for (int q = 0; q < kInFlight; ++q) {
+                if (dst[q] >= (u32)n) continue;                            // no edge in this slot, or a malformed edge: never fault
+                const u32 tq = ty[q] >= (u32)MS ? ty[q] % (u32)MS : ty[q];
+                const u32 *row = src + (size_t)u[q] * MW;
+                const u32 lo = rotated_word(row, w[q], tq, MS, MW);
+                if (lo) atomicOr(rows + (size_t)dst[q] * stride + w[q], lo);
+                if (pairs) {
+                    const u32 hi = rotated_word(row, w[q] + 1, tq, MS, MW);
+                    if (hi) atomicOr(rows + (size_t)dst[q] * stride + w[q] + 1, hi);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (out != nullptr)
+        for (int v = blockIdx.x; v < n; v += gridDim.x)
+            for (int w = threadIdx.x; w < MW; w += blockDim.x) out[(size_t)v * MW + w] = rows[(size_t)v * stride + w];
 }
 
 // In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.
@@ -763,20 +847,39 @@ __device__ __forceinline__ u32 eval_clause_layer_transposed(const DevModel &m, c
             u32 iw = __shfl_sync(kFull, iw_l, bw);
             const int w = w0 + bw;
             // up to four included literals per step, their loads issued together
-            auto literal_row = [&](int b) -> u32 {
-                if (d == 0) return tg.T[(size_t)(b * WT + w) * tg.S + col];
-                const int l = 32 * w + b;                                   // message literal: positive bits, then their complements
-                const int p = l < m.MS ? l : l - m.MS;
-                const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + col];
-                return l < m.MS ? x : ~x;
-            };
-            while (iw) {
-                u32 x0, x1 = kFull, x2 = kFull, x3 = kFull;
-                x0 = literal_row(__ffs(iw) - 1); iw &= iw - 1;
-                if (iw) { x1 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
-                if (iw) { x2 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
-                if (iw) { x3 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
-                r &= (x0 & x1) & (x2 & x3);
+            if (d == 0 || (m.MS & 31) == 0) {
+                // The 32 literals of an include word sit WT * S words apart in T, and a message word is all positive bits
+                // (w < MW) or all complements: one multiply-add and one load per included literal, the rows of a
+                // complement word are ORed and taken out of r at the end.
+                const bool neg = d > 0 && w >= m.MW;
+                const u32 *base = tg.T + (size_t)(neg ? w - m.MW : w) * tg.S + col;
+                const int step = WT * tg.S;
+                u32 acc = neg ? 0u : kFull;
+                while (iw) {
+                    u32 x0, x1, x2, x3;
+                    x0 = base[(__ffs(iw) - 1) * step]; iw &= iw - 1;
+                    x1 = x0; x2 = x0; x3 = x0;
+                    if (iw) { x1 = base[(__ffs(iw) - 1) * step]; iw &= iw - 1; }
+                    if (iw) { x2 = base[(__ffs(iw) - 1) * step]; iw &= iw - 1; }
+                    if (iw) { x3 = base[(__ffs(iw) - 1) * step]; iw &= iw - 1; }
+                    acc = neg ? acc | ((x0 | x1) | (x2 | x3)) : acc & ((x0 & x1) & (x2 & x3));
+                }
+                r &= neg ? ~acc : acc;
+            } else {
+                auto literal_row = [&](int b) -> u32 {
+                    const int l = 32 * w + b;                                   // message literal: positive bits, then their complements
+                    const int p = l < m.MS ? l : l - m.MS;
+                    const u32 x = tg.T[(size_t)((p & 31) * WT + (p >> 5)) * tg.S + col];
+                    return l < m.MS ? x : ~x;
+                };
+                while (iw) {
+                    u32 x0, x1 = kFull, x2 = kFull, x3 = kFull;
+                    x0 = literal_row(__ffs(iw) - 1); iw &= iw - 1;
+                    if (iw) { x1 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                    if (iw) { x2 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                    if (iw) { x3 = literal_row(__ffs(iw) - 1); iw &= iw - 1; }
+                    r &= (x0 & x1) & (x2 & x3);
+                }
             }
             alive = __any_sync(kFull, r != 0);
         }

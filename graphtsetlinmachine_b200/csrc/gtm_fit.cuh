@@ -13,6 +13,8 @@ struct FitArgs {
     int epochs;
     unsigned long long *exchange;   // this rank's vote exchange area, see exchange_class_sums
     u32 *P_pair[2];         // message buffers, ping-pong by graph parity ([D-1][max_nodes][MW] each)
+    u32 *Q_rows;            // [D-1][max_nodes][MW] destination message rows of the current graph, written by the CTAs that build
+                            // them from merged marks (graphs of more than 32 nodes), read by the feedback
     int max_nodes;
     unsigned *barrier;      // monotonically increasing arrival counter (zeroed before launch)
     int *error;             // set to 1 when a bounded wait gave up
@@ -210,13 +212,36 @@ __device__ __forceinline__ void draw4_at(const DevModel &m, int clause, u64 bloc
 // 4 consecutive draws; the warp's 128 outcomes are packed, in draw order, into 4 words returned in every lane:
 // bit t of the packed stream = [uniform(draw 4*first_block + 128*round + t) <= p]  (kernels.py:158-162 makes
 // bit b of a word's mask from the word's b-th draw; the caller aligns words to the stream with a funnel shift).
-__device__ __forceinline__ u32 bernoulli_nibbles(const DevModel &m, int clause, u64 block, float p, int lane)
+// Type-I mask probability of a layer: p = rd(1/s) and the number of 32-bit draws x whose uniform is <= p.  to_uniform is
+// monotone in x (conversion, exact scaling, one rounded addition), so [to_uniform(x) <= p] == [x < count] for every x:
+// one integer compare per draw instead of a conversion, a multiplication, an addition and a float compare.
+struct MaskProb {
+    float p;
+    u32 count;      // meaningless when p >= 1 (every draw passes; callers test p first)
+};
+
+__device__ __forceinline__ MaskProb mask_prob(float p)
+{
+    MaskProb mp;
+    mp.p = p;
+    // largest x with to_uniform(x) <= p, by bisection (to_uniform(0) = 2^-33; count = 0 when even that exceeds p)
+    unsigned long long lo = 0, hi = 0xffffffffull;
+    if (!(to_uniform(0u) <= p)) { mp.count = 0; return mp; }
+    while (lo < hi) {
+        const unsigned long long mid = (lo + hi + 1) >> 1;
+        if (to_uniform((u32)mid) <= p) lo = mid; else hi = mid - 1;
+    }
+    mp.count = (u32)(lo + 1);       // wraps to 0 only when p >= 1, which callers never ask for
+    return mp;
+}
+
+__device__ __forceinline__ u32 bernoulli_nibbles(const DevModel &m, int clause, u64 block, MaskProb p, int lane)
 {
     u32 o[4];
     draw4_at(m, clause, block, o);
     u32 nib = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) nib |= (to_uniform(o[i]) <= p ? 1u : 0u) << i;
+    for (int i = 0; i < 4; ++i) nib |= (o[i] < p.count ? 1u : 0u) << i;
     return nib << (4 * (lane & 7));
 }
 
@@ -245,10 +270,10 @@ template <int MAXSB>
 __device__ __forceinline__ u64 layer_feedback(const DevModel &m, int c, int layer, u32 *ta, int upd_lo, const int *update,
                                               bool clause_true, bool within_budget, const u32 *row, bool row_is_msg,
                                               u64 pos0, int g_begin, int g_end, int lane, u32 *pack, const u32 *pre, int pre_off,
-                                              float p)
+                                              MaskProb p)
 {
     const int W = layer == 0 ? m.L0 : m.M, SB = m.SB;
-    const bool all_ones = p >= 1.0f;         // every uniform is <= 1
+    const bool all_ones = p.p >= 1.0f;       // every uniform is <= 1
     const u64 first_block = pos0 >> 2;
     const int shift = (int)(pos0 & 3);       // the layer's first draw sits `shift` bits into the packed stream
     int positives = 0;
@@ -488,7 +513,7 @@ __device__ __forceinline__ Decision clause_decide(const DevModel &m, const Graph
 template <int MAXSB>
 __device__ __forceinline__ void clause_apply(const DevModel &m, const GraphView &gv, const ClauseView &cv, const FitArgs &a,
                                              const u32 *P, int p_nodes, const Decision &dec, int npos, int c, int lane,
-                                             u32 *pack, const u32 *pre, int pre0_off, int pre0_words, const float *p_mask)
+                                             u32 *pack, const u32 *pre, int pre0_off, int pre0_words, const MaskProb *p_mask)
 {
     const bool clause_true = dec.chosen != -1;
     if (m.K <= 32 && __ballot_sync(kFull, dec.upd_lo != 0) == 0) {      // no feedback for this clause: nothing drawn, nothing changes
@@ -513,7 +538,7 @@ template <int MAXSB>
 __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphView &gv, const ClauseView &cv,
                                                 const FitArgs &a, const u32 *bits, const u32 *P, int p_nodes,
                                                 const int *s_target, const float *s_thr, int c, int lane, u32 *pack,
-                                                const float *p_mask)
+                                                const MaskProb *p_mask)
 {
     const Decision dec = clause_decide(m, gv, cv, a, bits, s_target, s_thr, c, lane);
     clause_apply<MAXSB>(m, gv, cv, a, P, p_nodes, dec, 0, c, lane, pack, nullptr, 0, 0, p_mask);
@@ -523,7 +548,7 @@ __device__ __forceinline__ void clause_feedback(const DevModel &m, const GraphVi
 // first_block + 32q .. + 31 give 128 outcomes [uniform <= p], in draw order, = words 4q .. 4q+3 of the stream; words
 // below `need` are written to dst.
 __device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, u64 first_block, int need, int q, u32 *dst,
-                                                    int lane, float p)
+                                                    int lane, MaskProb p)
 {
     const u32 nib = bernoulli_nibbles(m, c, first_block + (u64)q * 32 + lane, p, lane);
     const u32 word = __reduce_or_sync(0xffu << (lane & 24), nib);
@@ -535,7 +560,7 @@ __device__ __forceinline__ void generate_mask_round(const DevModel &m, int c, u6
 // to shared memory once (constant indices here): a dynamically indexed parameter array would be spilled to local
 // memory and every access to it could miss the small L1 that is left beside the shared-memory carve-out.
 struct FitShared {
-    float p_mask[kMaxDepth];
+    MaskProb p_mask[kMaxDepth];
     u32 *P_peer[kMaxRanks][2];
 };
 
@@ -543,7 +568,7 @@ __device__ __forceinline__ void fill_fit_shared(FitShared *fs, const DevModel &m
 {
     if (threadIdx.x == 0) {
 #pragma unroll
-        for (int l = 0; l < kMaxDepth; ++l) fs->p_mask[l] = m.p_mask[l];
+        for (int l = 0; l < kMaxDepth; ++l) fs->p_mask[l] = mask_prob(m.p_mask[l]);
 #pragma unroll
         for (int r = 0; r < kMaxRanks; ++r) { fs->P_peer[r][0] = a.P_peer[r][0]; fs->P_peer[r][1] = a.P_peer[r][1]; }
     }

@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 GTM_LAP(t_clauses);
                 if (targets.local && merged_marks) {
                     __syncthreads();
-                    flush_marks(targets, gv.n, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
+                    flush_marks(targets, gv, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
                     GTM_LAP(t_merge);
                 } else if (targets.local) { // this CTA's share of the layer's messages, merged before the grid barrier
                     __syncthreads();

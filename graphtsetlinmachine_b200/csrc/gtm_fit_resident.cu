@@ -186,16 +186,19 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
         TransposedGraph tg;
         tg.T = s_T; tg.TM = s_T + (size_t)t_rows * a.t_stride; tg.S = a.t_stride; tg.words = (gv.n + 31) >> 5;
         const bool transposed = kBatchNodes && a.t_stride > 0 && gv.n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
-        if (a.timers == 3) GTM_LAPE(t_x0);
+        // larger graphs with a transposed copy: merged marks too; the destination rows are built in the local marks buffer
+        // (via the transposed buffer as scratch), transposed from there, and written to global memory for the feedback
+        const bool merged_large = kBatchNodes && !solo && transposed && s_part != nullptr && a.Q_rows != nullptr && m.D > 1 &&
+                                  gv.n * m.MW <= t_rows * a.t_stride &&
+                                  (((gv.n + 31) & ~31) + kTransposedTypes) * (m.MW | 1) <= a.part_words;
         // small graphs: the CTAs merge their source-node marks and build the message rows themselves (flush_marks)
         const bool merged_marks = !kBatchNodes && !solo && s_rows != nullptr && s_part != nullptr && gv.n <= 32 &&
                                   (32 + kTransposedTypes) * (m.MW | 1) <= a.part_words;
-        const u32 *rows_base = merged_marks ? s_rows : P;                  // message rows [D-1][rows_nodes][MW] of this graph
+        const u32 *rows_base = merged_marks ? s_rows : merged_large ? a.Q_rows : P;    // message rows [D-1][rows_nodes][MW] of this graph
         const int rows_nodes = merged_marks ? 32 : a.max_nodes;
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
-        if (a.timers == 3) GTM_LAPE(t_x1);
         fetch_sizes(step + 2, e_nxt2);
-        if (a.timers == 3) GTM_LAPE(t_x2); else GTM_LAPE(t_x0);
+        GTM_LAPE(t_x0);
 
         for (int d = 0; d < m.D; ++d) {
             const bool last = d == m.D - 1;
@@ -210,16 +213,23 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
                 if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, s_rows + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
+                if (merged_large) build_message_rows_large(P + (size_t)(d - 1) * layer_words, s_T, s_part, a.Q_rows + (size_t)(d - 1) * layer_words, gv, m.MS, m.MW);
+                if (a.timers == 3) GTM_LAPE(t_x1);
             }
             if (transposed) {
                 // this layer's literal rows, one bit per node: the graph's literals, or the messages of the layer below
                 if (d == 0) {
                     build_transposed(gv.X, gv.n, m.L0, m.L0, tg);
                     build_type_masks(gv.type, gv.n, g.n_types, tg);
+                } else if (merged_large) {
+                    build_transposed(s_part, gv.n, m.MW, m.MW | 1, tg);     // the rows build_message_rows_large left there
+                    __syncthreads();
+                    for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) s_part[t] = 0;   // this layer's marks
                 } else {
                     build_transposed(P + (size_t)(d - 1) * layer_words, gv.n, m.MW, m.MW, tg);
                 }
                 __syncthreads();
+                if (a.timers == 3) GTM_LAPE(t_x2);
             }
             ScatterTargets targets;
             targets.world = a.world;
@@ -242,10 +252,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 if (last && any)
                     for (int k = lane; k < m.K; k += 32) atomicAdd(&s_sum[k], cv.wgt[k]);
             }
-            if (a.timers != 3) GTM_LAPE(t_x1);
-            if (targets.local && merged_marks) {
+            if (a.timers == 3) GTM_LAPE(t_x3); else GTM_LAPE(t_x1);
+            if (targets.local && (merged_marks || merged_large)) {
                 __syncthreads();
-                flush_marks(targets, gv.n, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
+                flush_marks(targets, gv, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
                 if (a.timers != 3) GTM_LAPE(t_x3);
             } else if (targets.local) {     // this CTA's share of the layer's messages, merged before the grid barrier
                 __syncthreads();
@@ -256,7 +266,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             }
         }
         __syncthreads();
-        if (a.timers == 3) GTM_LAPE(t_x3); else GTM_LAPE(t_x2);
+        if (a.timers != 3) GTM_LAPE(t_x2);
         GTM_LAP(t_eval);
         if (solo) {
             for (int k = threadIdx.x; k < m.K; k += blockDim.x) {
@@ -271,7 +281,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
         // Layer 0's masks come from a Bernoulli stream that starts at Philox block B0 = (position after the node choice + K)
         // >> 2: at or before the first mask draw whatever the decisions turn out to be, so that its first rounds - enough
         // for one Type-I class - can be generated before the class sums are known.
-        const float p0 = s_fs.p_mask[0];
+        const MaskProb mp0 = s_fs.p_mask[0];
+        const float p0 = mp0.p;
         auto words0_of = [&](int npos, int off0) { return (npos > 0 && p0 < 1.0f) ? ((off0 + npos * m.L0 * 32 - 1) >> 5) + 1 : 0; };
         const int spec_rounds = (a.pre_words > 0 && p0 < 1.0f) ? (words0_of(1, m.K + 3) + 3) >> 2 : 0;
         if (a.pre_words > 0) {
@@ -284,7 +295,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 rec[5 + lane] = __float_as_int(pd.uni);
                 const u64 B0 = (pd.pos + (u64)m.K) >> 2;
                 for (int q = 0; q < spec_rounds; ++q)
-                    generate_mask_round(m, c, B0, 4 * spec_rounds, q, s_pre + (size_t)(c - c_lo) * a.pre_words, lane, p0);
+                    generate_mask_round(m, c, B0, 4 * spec_rounds, q, s_pre + (size_t)(c - c_lo) * a.pre_words, lane, mp0);
             }
         }
         bool inputs_done = true;
@@ -320,7 +331,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 u64 pos_l = dec.pos + (u64)npos * m.L0 * 32;
                 for (int l = 1; l < m.D; ++l) {
                     need += npos * m.M + 1;
-                    if (npos > 0 && s_fs.p_mask[l] < 1.0f) items += (npos * m.M + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
+                    if (npos > 0 && s_fs.p_mask[l].p < 1.0f) items += (npos * m.M + ((pos_l & 3) ? 1 : 0) + 3) >> 2;
                     pos_l += (u64)npos * m.M * 32;
                 }
                 __syncwarp();
@@ -360,7 +371,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     int r = i - firsti;
                     u32 *dst = s_pre + (size_t)ci * a.pre_words;
                     if (r < rounds0 - spec_rounds) {
-                        generate_mask_round(m, c_lo + ci, (pos - (u64)off0) >> 2, 4 * rounds0, spec_rounds + r, dst, lane, p0);
+                        generate_mask_round(m, c_lo + ci, (pos - (u64)off0) >> 2, 4 * rounds0, spec_rounds + r, dst, lane, mp0);
                         continue;
                     }
                     r -= max(0, rounds0 - spec_rounds);
@@ -368,7 +379,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     u64 pos_l = pos + (u64)npos * m.L0 * 32;
                     for (int l = 1; l < m.D; ++l) {
                         const int wneed = npos * m.M + ((pos_l & 3) ? 1 : 0);
-                        const int rounds = s_fs.p_mask[l] < 1.0f ? (wneed + 3) >> 2 : 0;
+                        const int rounds = s_fs.p_mask[l].p < 1.0f ? (wneed + 3) >> 2 : 0;
                         if (r < rounds) { generate_mask_round(m, c_lo + ci, pos_l >> 2, wneed, r, dst, lane, s_fs.p_mask[l]); break; }
                         r -= rounds;
                         dst += npos * m.M + 1;
@@ -539,6 +550,9 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
         for (int choice = part_possible ? 0 : 2; choice < 3; ++choice) {
             const int with_part = choice < 2, stage = choice != 1;
             int grid = std::max(1, std::min(per_sm * m->sm_count, (d.C + warps - 1) / warps));
+            // more CTAs than SMs: then two on (nearly) every SM, with fewer clauses each, rather than two on some SMs and
+            // one on the others - every step waits for the most loaded SM
+            if (grid > m->sm_count) grid = std::min(per_sm * m->sm_count, d.C);
             int cpb = (d.C + grid - 1) / grid;
             if (m->opt_fit_block_clauses > 0) cpb = m->opt_fit_block_clauses;
             grid = (d.C + cpb - 1) / cpb;
@@ -601,6 +615,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     memset(&a, 0, sizeof a);
     a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
     a.max_nodes = ds->max_nodes;
+    a.Q_rows = ds->Q_rows;
     a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
     a.class_sum_tap = m->class_sum_tap;
     a.phase_cycles = m->phase_cycles;

@@ -65,6 +65,7 @@ struct gtm_dataset {
     // learning scratch (every layer kept) and its message ping-pong
     EvalScratch fit_sc;
     u32 *P_pair[2] = {nullptr, nullptr};
+    u32 *Q_rows = nullptr;         // [D-1][max_nodes][MW] destination message rows of the current graph (learning, merged marks)
     // scoring scratch of the general path: one slice per CTA
     EvalScratch score_sc;
     size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;

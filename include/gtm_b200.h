@@ -90,7 +90,9 @@ int gtm_set_stream(gtm_model *model, void *cuda_stream);
  *   "fit_kernel":   0 = automatic, 1 = learning kernel with state in global memory, 2 = state-resident kernel
  *   "score_kernel": 0 = automatic, 1 = general kernel, 2 = node-stream kernel (depth 1), 3 = tile kernel (any depth,
  *                   graphs of at most 128 nodes); set it before the graph set is created
- *   "fit_timers":   1 = the learning kernels time their phases for gtm_debug_fit_phase_cycles (default 0)
+ *   "fit_timers":   1 = the learning kernels time their phases for gtm_debug_fit_phase_cycles (default 0); 2 and 3 = the
+ *                   state-resident kernel splits its evaluation phase instead of its feedback phase (see that function)
+ *   "fit_block_clauses": clauses per thread block of the state-resident learning kernel, 0 = automatic (default)
  *   "fit_wait_ms":  wall-time budget of ONE device-side wait of the learning kernels (grid barrier, vote exchange between
  *                   thread blocks or GPUs), 1..600000 ms, default 2000.  A wait that runs out ends the launch; gtm_fit
  *                   returns GTM_ERR_TIMEOUT, the CUDA context stays usable.  The state-resident kernel leaves the model as
@@ -235,12 +237,16 @@ int gtm_debug_evaluate(gtm_model *model, gtm_dataset *dataset, int number_of_nod
                        uint32_t *cno_out, uint32_t *messages_out, int32_t *n_inc_out, int32_t *class_sum_out);
 int gtm_debug_last_feedback(gtm_model *model, int32_t *clause_node_out, int32_t *class_clause_update_out);
 
-/* Profiling tap (no counterpart in the reference): SM clock cycles that CTA 0 of the last gtm_fit launch spent in
- * its phases, uint64[8] = {clause evaluation, waiting at grid barriers, summing vote partials, end of step (feedback), and
- * then for the state-resident kernel: decisions, work-item table, mask generation, automaton updates; for the
- * global-state kernel: clause loops, message merge, graph / message-row copies (these three are then not part of the
- * first figure), 0}.  Filled only by launches made
- * after gtm_set_option(model, "fit_timers", 1): the clock reads sit on the per-graph critical path. */
+/* Profiling tap (no counterpart in the reference): SM clock cycles that the first warp of CTA 0 of the last gtm_fit launch
+ * spent in its phases, uint64[8] = {clause evaluation, waiting at grid barriers, vote exchange (with the work done in
+ * its shadow), end of step, and then
+ *   state-resident kernel, "fit_timers" 1: decisions, work-item table, remaining mask generation, automaton updates;
+ *   state-resident kernel, "fit_timers" 2: next-graph copies issued, own clauses, waiting for the other warps, sending marks;
+ *   state-resident kernel, "fit_timers" 3: next-graph copies issued, message rows built, transposition, own clauses
+ *   (with 2 and 3 these four are not part of the first figure and the feedback is the fourth figure);
+ *   global-state kernel: clause loops, sending marks, message rows / copies (not part of the first figure), 0}.
+ * A phase that ends at a CTA barrier includes the wait for the CTA's slowest warp.  Filled only by launches made after
+ * gtm_set_option(model, "fit_timers", 1..3): the clock reads sit on the per-graph critical path. */
 int gtm_debug_fit_phase_cycles(gtm_model *model, uint64_t *cycles_out);
 
 /* Measurement aid (no counterpart in the reference): the device's rate of register-resident, dependence-free 32-bit
