@@ -63,8 +63,22 @@ def _worker(rank, world, port, tmpdir):
     g3, y3 = datasets.noisy_xor(1500, 1)
     run("xor", lambda: MultiClassGraphTsetlinMachine(10, 100, 1.0, depth=2, message_size=256, message_bits=2,
                                                      max_included_literals=4, seed=6, device=rank), g3, y3, 3)
+    # automaton layers wider than a warp (work items per 32-word stretch), small graphs (merged marks, rows per block)
+    np.random.seed(4)
+    g4 = random_graphs(40, rng, hv_size=1100, max_nodes=5, edge_types=2)
+    y4 = rng.integers(0, 2, size=40).astype(np.uint32)
+    run("wide", lambda: MultiClassGraphTsetlinMachine(24, 20, 4.0, depth=2, message_size=64, message_bits=2, seed=8, device=rank), g4, y4, 2)
+    # graphs of 200 nodes: merged marks with the rows built in the marks buffer
+    np.random.seed(4)
+    g5 = random_graphs(16, rng, hv_size=24, max_nodes=200, node_types=2, edge_types=3)
+    y5 = rng.integers(0, 2, size=16).astype(np.uint32)
+    run("large", lambda: MultiClassGraphTsetlinMachine(40, 30, 2.5, depth=3, message_size=96, message_bits=2, seed=9, device=rank), g5, y5, 2)
+    # fewer clauses than ranks: the second rank learns nothing and still takes part in every exchange and barrier
+    np.random.seed(4)
+    run("one_clause", lambda: MultiClassGraphTsetlinMachine(1, 10, 2.0, depth=2, message_size=64, message_bits=2, seed=10, device=rank), g1, y1, 2)
     if rank == 0:
-        np.save(os.path.join(tmpdir, "results.npy"), np.array([results[k] for k in ("depth1", "depth3", "xor")]))
+        np.save(os.path.join(tmpdir, "results.npy"),
+                np.array([results[k] for k in ("depth1", "depth3", "xor", "wide", "large", "one_clause")]))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -80,4 +94,4 @@ def test_clause_sharded_fit_equals_single_gpu_fit(engine_lib, tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     ok = np.load(tmp_path / "results.npy")
-    assert ok.tolist() == [True, True, True]
+    assert ok.tolist() == [True] * 6

@@ -2,12 +2,14 @@
 reference's kernels and (when its prebuilt host version travelled along) the reference kernels themselves.
 Everything is integer / bit work: the bar is equality."""
 
+import ctypes
 import os
 
 import numpy as np
 import pytest
 
 from cases import CASES, make_case, state_of
+from graphtsetlinmachine_b200 import _lib
 from oracle import build_ref
 from oracle.oracle import OracleTM
 from test_oracle import check_against_golden
@@ -128,6 +130,29 @@ def test_state_round_trip_and_load(engine_lib):
     a.fit(encY)
     b.fit(encY)
     assert_same_state(a, b, kw["depth"], "continued")
+    b.close()
+
+
+@pytest.mark.parametrize("options", [{"fit_block_clauses": 1}, {"fit_block_clauses": 5, "fit_timers": 2},
+                                     {"fit_timers": 3}, {"fit_timers": 1, "fit_kernel": 1}],
+                         ids=["one_clause_per_block", "five_per_block_timed", "timed", "global_state_timed"])
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_launch_shape_and_phase_timers_do_not_change_results(engine_lib, name, options):
+    """The learning result does not depend on how clauses are spread over thread blocks (every block boundary moves: more
+    blocks vote, merge marks and meet at the barriers) nor on the phase timers being on; the timers report something."""
+    kw, graphs, encY, epochs = make_case(name, seed=300 + sorted(CASES).index(name))
+    a, b = OracleTM(**kw), EngineTM(**kw, options=options)
+    for tm in (a, b):
+        tm.set_graphs(graphs)
+        tm.prepare()
+        for _ in range(epochs):
+            tm.fit(encY)
+    assert_same_state(a, b, kw["depth"], str(options))
+    assert np.array_equal(a.score(), b.score())
+    if options.get("fit_timers"):
+        cycles = (ctypes.c_uint64 * 8)()
+        _lib.check(engine_lib.gtm_debug_fit_phase_cycles(b.model, cycles))
+        assert sum(cycles) > 0
     b.close()
 
 

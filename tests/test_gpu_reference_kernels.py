@@ -223,7 +223,7 @@ def _assert_same_accuracy(a, b, what):
 
 def test_accuracy_after_training_matches_reference_kernels():
     """End-to-end accuracy, engine (Philox streams) against the reference's kernels on the same GPU (XORWOW states),
-    eight seeds per learner: the MNIST-shaped configuration after five passes over 10,000 graphs, and Noisy XOR at
+    the MNIST-shaped configuration after five passes over 10,000 graphs (sixteen seeds per learner), and Noisy XOR at
     s = 2.0 (where the task is learned reliably) after ten passes."""
     from graphtsetlinmachine_b200 import datasets
 
