@@ -16,7 +16,8 @@ struct FitArgs {
     u32 *Q_rows;            // [D-1][max_nodes][MW] destination message rows of the current graph, written by the CTAs that build
                             // them from merged marks (graphs of more than 32 nodes), read by the feedback
     int max_nodes;
-    unsigned *barrier;      // monotonically increasing arrival counter (zeroed before launch)
+    unsigned *barrier;      // monotonically increasing arrival counter: all CTAs (one GPU, zeroed before launch) or one arrival
+                            // per rank and barrier (clause-sharded fit), see grid_barrier
     int *error;             // set to 1 when a bounded wait gave up
     int *clause_node;       // [C]    tap: selected node of the last graph (kernels.py:347-349)
     int *update;            // [K][C] feedback type (kernels.py:385-387)
@@ -43,7 +44,8 @@ struct FitArgs {
     int world, rank;
     int c_begin, c_end;
     u32 tag_base;           // step tags of this launch are tag_base + step + 1
-    unsigned barrier_base;  // value of the arrival counters before this launch
+    unsigned barriers_done; // barriers of earlier launches on these counters (clause-sharded fit; 0 on one GPU)
+    unsigned *barrier_local; // this rank's local arrival counter (clause-sharded fit), see grid_barrier
     unsigned long long *exchange_peer[kMaxRanks];   // the exchange areas of all ranks
     unsigned *barrier_peer[kMaxRanks];
     u32 *P_peer[kMaxRanks][2];
@@ -65,30 +67,48 @@ struct WaitClock {
     }
 };
 
-// Barrier over all co-resident CTAs of all ranks (cooperative launch per rank; ranks of a clause-sharded fit run the
-// same step sequence).  Every CTA adds one arrival to the counter of EVERY rank (release; system scope when peers are
-// involved) and polls its own rank's counter (acquire).  Counters only grow, `target` is compared wrap-safely.  The
-// wait is bounded (WaitClock): when it runs out the CTA raises *error and gives up.  Returns false once any CTA gave up.
-__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned target)
+// Barrier number `nb` (counted from 1) over all co-resident CTAs of all ranks (cooperative launch per rank; the ranks of
+// a clause-sharded fit run the same step sequence).  Counters only grow; targets are compared wrap-safely.
+//   One GPU: every CTA adds one arrival to the counter (release) and polls it (acquire) until it reads nb * gridDim.x;
+//   the host zeroes the counter before every launch.
+//   Several GPUs, two levels: every CTA arrives on its own rank's LOCAL counter with one answering atomic (release at
+//   system scope: the CTA's marks may sit in peers' memory); the CTA whose arrival completes the rank's count for this
+//   barrier adds one arrival to the GLOBAL counter of every rank (release, system scope), and every CTA polls its own
+//   rank's global counter until it reads nb * world.  A peer's counter thus receives one remote atomic per rank and
+//   barrier instead of one per CTA (measured at 8 GPUs: the flat form spent tens of microseconds per barrier in remote
+//   atomics).  Both counters count over all launches of the shard set (nb continues from FitArgs::barriers_done).
+// The wait is bounded (WaitClock): when it runs out the CTA raises *error and gives up.  Returns false once any CTA gave up.
+__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
+        WaitClock clock;
         if (a.world == 1) {
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier) : "memory");
+            const unsigned expected = nb * (gridDim.x + (unsigned)a.missing);        // test hook: an arrival that never comes
+            while (true) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
+                if ((int)(seen - expected) >= 0) break;
+                if (*(volatile int *)a.error) break;
+                if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
+            }
         } else {
+            unsigned before;
+            asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(a.barrier_local) : "memory");
+            if (before + 1u == nb * (gridDim.x + (unsigned)a.missing)) {
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)      // constant indices: kernel parameters must not be indexed dynamically
-                if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
-        }
-        WaitClock clock;
-        const unsigned expected = target + (unsigned)a.missing;       // test hook: an arrival that never comes
-        while (true) {
-            unsigned seen;
-            if (a.world == 1) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
-            else asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
-            if ((int)(seen - expected) >= 0) break;
-            if (*(volatile int *)a.error) break;
-            if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
+                for (int r = 0; r < kMaxRanks; ++r)      // constant indices: kernel parameters must not be indexed dynamically
+                    if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
+            }
+            const unsigned expected = nb * (unsigned)a.world;
+            while (true) {
+                unsigned seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
+                if ((int)(seen - expected) >= 0) break;
+                if (*(volatile int *)a.error) break;
+                if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
+            }
         }
     }
     __syncthreads();

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
     const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
-    unsigned arrivals = a.barrier_base;
+    unsigned nb = a.barriers_done;           // barriers passed so far, see grid_barrier
 
     for (int k = threadIdx.x; k < m.K; k += blockDim.x) s_sum[k] = 0;
     for (int t = threadIdx.x; t < a.part_words; t += blockDim.x) s_part[t] = 0;
@@ -46,8 +46,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
             a.P_pair[0][t] = 0;
             a.P_pair[1][t] = 0;
         }
-        arrivals += gridDim.x * a.world;
-        if (!grid_barrier(a, arrivals)) return;
+        if (!grid_barrier(a, ++nb)) return;
     }
     // the whole first warp of CTA 0 reads the clock (a warp-uniform branch: one timing lane would serialise against the
     // other 31 and count their instructions as its own); lane 0 reports
@@ -123,8 +122,7 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 const bool last = d == m.D - 1;
                 if (d > 0) {
                     GTM_LAP(t_eval);
-                    arrivals += gridDim.x * a.world;
-                    if (!grid_barrier(a, arrivals)) return;
+                    if (!grid_barrier(a, ++nb)) return;
                     GTM_LAP(t_bar);
                     if (d == 1) clear_next_messages(m, a, par ? a.P_pair[0] : a.P_pair[1], step + 1 < steps ? (int)g.n_nodes[e_nxt] : 0);
                     // the marks of the layer below are complete: this CTA's message rows from them

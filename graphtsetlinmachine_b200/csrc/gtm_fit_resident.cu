@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
     const size_t layer_words = (size_t)a.max_nodes * m.MW;
     const int NC = a.NC;
     const u64 steps = (u64)a.epochs * (u64)a.count;
-    unsigned arrivals = a.barrier_base;
+    unsigned nb = a.barriers_done;           // barriers passed so far, see grid_barrier
 
     auto view_of = [&](int c) {
         u32 *basep = s_clauses + (size_t)(c - c_lo) * a.clause_words;
@@ -153,8 +153,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             a.P_pair[0][t] = 0;
             a.P_pair[1][t] = 0;
         }
-        arrivals += gridDim.x * a.world;
-        if (!grid_barrier(a, arrivals)) return;
+        if (!grid_barrier(a, ++nb)) return;
     }
     // the whole first warp of CTA 0 reads the clock (a warp-uniform branch: one timing lane would serialise against the
     // other 31 and count their instructions as its own); lane 0 reports
@@ -207,8 +206,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 if (solo) {
                     __syncthreads();
                 } else {
-                    arrivals += gridDim.x * a.world;
-                    if (!grid_barrier(a, arrivals)) return;
+                    if (!grid_barrier(a, ++nb)) return;
                 }
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
@@ -634,7 +632,8 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         a.world = cm.world; a.rank = cm.rank;
         const int per = shard_size(d.C, cm.world);
         a.c_begin = std::min(d.C, cm.rank * per); a.c_end = std::min(d.C, a.c_begin + per);
-        a.tag_base = cm.tag_base; a.barrier_base = cm.barrier_base;
+        a.tag_base = cm.tag_base; a.barriers_done = cm.barriers_done;
+        a.barrier_local = (unsigned *)((char *)cm.block + 128);
         for (int r = 0; r < cm.world; ++r) {
             char *base = (char *)cm.peer_block[r];
             a.barrier_peer[r] = (unsigned *)base;
@@ -651,7 +650,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         smem = cm.smem;
     } else {
         a.world = 1; a.rank = 0; a.c_begin = 0; a.c_end = d.C;
-        a.tag_base = 0; a.barrier_base = 0;
+        a.tag_base = 0; a.barriers_done = 0; a.barrier_local = nullptr;
         a.barrier_peer[0] = m->barrier; a.exchange_peer[0] = m->exchange;
         a.P_peer[0][0] = ds->P_pair[0]; a.P_peer[0][1] = ds->P_pair[1];
         GTM_CU(cudaMemsetAsync(m->barrier, 0, sizeof(unsigned), m->stream));
@@ -699,7 +698,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         const unsigned long long steps = (unsigned long long)epochs * (unsigned long long)count;
         const unsigned long long barriers = (d.D > 1 ? 1ull : 0ull) + steps * (unsigned long long)(d.D - 1);
         cm.tag_base += (u32)steps;
-        cm.barrier_base += (unsigned)(barriers * (unsigned long long)grid * (unsigned long long)cm.world);
+        cm.barriers_done += (unsigned)barriers;
     }
     int err = 0;
     GTM_CU(cudaMemcpyAsync(&err, m->error, sizeof(int), cudaMemcpyDeviceToHost, m->stream));

@@ -52,7 +52,7 @@ struct FitComm {
     size_t smem = 0;
     bool connected = false, broken = false;
     u32 tag_base = 0;
-    unsigned barrier_base = 0;
+    unsigned barriers_done = 0;    // grid barriers of all launches so far (the counters in `block` only grow)
 };
 
 struct gtm_dataset {
