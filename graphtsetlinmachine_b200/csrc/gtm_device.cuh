@@ -206,7 +206,6 @@ struct ScatterTargets {
     u32 *all;              // [kTransposedTypes][MW | 1] bits of clauses that are true on EVERY node of their type (one mark
                            // instead of one per node; flush_messages folds them into the rows), or null
     u32 *base[kMaxRanks];
-    u32 *own;              // flush_marks: this rank's merged-marks rows of the layer (the only buffer it writes)
 };
 
 __device__ __forceinline__ u32 *local_row(const ScatterTargets &t, int v, int MW)
@@ -333,11 +332,10 @@ __device__ __forceinline__ void flush_messages(const ScatterTargets &t, const Gr
 
 // Small graphs (at most 32 nodes), learning kernels: instead of walking the edges in every CTA and sending every rotated
 // row to the shared destination rows with atomics (flush_messages), a CTA sends only its SOURCE-node marks - one atomic
-// per non-empty word (pair) of a node, no edge walk, no answer needed - into its rank's merged-marks buffer (global
-// rows, node-major).  In a clause-sharded fit the barrier that follows copies every rank's merged marks into a slot on
-// every peer (MarkSend), with plain stores.  After the barrier every CTA reads the merged marks of all ranks once
-// (world * n * MW words) and builds the destination rows itself, in shared memory (build_message_rows).
-// All threads of the CTA, between two CTA barriers.
+// per non-empty word (pair) of a node, no edge walk, no answer needed on a single GPU - into the layer's merged-marks
+// buffer (the same global rows, node-major, on every rank; a clause-sharded fit sends a peer only the bits that were new
+// in its own buffer).  After the grid barrier every CTA reads the merged marks once (n * MW words) and builds the
+// destination rows itself, in shared memory (build_message_rows).  All threads of the CTA, between two CTA barriers.
 __device__ __forceinline__ void flush_marks(const ScatterTargets &t, const GraphView &gv, int MW)
 {
     const int n = gv.n;
@@ -359,37 +357,40 @@ __device__ __forceinline__ void flush_marks(const ScatterTargets &t, const Graph
         const u32 lo = row[w], hi = pairs ? row[w + 1] : 0u;
         if ((lo | hi) == 0) continue;
         const size_t at = (size_t)u * MW + w;
-        if (pairs) atomicOr(reinterpret_cast<unsigned long long *>(t.own + at), ((unsigned long long)hi << 32) | lo);
-        else atomicOr(t.own + at, lo);
+        if (pairs) {
+            unsigned long long v = ((unsigned long long)hi << 32) | lo;
+            if (t.world == 1) { atomicOr(reinterpret_cast<unsigned long long *>(t.base[0] + at), v); continue; }
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r == t.rank) v &= ~atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
+            if (v == 0) continue;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < t.world && r != t.rank) atomicOr(reinterpret_cast<unsigned long long *>(t.base[r] + at), v);
+        } else {
+            u32 v = lo;
+            if (t.world == 1) { atomicOr(t.base[0] + at, v); continue; }
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r == t.rank) v &= ~atomicOr(t.base[r] + at, v);
+            if (v == 0) continue;
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < t.world && r != t.rank) atomicOr(t.base[r] + at, v);
+        }
     }
-}
-
-// The other ranks' merged marks of a layer, as the barrier left them in this rank's slots (MarkSend): `slots` = this
-// rank's slot region of the step's parity, offset to the layer; source rank q's words start at q * slot_words.
-struct PeerMarks {
-    const u32 *slots;
-    int slot_words, world, rank;
-};
-
-__device__ __forceinline__ u32 merged_mark_word(const u32 *marks, const PeerMarks &pm, int i)
-{
-    u32 v = __ldcg(marks + i);
-    for (int q = 0; q < pm.world; ++q)
-        if (q != pm.rank) v |= __ldcg(pm.slots + (size_t)q * pm.slot_words + i);
-    return v;
 }
 
 // Destination rows of one layer from its merged source marks: rows[v] = OR over the edges (u -> v, type t) of marks[u]
 // rotated up by t ((hv + t) mod MS, kernels.py:581).  `marks` = the layer's merged-marks rows in global memory (complete:
 // call after the grid barrier), `tmp` = a CTA buffer of n rows with stride MW | 1 (the local marks buffer, which is left
 // cleared for the next layer), `rows` = [32][MW] in shared memory.  All threads of the CTA; ends with a CTA barrier.
-__device__ __forceinline__ void build_message_rows(const u32 *marks, const PeerMarks &pm, u32 *tmp, u32 *rows, const GraphView &gv,
-                                                   int MS, int MW)
+__device__ __forceinline__ void build_message_rows(const u32 *marks, u32 *tmp, u32 *rows, const GraphView &gv, int MS, int MW)
 {
     const int n = gv.n, stride = MW | 1;
     for (int i = threadIdx.x; i < n * MW; i += blockDim.x) {
         const int u = i / MW, w = i - u * MW;
-        tmp[u * stride + w] = pm.world > 1 ? merged_mark_word(marks, pm, i) : __ldcg(marks + i);
+        tmp[u * stride + w] = __ldcg(marks + i);
         rows[i] = 0;
     }
     __syncthreads();
@@ -420,14 +421,12 @@ __device__ __forceinline__ void build_message_rows(const u32 *marks, const PeerM
 // merged marks (node-major, stride MW), `rows` = the CTA's local marks buffer (n rows, stride MW | 1), which is left
 // holding the destination rows; `out` (global, node-major, stride MW), when given, receives them too, every CTA writing
 // the rows b, b + gridDim.x, ... - the feedback of the step reads single rows there.  All threads; ends with a barrier.
-__device__ __forceinline__ void build_message_rows_large(const u32 *marks, const PeerMarks &pm, u32 *src, u32 *rows, u32 *out,
-                                                         const GraphView &gv, int MS, int MW)
+__device__ __forceinline__ void build_message_rows_large(const u32 *marks, u32 *src, u32 *rows, u32 *out, const GraphView &gv,
+                                                         int MS, int MW)
 {
     const int n = gv.n, stride = MW | 1;
     constexpr int kInFlight = 4;      // loads per thread that are issued together (a larger graph's arrays are in global memory)
-    if (pm.world > 1) {
-        for (int i = threadIdx.x; i < n * MW; i += blockDim.x) src[i] = merged_mark_word(marks, pm, i);
-    } else if ((reinterpret_cast<uintptr_t>(marks) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    if ((reinterpret_cast<uintptr_t>(marks) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
         // 16 bytes per asynchronous copy, all of a thread's copies in flight at once
         const int quads = (n * MW) >> 2;
         for (int i = threadIdx.x; i < quads; i += blockDim.x) {

@@ -49,11 +49,6 @@ struct FitArgs {
     unsigned long long *exchange_peer[kMaxRanks];   // the exchange areas of all ranks
     unsigned *barrier_peer[kMaxRanks];
     u32 *P_peer[kMaxRanks][2];
-    // merged marks between GPUs: every rank has, per parity, one slot per SOURCE rank ([world][D-1][max_nodes][MW]); the rank's
-    // merged marks of a layer are copied into its slot on every peer by the CTA that completes the rank's barrier arrival
-    u32 *S_peer[kMaxRanks][2];
-    u32 *S_own[2];          // this rank's own slot regions (= S_peer[rank])
-    int slot_words;         // words per source rank in a slot region
 };
 
 // Every device-side wait (grid barrier, vote exchange) is bounded by wall time: FitArgs::wait_ns, set from the model
@@ -79,28 +74,16 @@ struct WaitClock {
 //   Several GPUs, two levels: every CTA arrives on its own rank's LOCAL counter with one answering atomic (release at
 //   system scope: the CTA's marks may sit in peers' memory); the CTA whose arrival completes the rank's count for this
 //   barrier adds one arrival to the GLOBAL counter of every rank (release, system scope), and every CTA polls its own
-//   rank's global counter until it reads nb * world.  Before it signals, the completing CTA also copies what the barrier
-//   carries (MarkSend) to the peers.  A peer's counter thus receives one remote atomic per rank and
+//   rank's global counter until it reads nb * world.  A peer's counter thus receives one remote atomic per rank and
 //   barrier instead of one per CTA (measured at 8 GPUs: the flat form spent tens of microseconds per barrier in remote
 //   atomics).  Both counters count over all launches of the shard set (nb continues from FitArgs::barriers_done).
 // The wait is bounded (WaitClock): when it runs out the CTA raises *error and gives up.  Returns false once any CTA gave up.
-// What the barrier carries to the other GPUs (clause-sharded fit, merged marks): `words` words at `src` (this rank's
-// merged marks of a layer, complete once all CTAs of the rank have arrived) go to word offset `at` of this rank's slot
-// on every peer, parity `par`.  words == 0: nothing.
-struct MarkSend {
-    const u32 *src;
-    int words;
-    size_t at;
-    int par;
-};
-
-__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb, const MarkSend &send)
+__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb)
 {
-    __shared__ int s_last;
     __syncthreads();
-    if (a.world == 1) {
-        if (threadIdx.x == 0) {
-            WaitClock clock;
+    if (threadIdx.x == 0) {
+        WaitClock clock;
+        if (a.world == 1) {
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier) : "memory");
             const unsigned expected = nb * (gridDim.x + (unsigned)a.missing);        // test hook: an arrival that never comes
             while (true) {
@@ -110,60 +93,26 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb, cons
                 if (*(volatile int *)a.error) break;
                 if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
             }
-        }
-        __syncthreads();
-        return *(volatile int *)a.error == 0;
-    }
-    if (threadIdx.x == 0) {
-        unsigned before;
-        asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(a.barrier_local) : "memory");
-        s_last = before + 1u == nb * (gridDim.x + (unsigned)a.missing);
-    }
-    __syncthreads();
-    const bool last = s_last != 0;
-    if (last && send.words > 0) {
-        // the whole CTA copies the rank's merged marks into the rank's slot on every peer: plain stores, 16 bytes where
-        // the addresses allow; thread 0's release below publishes them
+        } else {
+            unsigned before;
+            asm volatile("atom.acq_rel.sys.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(a.barrier_local) : "memory");
+            if (before + 1u == nb * (gridDim.x + (unsigned)a.missing)) {
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {                // constant indices: kernel parameters must not be indexed dynamically
-            if (r >= a.world || r == a.rank) continue;
-            u32 *dst = (send.par ? a.S_peer[r][1] : a.S_peer[r][0]) + (size_t)a.rank * a.slot_words + send.at;
-            int done = 0;
-            if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(send.src)) & 15) == 0) {
-                const int quads = send.words >> 2;
-                for (int i = threadIdx.x; i < quads; i += blockDim.x)
-                    reinterpret_cast<uint4 *>(dst)[i] = __ldcg(reinterpret_cast<const uint4 *>(send.src) + i);
-                done = quads << 2;
+                for (int r = 0; r < kMaxRanks; ++r)      // constant indices: kernel parameters must not be indexed dynamically
+                    if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
             }
-            for (int i = done + threadIdx.x; i < send.words; i += blockDim.x) dst[i] = __ldcg(send.src + i);
-        }
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) {
-        WaitClock clock;
-        if (last) {
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < a.world) asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(a.barrier_peer[r]) : "memory");
-        }
-        const unsigned expected = nb * (unsigned)a.world;
-        while (true) {
-            unsigned seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
-            if ((int)(seen - expected) >= 0) break;
-            if (*(volatile int *)a.error) break;
-            if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
+            const unsigned expected = nb * (unsigned)a.world;
+            while (true) {
+                unsigned seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier) : "memory");
+                if ((int)(seen - expected) >= 0) break;
+                if (*(volatile int *)a.error) break;
+                if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
+            }
         }
     }
     __syncthreads();
     return *(volatile int *)a.error == 0;
-}
-
-__device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb)
-{
-    MarkSend none;
-    none.src = nullptr; none.words = 0; none.at = 0; none.par = 0;
-    return grid_barrier(a, nb, none);
 }
 
 // Per-class quantities of the feedback decision that do not depend on the clause (kernels.py:373-384):

@@ -122,21 +122,11 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 const bool last = d == m.D - 1;
                 if (d > 0) {
                     GTM_LAP(t_eval);
-                    MarkSend send;       // the marks of the layer below travel with the barrier (clause-sharded fit)
-                    send.src = P + (size_t)(d - 1) * layer_words;
-                    send.words = (a.world > 1 && merged_marks) ? gv.n * m.MW : 0;
-                    send.at = (size_t)(d - 1) * layer_words;
-                    send.par = par;
-                    if (!grid_barrier(a, ++nb, send)) return;
+                    if (!grid_barrier(a, ++nb)) return;
                     GTM_LAP(t_bar);
                     if (d == 1) clear_next_messages(m, a, par ? a.P_pair[0] : a.P_pair[1], step + 1 < steps ? (int)g.n_nodes[e_nxt] : 0);
                     // the marks of the layer below are complete: this CTA's message rows from them
-                    if (merged_marks) {
-                        PeerMarks pm;
-                        pm.slots = (par ? a.S_own[1] : a.S_own[0]) + (size_t)(d - 1) * layer_words;
-                        pm.slot_words = a.slot_words; pm.world = a.world; pm.rank = a.rank;
-                        build_message_rows(P + (size_t)(d - 1) * layer_words, pm, s_part, const_cast<u32 *>(s_rows) + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
-                    }
+                    if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, const_cast<u32 *>(s_rows) + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
                 }
                 GTM_LAP(t_stage);
                 ScatterTargets targets;
@@ -147,7 +137,6 @@ __global__ void __launch_bounds__(512, 1) fit_kernel(DevModel m, DevGraphs g, Ev
                 targets.local = (!last && s_part != nullptr && ((gv.n + 31) & ~31) * (m.MW | 1) <= a.part_words) ? s_part : nullptr;
                 #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
-                targets.own = P + (size_t)d * layer_words;
                 for (int c = a.c_begin + gwarp; c < a.c_end; c += nwarps) {
                     const ClauseView cv = global_view(m, sc.n_inc, c);
                     if (c + nwarps < a.c_end) {       // the next clause's include words are on their way while this one is evaluated

@@ -206,20 +206,12 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 if (solo) {
                     __syncthreads();
                 } else {
-                    MarkSend send;       // the marks of the layer below travel with the barrier (clause-sharded fit)
-                    send.src = P + (size_t)(d - 1) * layer_words;
-                    send.words = (a.world > 1 && (merged_marks || merged_large)) ? gv.n * m.MW : 0;
-                    send.at = (size_t)(d - 1) * layer_words;
-                    send.par = par;
-                    if (!grid_barrier(a, ++nb, send)) return;
+                    if (!grid_barrier(a, ++nb)) return;
                 }
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
-                PeerMarks pm;
-                pm.slots = (par ? a.S_own[1] : a.S_own[0]) + (size_t)(d - 1) * layer_words;
-                pm.slot_words = a.slot_words; pm.world = a.world; pm.rank = a.rank;
-                if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, pm, s_part, s_rows + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
-                if (merged_large) build_message_rows_large(P + (size_t)(d - 1) * layer_words, pm, s_T, s_part, a.Q_rows + (size_t)(d - 1) * layer_words, gv, m.MS, m.MW);
+                if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, s_rows + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
+                if (merged_large) build_message_rows_large(P + (size_t)(d - 1) * layer_words, s_T, s_part, a.Q_rows + (size_t)(d - 1) * layer_words, gv, m.MS, m.MW);
                 if (a.timers == 3) GTM_LAPE(t_x1);
             }
             if (transposed) {
@@ -247,7 +239,6 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             targets.all = (targets.local != nullptr && transposed) ? s_part + a.part_words - all_words : nullptr;
             #pragma unroll
                 for (int r = 0; r < kMaxRanks; ++r) targets.base[r] = (par ? s_fs.P_peer[r][1] : s_fs.P_peer[r][0]) + (size_t)d * layer_words;
-            targets.own = P + (size_t)d * layer_words;
             for (int c = c_lo + warp; c < c_hi; c += nwarps) {
                 const ClauseView cv = view_of(c);
                 const u32 any = transposed
@@ -649,8 +640,6 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
             a.exchange_peer[r] = (unsigned long long *)(base + cm.exchange_off);
             a.P_peer[r][0] = (u32 *)(base + cm.P_off[0]);
             a.P_peer[r][1] = (u32 *)(base + cm.P_off[1]);
-            a.S_peer[r][0] = (u32 *)(base + cm.S_off[0]);
-            a.S_peer[r][1] = (u32 *)(base + cm.S_off[1]);
         }
         // the accumulators of the vote exchange start every launch at zero (they are this rank's own; the slots that
         // peers write keep their tags)
@@ -682,8 +671,6 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
     a.P_pair[0] = a.P_peer[a.rank][0]; a.P_pair[1] = a.P_peer[a.rank][1];
-    a.S_own[0] = a.S_peer[a.rank][0]; a.S_own[1] = a.S_peer[a.rank][1];
-    a.slot_words = (int)(cm.slot_bytes / sizeof(u32));
 
     DevModel dm = d;
     if (resident) {
@@ -759,11 +746,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     const size_t ex_bytes = (exchange_bytes(world, d.K) + 255) & ~(size_t)255;
     cm.P_off[0] = cm.exchange_off + ex_bytes;
     cm.P_off[1] = cm.P_off[0] + p_bytes;
-    // slots for the merged marks of every source rank, per parity
-    cm.slot_bytes = p_bytes;
-    cm.S_off[0] = cm.P_off[1] + p_bytes;
-    cm.S_off[1] = cm.S_off[0] + (size_t)world * p_bytes;
-    cm.bytes = cm.S_off[1] + (size_t)world * p_bytes;
+    cm.bytes = cm.P_off[1] + p_bytes;
     GTM_CU(cudaMalloc(&cm.block, cm.bytes));
     GTM_CU(cudaMemset(cm.block, 0, cm.bytes));
     cm.world = world; cm.rank = rank;
