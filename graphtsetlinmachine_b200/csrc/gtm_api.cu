@@ -453,7 +453,9 @@ static int dataset_build(gtm_model *m, const gtm_graphs_view *v, gtm_dataset *ds
     GTM_TRY(scratch(ds, &ds->fit_sc.n_inc, (size_t)d.C));
     GTM_TRY(scratch(ds, &ds->P_pair[0], p_words));
     GTM_TRY(scratch(ds, &ds->P_pair[1], p_words));
-    GTM_TRY(scratch(ds, &ds->Q_rows, p_words));
+    GTM_TRY(scratch(ds, &ds->Q_pair[0], p_words));
+    GTM_TRY(scratch(ds, &ds->Q_pair[1], p_words));
+    GTM_TRY(scratch(ds, &ds->rank_barrier, 64));
     ds->fit_sc.P = ds->P_pair[0];
 
     // general scoring scratch: one slice per resident CTA

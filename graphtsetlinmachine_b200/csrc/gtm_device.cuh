@@ -417,77 +417,45 @@ __device__ __forceinline__ void build_message_rows(const u32 *marks, u32 *tmp, u
     __syncthreads();
 }
 
-// build_message_rows for graphs of any size.  `src` = a CTA buffer of at least n * MW words that receives a copy of the
-// merged marks (node-major, stride MW), `rows` = the CTA's local marks buffer (n rows, stride MW | 1), which is left
-// holding the destination rows; `out` (global, node-major, stride MW), when given, receives them too, every CTA writing
-// the rows b, b + gridDim.x, ... - the feedback of the step reads single rows there.  All threads; ends with a barrier.
-__device__ __forceinline__ void build_message_rows_large(const u32 *marks, u32 *src, u32 *rows, u32 *out, const GraphView &gv,
-                                                         int MS, int MW)
+// Destination rows of a larger graph from the layer's merged marks, the work shared by the CTAs of the rank: CTA b
+// takes the source nodes b, b + gridDim.x, ... and ORs their rotated marks into the destination rows `out` (global,
+// node-major, stride MW, zero before the pass) with atomics that need no answer - n * degree * MW / 2 atomics per layer
+// for the whole rank.  `marks` = the layer's merged-marks rows (complete: call after the grid barrier); a rank-local
+// barrier has to follow before `out` is read.  All threads of the CTA.
+__device__ __forceinline__ void scatter_message_rows_share(const u32 *marks, u32 *out, const GraphView &gv, int MS, int MW)
 {
-    const int n = gv.n, stride = MW | 1;
-    constexpr int kInFlight = 4;      // loads per thread that are issued together (a larger graph's arrays are in global memory)
-    if ((reinterpret_cast<uintptr_t>(marks) & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        // 16 bytes per asynchronous copy, all of a thread's copies in flight at once
-        const int quads = (n * MW) >> 2;
-        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-            const unsigned dst = (unsigned)__cvta_generic_to_shared(src + 4 * i);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(marks + 4 * i) : "memory");
-        }
-        for (int i = 4 * quads + threadIdx.x; i < n * MW; i += blockDim.x) src[i] = __ldcg(marks + i);
-    } else {
-        for (int i0 = threadIdx.x; i0 < n * MW; i0 += kInFlight * blockDim.x) {
-            u32 v[kInFlight];
-#pragma unroll
-            for (int q = 0; q < kInFlight; ++q) v[q] = i0 + q * (int)blockDim.x < n * MW ? __ldcg(marks + i0 + q * blockDim.x) : 0u;
-#pragma unroll
-            for (int q = 0; q < kInFlight; ++q) if (i0 + q * (int)blockDim.x < n * MW) src[i0 + q * blockDim.x] = v[q];
-        }
-    }
-    for (int i = threadIdx.x; i < ((n + 31) & ~31) * stride; i += blockDim.x) rows[i] = 0;     // the local marks, sent already
-    asm volatile("cp.async.wait_all;" ::: "memory");     // also completes the next graph's staging copies, harmlessly
-    __syncthreads();
+    const int n = gv.n;
     const bool pairs = (MW & 1) == 0;
     const int per_row = pairs ? MW >> 1 : MW;
-    const int items = n * per_row;                  // (source node, word or word pair)
-    for (int i0 = threadIdx.x; i0 < items; i0 += kInFlight * blockDim.x) {
-        int u[kInFlight], w[kInFlight];
-        u32 e0[kInFlight], deg[kInFlight], maxdeg = 0;
-#pragma unroll
-        for (int q = 0; q < kInFlight; ++q) {
-            const int i = i0 + q * (int)blockDim.x;
-            u[q] = i < items ? i / per_row : 0;
-            w[q] = (i - u[q] * per_row) << (pairs ? 1 : 0);
-            e0[q] = gv.eidx[u[q]] - gv.e_off;
-            deg[q] = i < items ? gv.degree[u[q]] : 0u;
-        }
-#pragma unroll
-        for (int q = 0; q < kInFlight; ++q) maxdeg = max(maxdeg, deg[q]);
-        for (u32 k = 0; k < maxdeg; ++k) {
-            u32 dst[kInFlight], ty[kInFlight];
-#pragma unroll
-            for (int q = 0; q < kInFlight; ++q) {
-                const bool row_ok = k < deg[q] && e0[q] + k < gv.e_cnt;
-                dst[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k)] : ~0u;
-                ty[q] = row_ok ? gv.edge[2 * (size_t)(e0[q] + k) + 1] : 0u;
+    const int mine = ((int)blockIdx.x < n) ? (n - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;     // source nodes of this CTA
+    for (int i = threadIdx.x; i < mine * per_row; i += blockDim.x) {
+        const int u = (int)blockIdx.x + (i / per_row) * (int)gridDim.x, w = (i % per_row) << (pairs ? 1 : 0);
+        const u32 *row = marks + (size_t)u * MW;
+        const u32 e0 = gv.eidx[u] - gv.e_off, deg = gv.degree[u];
+        for (u32 k = 0; k < deg && e0 + k < gv.e_cnt; ++k) {
+            const u32 dst = gv.edge[2 * (size_t)(e0 + k)], ty = gv.edge[2 * (size_t)(e0 + k) + 1];
+            if (dst >= (u32)n) continue;                               // malformed edge: ignore, never fault
+            const u32 tq = ty >= (u32)MS ? ty % (u32)MS : ty;
+            u32 lo, hi = 0;
+            if ((MS & 31) == 0) {                                       // two or three words of the source row, read past L1
+                const u32 start = (u32)(32 * w + MS - (int)tq);
+                const u32 s0 = start >= (u32)MS ? start - (u32)MS : start;
+                const int i0 = (int)(s0 >> 5), sh = (int)(s0 & 31);
+                const int i1 = i0 + 1 < MW ? i0 + 1 : 0, i2 = i1 + 1 < MW ? i1 + 1 : 0;
+                const u32 a0 = __ldcg(row + i0), a1 = __ldcg(row + i1);
+                lo = __funnelshift_r(a0, a1, sh);
+                if (pairs) hi = __funnelshift_r(a1, __ldcg(row + i2), sh);
+            } else {
+                lo = rotated_word(row, w, tq, MS, MW);
+                if (pairs) hi = rotated_word(row, w + 1, tq, MS, MW);
             }
-#pragma unroll
-            for (int q = 0; q < kInFlight; ++q) {
-                if (dst[q] >= (u32)n) continue;                            // no edge in this slot, or a malformed edge: never fault
-                const u32 tq = ty[q] >= (u32)MS ? ty[q] % (u32)MS : ty[q];
-                const u32 *row = src + (size_t)u[q] * MW;
-                const u32 lo = rotated_word(row, w[q], tq, MS, MW);
-                if (lo) atomicOr(rows + (size_t)dst[q] * stride + w[q], lo);
-                if (pairs) {
-                    const u32 hi = rotated_word(row, w[q] + 1, tq, MS, MW);
-                    if (hi) atomicOr(rows + (size_t)dst[q] * stride + w[q] + 1, hi);
-                }
+            if (pairs) {
+                if (lo | hi) atomicOr(reinterpret_cast<unsigned long long *>(out + (size_t)dst * MW + w), ((unsigned long long)hi << 32) | lo);
+            } else if (lo) {
+                atomicOr(out + (size_t)dst * MW + w, lo);
             }
         }
     }
-    __syncthreads();
-    if (out != nullptr)
-        for (int v = blockIdx.x; v < n; v += gridDim.x)
-            for (int w = threadIdx.x; w < MW; w += blockDim.x) out[(size_t)v * MW + w] = rows[(size_t)v * stride + w];
 }
 
 // In-register transpose of a 32x32 bit matrix: on return bit i of a[b] is what bit b of a[i] was.

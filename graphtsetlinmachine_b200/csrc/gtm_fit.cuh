@@ -13,8 +13,9 @@ struct FitArgs {
     int epochs;
     unsigned long long *exchange;   // this rank's vote exchange area, see exchange_class_sums
     u32 *P_pair[2];         // message buffers, ping-pong by graph parity ([D-1][max_nodes][MW] each)
-    u32 *Q_rows;            // [D-1][max_nodes][MW] destination message rows of the current graph, written by the CTAs that build
-                            // them from merged marks (graphs of more than 32 nodes), read by the feedback
+    u32 *Q_pair[2];         // [D-1][max_nodes][MW] destination message rows by graph parity, which the CTAs of the rank build
+                            // together from the merged marks (graphs of more than 32 nodes, scatter_message_rows_share)
+    unsigned *barrier_rank; // arrival counter of the barriers among this rank's CTAs only (zeroed before launch)
     int max_nodes;
     unsigned *barrier;      // monotonically increasing arrival counter: all CTAs (one GPU, zeroed before launch) or one arrival
                             // per rank and barrier (clause-sharded fit), see grid_barrier
@@ -109,6 +110,27 @@ __device__ __forceinline__ bool grid_barrier(const FitArgs &a, unsigned nb)
                 if (*(volatile int *)a.error) break;
                 if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
             }
+        }
+    }
+    __syncthreads();
+    return *(volatile int *)a.error == 0;
+}
+
+// Barrier number `nb` (counted from 1 in every launch) among the CTAs of this rank only: what they exchange lives in
+// this GPU's memory, so device scope is enough and no other GPU is involved.  Bounded like every other wait.
+__device__ __forceinline__ bool rank_barrier(const FitArgs &a, unsigned nb)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        WaitClock clock;
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.barrier_rank) : "memory");
+        const unsigned expected = nb * (gridDim.x + (unsigned)a.missing);            // test hook: an arrival that never comes
+        while (true) {
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.barrier_rank) : "memory");
+            if ((int)(seen - expected) >= 0) break;
+            if (*(volatile int *)a.error) break;
+            if (clock.expired(a.wait_ns)) { atomicExch(a.error, 1); break; }
         }
     }
     __syncthreads();

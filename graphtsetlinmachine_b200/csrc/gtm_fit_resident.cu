@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
     const int NC = a.NC;
     const u64 steps = (u64)a.epochs * (u64)a.count;
     unsigned nb = a.barriers_done;           // barriers passed so far, see grid_barrier
+    unsigned nb_rank = 0;                    // and those among this rank's CTAs only, see rank_barrier
 
     auto view_of = [&](int c) {
         u32 *basep = s_clauses + (size_t)(c - c_lo) * a.clause_words;
@@ -187,13 +188,13 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
         const bool transposed = kBatchNodes && a.t_stride > 0 && gv.n > 32 && tg.words <= a.t_stride && g.n_types <= kTransposedTypes;
         // larger graphs with a transposed copy: merged marks too; the destination rows are built in the local marks buffer
         // (via the transposed buffer as scratch), transposed from there, and written to global memory for the feedback
-        const bool merged_large = kBatchNodes && !solo && transposed && s_part != nullptr && a.Q_rows != nullptr && m.D > 1 &&
-                                  gv.n * m.MW <= t_rows * a.t_stride &&
+        const bool merged_large = kBatchNodes && !solo && transposed && s_part != nullptr && a.Q_pair[0] != nullptr && m.D > 1 &&
                                   (((gv.n + 31) & ~31) + kTransposedTypes) * (m.MW | 1) <= a.part_words;
+        u32 *Q = par ? a.Q_pair[1] : a.Q_pair[0];
         // small graphs: the CTAs merge their source-node marks and build the message rows themselves (flush_marks)
         const bool merged_marks = !kBatchNodes && !solo && s_rows != nullptr && s_part != nullptr && gv.n <= 32 &&
                                   (32 + kTransposedTypes) * (m.MW | 1) <= a.part_words;
-        const u32 *rows_base = merged_marks ? s_rows : merged_large ? a.Q_rows : P;    // message rows [D-1][rows_nodes][MW] of this graph
+        const u32 *rows_base = merged_marks ? s_rows : merged_large ? Q : P;    // message rows [D-1][rows_nodes][MW] of this graph
         const int rows_nodes = merged_marks ? 32 : a.max_nodes;
         fetch_graph(step + 1, e_nxt);      // lands in the other stage buffer while this step runs
         fetch_sizes(step + 2, e_nxt2);
@@ -211,7 +212,18 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                 GTM_LAP(t_bar);
                 if (d == 1) clear_next_messages(m, a, par ? P_even : P_odd, step + 1 < steps ? s_size[(slot3 == 2 ? 0 : slot3 + 1) * 4] : 0);
                 if (merged_marks) build_message_rows(P + (size_t)(d - 1) * layer_words, s_part, s_rows + (size_t)(d - 1) * 32 * m.MW, gv, m.MS, m.MW);
-                if (merged_large) build_message_rows_large(P + (size_t)(d - 1) * layer_words, s_T, s_part, a.Q_rows + (size_t)(d - 1) * layer_words, gv, m.MS, m.MW);
+                if (kBatchNodes && d == 1 && !solo && a.Q_pair[0] != nullptr) {
+                    // the other parity's destination rows, last read in the step before this one, are cleared for the step
+                    // after it - in every step, whichever way this step's graph passes its messages
+                    u32 *Q_other = par ? a.Q_pair[0] : a.Q_pair[1];
+                    const size_t words = (size_t)(m.D - 1) * layer_words;
+                    for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < words; t += (size_t)gridDim.x * blockDim.x) Q_other[t] = 0;
+                }
+                if (merged_large) {
+                    // the rank's CTAs build the layer's destination rows together, in global memory, and meet again
+                    scatter_message_rows_share(P + (size_t)(d - 1) * layer_words, Q + (size_t)(d - 1) * layer_words, gv, m.MS, m.MW);
+                    if (!rank_barrier(a, ++nb_rank)) return;
+                }
                 if (a.timers == 3) GTM_LAPE(t_x1);
             }
             if (transposed) {
@@ -220,9 +232,7 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
                     build_transposed(gv.X, gv.n, m.L0, m.L0, tg);
                     build_type_masks(gv.type, gv.n, g.n_types, tg);
                 } else if (merged_large) {
-                    build_transposed(s_part, gv.n, m.MW, m.MW | 1, tg);     // the rows build_message_rows_large left there
-                    __syncthreads();
-                    for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) s_part[t] = 0;   // this layer's marks
+                    build_transposed(Q + (size_t)(d - 1) * layer_words, gv.n, m.MW, m.MW, tg);
                 } else {
                     build_transposed(P + (size_t)(d - 1) * layer_words, gv.n, m.MW, m.MW, tg);
                 }
@@ -254,6 +264,10 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
             if (targets.local && (merged_marks || merged_large)) {
                 __syncthreads();
                 flush_marks(targets, gv, m.MW);   // build_message_rows reuses and clears the buffer after the grid barrier
+                if (merged_large) {               // ... larger graphs never come back to it: cleared here
+                    __syncthreads();
+                    for (int t = threadIdx.x; t < ((gv.n + 31) & ~31) * (m.MW | 1); t += blockDim.x) targets.local[t] = 0;
+                }
                 if (a.timers != 3) GTM_LAPE(t_x3);
             } else if (targets.local) {     // this CTA's share of the layer's messages, merged before the grid barrier
                 __syncthreads();
@@ -613,7 +627,6 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     memset(&a, 0, sizeof a);
     a.Y = Y_dev; a.first = first; a.count = count; a.epochs = epochs;
     a.max_nodes = ds->max_nodes;
-    a.Q_rows = ds->Q_rows;
     a.error = m->error; a.clause_node = m->clause_node; a.update = m->update;
     a.class_sum_tap = m->class_sum_tap;
     a.phase_cycles = m->phase_cycles;
@@ -623,6 +636,13 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     a.NC = ds->NC;
     const size_t p_bytes = (size_t)std::max(1, d.D - 1) * ds->max_nodes * d.MW * sizeof(u32);
     GTM_CU(cudaMemsetAsync(m->error, 0, sizeof(int), m->stream));
+    a.Q_pair[0] = ds->Q_pair[0]; a.Q_pair[1] = ds->Q_pair[1];
+    a.barrier_rank = ds->rank_barrier;
+    GTM_CU(cudaMemsetAsync(ds->rank_barrier, 0, sizeof(unsigned), m->stream));
+    if (d.D > 1) {      // the rows of both parities start empty; each step clears the other parity's for the step after it
+        GTM_CU(cudaMemsetAsync(ds->Q_pair[0], 0, p_bytes, m->stream));
+        GTM_CU(cudaMemsetAsync(ds->Q_pair[1], 0, p_bytes, m->stream));
+    }
 
     int grid, block;
     size_t smem;

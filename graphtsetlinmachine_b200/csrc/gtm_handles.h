@@ -65,7 +65,8 @@ struct gtm_dataset {
     // learning scratch (every layer kept) and its message ping-pong
     EvalScratch fit_sc;
     u32 *P_pair[2] = {nullptr, nullptr};
-    u32 *Q_rows = nullptr;         // [D-1][max_nodes][MW] destination message rows of the current graph (learning, merged marks)
+    u32 *Q_pair[2] = {nullptr, nullptr};   // [D-1][max_nodes][MW] destination message rows by graph parity (learning, merged marks)
+    unsigned *rank_barrier = nullptr;      // arrival counter of the barriers among one rank's CTAs
     // scoring scratch of the general path: one slice per CTA
     EvalScratch score_sc;
     size_t cno_stride = 0, P_stride = 0, ninc_stride = 0;
