@@ -27,11 +27,11 @@ constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I clas
 // Per graph the remaining global traffic is the vote exchange and, for depth > 1, the message rows.
 // State is loaded at the start of the launch and written back at its end.
 //   shared memory: [K] vote partial | [K] totals | [2][K] targets | [3][4] graph sizes | [2] staged graphs |
-//                  [12] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
+//                  [warps] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
 //                  per owned clause: clause_words words =
 //                  draw counter (2) | include count (1) | pad (1) | weights [K] | hypervector [MB] | node words [2][NC] | planes
 template <int MAXSB, bool kBatchNodes, bool kOneLayer>
-__global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, DevGraphs g, FitArgs a)
+__global__ void __launch_bounds__(768, 1) fit_resident_kernel(DevModel m_in, DevGraphs g, FitArgs a)
 {
     // kOneLayer: the depth is the compile-time constant 1, which removes the message passing, the grid barriers and the
     // message-layer feedback from the code.  The kernel's loop body is executed once per graph: what it does not contain
@@ -47,8 +47,8 @@ __global__ void __launch_bounds__(384, 2) fit_resident_kernel(DevModel m_in, Dev
     float *s_thr = reinterpret_cast<float *>(s_mem + 5 * KP);
     int *s_size = s_mem + 6 * KP;                                           // [3][4]: n, first node, first edge row, edge rows
     u32 *s_stage = reinterpret_cast<u32 *>(s_size + 12);                    // [2][kStageWords]
-    u32 *s_pack = s_stage + (a.stage ? 2 * kStageWords : 0);                                // [12][kPackWords]
-    int *s_rec = reinterpret_cast<int *>(s_pack + 12 * kPackWords);       // [clauses_per_cta][kRecWords] decisions of the step
+    u32 *s_pack = s_stage + (a.stage ? 2 * kStageWords : 0);                                // [warps][kPackWords]
+    int *s_rec = reinterpret_cast<int *>(s_pack + (blockDim.x >> 5) * kPackWords);       // [clauses_per_cta][kRecWords] decisions of the step
     int *s_item_off = s_rec + (size_t)a.clauses_per_cta * kRecWords;       // work-item table: entries, items, then (clause, first item) pairs
     u32 *s_pre = reinterpret_cast<u32 *>(s_item_off + 2 * a.clauses_per_cta + 2);   // [clauses_per_cta][pre_words]
     u32 *s_clauses = s_pre + (size_t)a.clauses_per_cta * a.pre_words;
@@ -520,7 +520,9 @@ int fit_grid_for_global_state(const DevModel &d, int sm_count, int block, int *g
 
 static int words_for(int bits) { return (bits - 1) / 32 + 1; }
 
-constexpr int kResidentThreads = 384;   // 12 warps, two CTAs per SM
+constexpr int kResidentThreads = 384;   // 12 warps when two CTAs share an SM; a CTA that has its SM to itself gets a warp per
+                                        // clause, up to kResidentMaxWarps (the kernel's register budget is that of 768 threads)
+constexpr int kResidentMaxWarps = 24;
 
 // The state-resident kernel for the automaton width, with four-at-a-time node words for graph sets of more than 32 nodes per graph.
 static const void *resident_kernel_for(int state_bits, int max_nodes, int depth)
@@ -534,7 +536,7 @@ static const void *resident_kernel_for(int state_bits, int max_nodes, int depth)
 }
 
 // Shape of a state-resident launch, or grid == 0 when the model's state does not fit in shared memory.
-struct ResidentPlan { int grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0; size_t smem = 0; };
+struct ResidentPlan { int threads = kResidentThreads, grid = 0, clauses_per_cta = 0, clause_words = 0, pre_words = 0, solo = 0, p_smem_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0; size_t smem = 0; };
 
 static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int n_clauses, bool solo_allowed)
 {
@@ -569,7 +571,11 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
             if (m->opt_fit_block_clauses > 0) cpb = m->opt_fit_block_clauses;
             grid = (d.C + cpb - 1) / cpb;
             if (grid > per_sm * m->sm_count) continue;
-            size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + (stage ? 2 * (size_t)kStageWords : 0) + 12 * (size_t)kPackWords) * sizeof(int) +
+            // one CTA per SM: a warp per clause where the CTA has more clauses than the usual twelve warps (two rounds of
+            // clause work per phase otherwise); tried first, the usual size second
+            for (int attempt = (per_sm == 1 && cpb > warps) ? 0 : 1; attempt < 2; ++attempt) {
+            const int cta_warps = attempt == 0 ? std::min(kResidentMaxWarps, cpb) : warps;
+            size_t smem = ((size_t)6 * ((d.K + 3) & ~3) + 12 + (stage ? 2 * (size_t)kStageWords : 0) + (size_t)cta_warps * kPackWords) * sizeof(int) +
                           ((size_t)cpb * kRecWords + 2 * (size_t)cpb + 2 + (size_t)cpb * pre_words) * sizeof(int) +
                           (size_t)cpb * words * sizeof(u32);
             // a model that one CTA learns alone needs no grid-wide step; its message buffers (two parities) then live in
@@ -589,15 +595,17 @@ static ResidentPlan plan_resident(const gtm_model *m, const gtm_dataset *ds, int
                 }
             }
             if (with_t) smem += t_bytes;
-            if (smem > 200 * 1024) continue;
+            if (smem > 220 * 1024) continue;
             if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); continue; }
             int occ = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, kResidentThreads, smem) != cudaSuccess) { cudaGetLastError(); continue; }
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, 32 * cta_warps, smem) != cudaSuccess) { cudaGetLastError(); continue; }
             if ((long long)occ * m->sm_count < grid) continue;
+            plan.threads = 32 * cta_warps;
             plan.grid = grid; plan.clauses_per_cta = cpb; plan.clause_words = words; plan.pre_words = pre_words; plan.smem = smem;
             plan.solo = solo; plan.p_smem_words = p_smem_words; plan.part_words = part_words; plan.stage = stage; plan.rows_words = rows_words;
             plan.t_stride = with_t ? t_stride : 0;
             return plan;
+            }
         }
     }
     return plan;
@@ -644,7 +652,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         GTM_CU(cudaMemsetAsync(ds->Q_pair[1], 0, p_bytes, m->stream));
     }
 
-    int grid, block;
+    int grid, block, resident_threads = kResidentThreads;
     size_t smem;
     const void *fn;
     bool resident;
@@ -665,7 +673,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         // peers write keep their tags)
         GTM_CU(cudaMemsetAsync((char *)cm.block + cm.exchange_off + (size_t)2 * cm.world * d.K * sizeof(unsigned long long), 0,
                                (size_t)4 * d.K * sizeof(unsigned long long), m->stream));
-        resident = cm.resident; grid = cm.grid;
+        resident = cm.resident; grid = cm.grid; resident_threads = cm.threads;
         a.clauses_per_cta = cm.clauses_per_cta; a.clause_words = cm.clause_words; a.pre_words = cm.pre_words; a.part_words = cm.part_words; a.stage = cm.stage; a.t_stride = cm.t_stride; a.rows_words = cm.rows_words;
         smem = cm.smem;
     } else {
@@ -687,7 +695,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
         grid = resident ? plan.grid : m->fit_grid;
         a.clauses_per_cta = plan.clauses_per_cta; a.clause_words = plan.clause_words; a.pre_words = plan.pre_words;
         a.solo = plan.solo; a.p_smem_words = plan.p_smem_words; a.part_words = plan.part_words; a.stage = plan.stage; a.t_stride = plan.t_stride; a.rows_words = plan.rows_words;
-        smem = plan.smem;
+        smem = plan.smem; resident_threads = plan.threads;
     }
     a.barrier = a.barrier_peer[a.rank]; a.exchange = a.exchange_peer[a.rank];
     a.P_pair[0] = a.P_peer[a.rank][0]; a.P_pair[1] = a.P_peer[a.rank][1];
@@ -695,7 +703,7 @@ int launch_fit(gtm_model *m, gtm_dataset *ds, int n_types, const int *Y_dev, int
     DevModel dm = d;
     if (resident) {
         fn = resident_kernel_for(d.SB, ds->max_nodes, d.D);
-        block = kResidentThreads;
+        block = resident_threads;
         // static and dynamic shared memory together may pass 48 KB well before the dynamic part alone does
         if (smem > 16 * 1024) GTM_CU(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void *args[] = {&dm, &g, &a};
@@ -755,7 +763,7 @@ extern "C" int gtm_shard_prepare(gtm_model *m, gtm_dataset *ds, int world, int r
     if (m->opt_fit_kernel != 1) plan = plan_resident(m, ds, per, false);
     cm.resident = plan.grid > 0;
     if (cm.resident) {
-        cm.grid = plan.grid; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
+        cm.grid = plan.grid; cm.threads = plan.threads; cm.clauses_per_cta = plan.clauses_per_cta; cm.clause_words = plan.clause_words;
         cm.pre_words = plan.pre_words; cm.part_words = plan.part_words; cm.stage = plan.stage; cm.t_stride = plan.t_stride; cm.rows_words = plan.rows_words; cm.smem = plan.smem;
     } else {
         const int warps = m->fit_block / 32;

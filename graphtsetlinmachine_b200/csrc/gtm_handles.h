@@ -48,7 +48,7 @@ struct FitComm {
     size_t bytes = 0, exchange_off = 0, P_off[2] = {0, 0};
     int world = 1, rank = 0, grid = 0;
     bool resident = false;
-    int clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0;
+    int threads = 384, clauses_per_cta = 0, clause_words = 0, pre_words = 0, part_words = 0, stage = 1, t_stride = 0, rows_words = 0;
     size_t smem = 0;
     bool connected = false, broken = false;
     u32 tag_base = 0;
