@@ -512,12 +512,13 @@ def run_config(idx, ctx, steps, warmup, headline):
         cudart.cudaHostRegister(a.ctypes.data, a.nbytes, 0)
     h2d = int(sum(a.nbytes for a in pinned))
     d2h = int(out_host.nbytes)
-    e2e_steps = max(1, min(steps, 5))
+    e2e_steps = max(1, min(steps, 10))
 
     def e2e_step():
         tm.graphs_signature_test = np.array([])              # forget the cached upload: copy the inputs again
         scorer.score_local(global_set, out=out_host)
 
+    e2e_step()
     e2e_step()
     barrier()
     t0 = time.perf_counter()
