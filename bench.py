@@ -123,6 +123,15 @@ NCU_DRAM_BYTES_PER_GRAPH = {1: (270.0e6 + 30.0e6) / 4194304,
                             4: (145.0e6 + 390.0e6) / 512,
                             5: (8.885644e9 + 3.636144e9) / 32768}
 
+# what binds the scoring kernel of every configuration according to its ncu capture (profiles/)
+NCU_BINDING = {
+    1: "tile_score_kernel<2>: short barrier-separated phases per tile (barrier stall 17.7 warps per issue); shared-memory wavefronts 27 % of peak, DRAM 1.2 %",
+    2: "stream_score_kernel<10>: shared memory (wavefronts 64 % of peak, short-scoreboard stall 5.7 warps per issue); DRAM 0.5 %",
+    3: "stream_score_kernel<10>: shared memory (wavefronts 62 % of peak); DRAM 0.5 %",
+    4: "score_graphs_kernel<1>: latency at 16 warps per SM with find-first-set loops on the quarter-rate pipe (XU 30 %, issue slots 43 %); DRAM 0.4 %",
+    5: "tile_score_kernel<10>: shared memory (wavefronts 76 % of peak, 4.8 % of them from bank conflicts, issue slots 53 %); DRAM 7.9 %",
+}
+
 
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
@@ -590,6 +599,7 @@ def run_config(idx, ctx, steps, warmup, headline):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None if traffic is None else traffic * n, "peak_source": peak_src,
                      "bytes_per_launch": shape["bytes_per_graph"] * n, "bytes_per_graph": shape["bytes_per_graph"],
+                     "binding_resource_ncu": NCU_BINDING.get(idx),
                      "int_ops": {"dense_lop3_per_graph": shape["lop3_per_graph"], "achieved_tlop3_s": tlop3,
                                  "peak_tlop3_s": int_peak, "frac": tlop3 / max(int_peak, 1e-9),
                                  "peak_source": "register-resident independent LOP3 chains measured in this run (gtm_debug_logic_op_rate)",
